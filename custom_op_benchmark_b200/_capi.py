@@ -1,0 +1,89 @@
+"""ctypes binding of libgraphop_b200.so, the C ABI declared in include/graphop_b200.h.
+
+The library is loaded from this package's directory and nowhere else.  There is no
+fallback: if the shared object is missing or a symbol cannot be resolved, importing the
+ops fails with an error that says how to build it.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libgraphop_b200.so")
+
+OK, ERR_INVALID_ARGUMENT, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_CUDA = range(5)
+
+OP_MASKEDMM_FWD, OP_MASKEDMM_BWD, OP_NODE_MUL_EDGE_FWD, OP_NODE_MUL_EDGE_BWD, OP_SOFTMAX_FWD, \
+    OP_SOFTMAX_BWD, OP_SPMM_FWD, OP_SPMM_BWD, OP_ATTENTION_FWD, OP_ATTENTION_BWD = range(10)
+
+ELEM_SUFFIXES = ("f32", "f64", "bf16")
+INDEX_SUFFIXES = ("i32", "i64")
+
+_P, _I64, _INT, _SZ, _DBL = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t, ctypes.c_double
+_TAIL = [_P, _SZ, _P]  # workspace, workspace_bytes, stream
+
+# argument lists of the typed entry points, in the order of include/graphop_b200.h
+SIGNATURES = {
+    "maskedmm_csr_forward": [_P] * 7 + [_I64] * 4 + [_INT] * 2 + _TAIL,
+    "maskedmm_csr_backward": [_P] * 4 + [_I64] + [_P] * 4 + [_I64] + [_P] * 5 + [_I64] * 3 + [_INT] * 2 + _TAIL,
+    "node_mul_edge_forward": [_P] * 6 + [_I64] * 3 + [_INT] * 2 + _TAIL,
+    "node_mul_edge_backward": [_P] * 8 + [_I64] * 3 + [_INT] * 2 + _TAIL,
+    "sparse_softmax_forward": [_P] * 5 + [_I64] * 3 + [_INT] + _TAIL,
+    "sparse_softmax_backward": [_P] * 6 + [_I64] * 3 + [_INT] + _TAIL,
+    "vector_spmm_forward": [_P] * 7 + [_I64] * 4 + [_INT] * 2 + _TAIL,
+    "vector_spmm_backward": [_P] * 4 + [_I64] + [_P] * 4 + [_I64] + [_P] * 5 + [_I64] * 3 + [_INT] * 2 + _TAIL,
+    "attention_forward": [_P] * 3 + [_I64] + [_P] * 3 + [_DBL] + [_P] * 2 + [_I64] * 3 + [_INT] * 2 + _TAIL,
+    "attention_backward": [_P] * 3 + [_I64] + [_P] * 3 + [_I64] + [_P] * 6 + [_DBL] + [_P] * 3 + [_I64] * 3
+                          + [_INT] * 2 + _TAIL,
+}
+
+UNTYPED = {
+    "graphop_version": ([], _INT),
+    "graphop_error_string": ([_INT], ctypes.c_char_p),
+    "graphop_last_cuda_error": ([], _INT),
+    "graphop_workspace_bytes": ([_INT, _I64, _I64, _INT, _INT, _INT, _INT], _SZ),
+    "graphop_check_graph_i32": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
+    "graphop_check_graph_i64": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
+}
+
+
+def exported_symbols():
+    """Every symbol include/graphop_b200.h declares."""
+    names = list(UNTYPED)
+    for op in SIGNATURES:
+        for e in ELEM_SUFFIXES:
+            for i in INDEX_SUFFIXES:
+                names.append("graphop_%s_%s_%s" % (op, e, i))
+    return names
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library with argtypes set; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "graphop_b200: %s is missing; build it with `python -m custom_op_benchmark_b200.build` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback." % LIB_PATH)
+    handle = ctypes.CDLL(LIB_PATH)
+    for name, (args, res) in UNTYPED.items():
+        fn = getattr(handle, name)
+        fn.argtypes, fn.restype = args, res
+    for op, args in SIGNATURES.items():
+        for e in ELEM_SUFFIXES:
+            for i in INDEX_SUFFIXES:
+                fn = getattr(handle, "graphop_%s_%s_%s" % (op, e, i))
+                fn.argtypes, fn.restype = args, _INT
+    _lib = handle
+    return handle
+
+
+def error_message(code):
+    handle = lib()
+    msg = handle.graphop_error_string(code).decode()
+    if code == ERR_CUDA:
+        msg += " (cudaError %d)" % handle.graphop_last_cuda_error()
+    return msg

@@ -1,0 +1,603 @@
+// Host side of the C ABI: argument checks, workspace carving, kernel selection and the
+// launch sequences.  Everything here enqueues on the caller's stream and never synchronises.
+#pragma once
+#include <cstdio>
+#include <type_traits>
+
+#include "../../include/graphop_b200.h"
+#include "gk_common.cuh"
+#include "gk_ops.cuh"
+#include "gk_softmax.cuh"
+
+namespace gk {
+
+inline thread_local int g_last_cuda_error = 0;
+
+#define GK_CUDA(expr)                                   \
+  do {                                                  \
+    cudaError_t err__ = (expr);                         \
+    if (err__ != cudaSuccess) {                         \
+      g_last_cuda_error = (int)err__;                   \
+      return GRAPHOP_ERR_CUDA;                          \
+    }                                                   \
+  } while (0)
+#define GK_LAUNCH_CHECK() GK_CUDA(cudaGetLastError())
+#define GK_TRY(expr)                    \
+  do {                                  \
+    int rc__ = (expr);                  \
+    if (rc__ != GRAPHOP_OK) return rc__; \
+  } while (0)
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+// Bump allocator over the caller's workspace.  With base == nullptr it only measures.
+struct Arena {
+  char* base;
+  size_t cap, used = 0;
+  bool overflow = false;
+  Arena(void* b, size_t c) : base((char*)b), cap(c) {}
+  void* take(size_t bytes) {
+    const size_t at = used;
+    used += align_up(bytes ? bytes : 1);
+    if (!base) return nullptr;
+    if (used > cap) { overflow = true; return nullptr; }
+    return base + at;
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// tiling
+// ---------------------------------------------------------------------------------------
+constexpr int kCarryTile = 256;
+constexpr int kMaxLevels = 12;
+
+// Positions per warp at level 0: small graphs get small tiles so that every SM has work,
+// large graphs get 256 so that carries stay a fraction of a percent of the traffic.
+inline int pick_tile(long long n_edges) {
+  long long t = 32;
+  while (t < 256 && n_edges / t > 16384) t <<= 1;
+  return (int)t;
+}
+
+struct Levels {
+  int n = 0;
+  long long len[kMaxLevels];
+  int tile[kMaxLevels];
+  long long ntiles[kMaxLevels];
+};
+inline Levels make_levels(long long n_edges, int tile0) {
+  Levels lv;
+  long long len = n_edges;
+  int tile = tile0;
+  for (;;) {
+    const long long nt = (len + tile - 1) / tile;
+    lv.len[lv.n] = len; lv.tile[lv.n] = tile; lv.ntiles[lv.n] = nt;
+    ++lv.n;
+    if (nt <= 1 || lv.n == kMaxLevels) break;
+    len = 2 * nt;
+    tile = kCarryTile;
+  }
+  return lv;
+}
+
+inline unsigned grid_for_warps(long long warps, int warps_per_cta) {
+  long long g = (warps + warps_per_cta - 1) / warps_per_cta;
+  return (unsigned)(g < 1 ? 1 : g);
+}
+
+// ---------------------------------------------------------------------------------------
+// graph preparation: erow[] and 32-bit index arrays
+// ---------------------------------------------------------------------------------------
+struct GraphView {
+  const PlanHeader* hdr;
+  const int32_t* erow;
+  const int32_t* other;  // may be null (ops without a second endpoint)
+  const int32_t* eid;    // may be null: identity
+  long long E;
+};
+
+template <typename I>
+inline int prepare_graph(Arena& ar, const I* row, const I* indptr, const I* eid, const I* indices, long long C,
+                         long long E, cudaStream_t st, GraphView* g) {
+  auto* hdr = (PlanHeader*)ar.take(sizeof(PlanHeader));
+  auto* erow = (int32_t*)ar.take((size_t)E * 4);
+  int32_t* other32 = nullptr;
+  int32_t* eid32 = nullptr;
+  if (sizeof(I) == 8) {
+    if (indices) other32 = (int32_t*)ar.take((size_t)E * 4);
+    if (eid) eid32 = (int32_t*)ar.take((size_t)E * 4);
+  }
+  if (!ar.base) return GRAPHOP_OK;
+  if (ar.overflow) return GRAPHOP_ERR_WORKSPACE;
+  const long long warps = (E + kExpandTile - 1) / kExpandTile;
+  expand_rows_kernel<I><<<grid_for_warps(warps, kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(row, indptr, C, E, erow, hdr);
+  GK_LAUNCH_CHECK();
+  g->hdr = hdr;
+  g->erow = erow;
+  g->E = E;
+  if (sizeof(I) == 8) {
+    const unsigned grid = (unsigned)((E + 1023) / 1024 < 4096 ? (E + 1023) / 1024 : 4096);
+    if (indices) {
+      narrow_index_kernel<I><<<grid ? grid : 1, 256, 0, st>>>(indices, other32, E);
+      GK_LAUNCH_CHECK();
+    }
+    if (eid) {
+      narrow_index_kernel<I><<<grid ? grid : 1, 256, 0, st>>>(eid, eid32, E);
+      GK_LAUNCH_CHECK();
+    }
+    g->other = other32;
+    g->eid = eid32;
+  } else {
+    g->other = (const int32_t*)indices;
+    g->eid = (const int32_t*)eid;
+  }
+  return GRAPHOP_OK;
+}
+
+inline int zero_uncovered(const GraphView& g, void* out, size_t bytes, cudaStream_t st) {
+  const long long words = (long long)(bytes / 4);
+  if (words == 0) return GRAPHOP_OK;
+  const unsigned grid = (unsigned)((words + 1023) / 1024 < 2048 ? (words + 1023) / 1024 : 2048);
+  zero_uncovered_kernel<uint32_t><<<grid, 256, 0, st>>>(g.hdr, g.E, (uint32_t*)out, words);
+  GK_LAUNCH_CHECK();
+  return GRAPHOP_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// vector shape selection
+// ---------------------------------------------------------------------------------------
+template <typename T> struct VecMax { static constexpr int value = 16 / (int)sizeof(T); };
+
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+inline bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+struct VecShape { int V, R, S; };
+// V elements per slot and R slots per lane for an H*D row; R = 0: does not fit 8 slots per lane.
+template <typename T>
+inline VecShape pick_shape(int HD, int D, bool all_aligned) {
+  VecShape s;
+  constexpr int VM = VecMax<T>::value;
+  s.V = (all_aligned && D % VM == 0) ? VM : 1;
+  s.S = HD / s.V;
+  if (s.V == 1) s.R = s.S <= 256 ? 8 : 0;
+  else s.R = s.S <= 32 ? 1 : s.S <= 64 ? 2 : s.S <= 128 ? 4 : s.S <= 256 ? 8 : 0;
+  return s;
+}
+
+// Calls f(integral_constant<int,V>, integral_constant<int,R>) for the instantiated pairs.
+template <typename T, class F>
+inline int dispatch_shape(const VecShape& s, F&& f) {
+  constexpr int VM = VecMax<T>::value;
+  using std::integral_constant;
+  if (s.V == 1 && s.R == 8) return f(integral_constant<int, 1>{}, integral_constant<int, 8>{});
+  if (s.V == VM) {
+    switch (s.R) {
+      case 1: return f(integral_constant<int, VM>{}, integral_constant<int, 1>{});
+      case 2: return f(integral_constant<int, VM>{}, integral_constant<int, 2>{});
+      case 4: return f(integral_constant<int, VM>{}, integral_constant<int, 4>{});
+      case 8: return f(integral_constant<int, VM>{}, integral_constant<int, 8>{});
+    }
+  }
+  return GRAPHOP_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------
+// level-0 + carry-level launch sequence of a row-producing op
+// ---------------------------------------------------------------------------------------
+// `make_op(carry_out, carry_in)` returns the op bound to one level's carry buffers.
+template <class MakeOp>
+inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_rows, size_t carry_elem_bytes,
+                          long long carry_stride, cudaStream_t st, MakeOp&& make_op) {
+  const Levels lv = make_levels(g.E, tile0);
+  void* carry[kMaxLevels];
+  int32_t* rows[kMaxLevels + 1];
+  rows[0] = nullptr;
+  for (int k = 0; k < lv.n; ++k) {
+    const bool last = k == lv.n - 1;
+    carry[k] = last ? nullptr : ar.take((size_t)(2 * lv.ntiles[k]) * carry_stride * carry_elem_bytes);
+    rows[k + 1] = last ? nullptr : (int32_t*)ar.take((size_t)(2 * lv.ntiles[k]) * 4);
+  }
+  if (!ar.base) return GRAPHOP_OK;
+  if (ar.overflow) return GRAPHOP_ERR_WORKSPACE;
+  for (int k = 0; k < lv.n; ++k) {
+    auto op = make_op(carry[k], k ? carry[k - 1] : nullptr);
+    using Op = decltype(op);
+    const unsigned grid = grid_for_warps(lv.ntiles[k], kWarpsPerCta);
+    if (k == 0)
+      walk_kernel<Op, false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E, lv.tile[0],
+                                                                n_rows, rows[1]);
+    else
+      walk_kernel<Op, true><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, rows[k], nullptr, nullptr, lv.len[k],
+                                                               lv.tile[k], n_rows, rows[k + 1]);
+    GK_LAUNCH_CHECK();
+  }
+  return GRAPHOP_OK;
+}
+
+// out[node] = sum_k w[eid[k]] * feat(k): picks the vector shape, splits very wide rows into
+// feature blocks of 256 slots (each block is an independent aggregation).
+template <typename T, bool kEdgeFeat>
+inline int run_aggregate(Arena& ar, const GraphView& g, const T* w, const T* x, T* y, long long n_rows, int H, int D,
+                         cudaStream_t st) {
+  using A = typename AccOf<T>::type;
+  const int HD = H * D;
+  const bool al = aligned16(x) && aligned16(y);
+  VecShape s = pick_shape<T>(HD, D, al);
+  const int tile0 = pick_tile(g.E);
+  const int block_elems = 256 * s.V;  // widest register-resident block
+  for (int feat0 = 0; feat0 < HD; feat0 += block_elems) {
+    const int elems = HD - feat0 < block_elems ? HD - feat0 : block_elems;
+    VecShape b = s;
+    b.S = elems / s.V;
+    if (s.V == 1) b.R = 8;
+    else b.R = b.S <= 32 ? 1 : b.S <= 64 ? 2 : b.S <= 128 ? 4 : 8;
+    const size_t mark = ar.used;
+    GK_TRY((dispatch_shape<T>(b, [&](auto Vc, auto Rc) -> int {
+      constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+      return run_row_levels(ar, g, tile0, n_rows, sizeof(A), HD, st, [&](void* cout, void* cin) {
+        AggregateOp<T, V, R, kEdgeFeat> op;
+        op.w = w; op.x = x; op.y = y; op.carry = (A*)cout; op.carry_in = (const A*)cin;
+        op.H = H; op.D = D; op.HD = HD; op.S = b.S; op.feat0 = feat0;
+        return op;
+      });
+    })));
+    if (feat0 + block_elems < HD) ar.used = mark;  // blocks run back to back on one stream: reuse the scratch
+  }
+  return GRAPHOP_OK;
+}
+
+// y[eid[k], h] = a[node(k), h, :] . feat(k)[h, :]
+template <typename T, bool kEdgeFeat>
+inline int run_edge_dot(const GraphView& g, const T* a, const T* b, T* y, int H, int D, cudaStream_t st) {
+  const int HD = H * D;
+  const bool al = aligned16(a) && aligned16(b);
+  const VecShape s = pick_shape<T>(HD, D, al);
+  const int tile0 = pick_tile(g.E);
+  const long long nt = (g.E + tile0 - 1) / tile0;
+  const unsigned grid = grid_for_warps(nt, kWarpsPerCta);
+  const int lph = D / s.V;
+  if (s.R == 0 || !is_pow2(lph)) {
+    EdgeDotAnyOp<T, kEdgeFeat> op;
+    op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD;
+    walk_kernel<decltype(op), false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E, tile0, 0,
+                                                                        nullptr);
+    GK_LAUNCH_CHECK();
+    return GRAPHOP_OK;
+  }
+  return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
+    constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+    EdgeDotOp<T, V, R, kEdgeFeat> op;
+    op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = lph;
+    walk_kernel<decltype(op), false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E, tile0, 0,
+                                                                        nullptr);
+    GK_LAUNCH_CHECK();
+    return (int)GRAPHOP_OK;
+  });
+}
+
+// dB[eid[k], :] = sum_h dy[eid[k], h] * A[node(k), h, :]
+template <typename T>
+inline int run_edge_mix(const GraphView& g, const T* dy, const T* a, T* db, int H, int D, cudaStream_t st) {
+  constexpr int VM = VecMax<T>::value;
+  const bool vec = aligned16(a) && aligned16(db) && D % VM == 0;
+  const long long total = g.E * (vec ? D / VM : D);
+  const unsigned grid = (unsigned)((total + 255) / 256 < (1 << 20) ? (total + 255) / 256 : (1 << 20));
+  if (vec) edge_mix_heads_kernel<T, VM><<<grid ? grid : 1, 256, 0, st>>>(g.erow, g.eid, dy, a, db, g.E, H, D);
+  else edge_mix_heads_kernel<T, 1><<<grid ? grid : 1, 256, 0, st>>>(g.erow, g.eid, dy, a, db, g.E, H, D);
+  GK_LAUNCH_CHECK();
+  return GRAPHOP_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// softmax
+// ---------------------------------------------------------------------------------------
+template <typename T, int H, bool kBackward>
+inline int run_softmax_heads(Arena& ar, const GraphView& g, const T* in0, const T* in1, T* out, long long n_nodes,
+                             int hs, int h0, cudaStream_t st) {
+  using A = typename AccOf<T>::type;
+  constexpr int kTile = SoftmaxSteps<H>::value * 32;
+  constexpr int kW = kBackward ? H : 2 * H;
+  const long long nt0 = (g.E + kTile - 1) / kTile;
+  // level 0 is the lane-per-edge kernel; levels >= 1 are generic carry levels over 2*nt0 slots
+  Levels lv = make_levels(2 * nt0, kCarryTile);
+  A* carry0 = (A*)ar.take((size_t)(2 * nt0) * kW * sizeof(A));
+  int32_t* rows1 = (int32_t*)ar.take((size_t)(2 * nt0) * 4);
+  A* stats = (A*)ar.take((size_t)n_nodes * kW * sizeof(A));
+  void* carry[kMaxLevels];
+  int32_t* rows[kMaxLevels + 1];
+  for (int k = 0; k < lv.n; ++k) {
+    const bool last = k == lv.n - 1;
+    carry[k] = last ? nullptr : ar.take((size_t)(2 * lv.ntiles[k]) * kW * sizeof(A));
+    rows[k + 1] = last ? nullptr : (int32_t*)ar.take((size_t)(2 * lv.ntiles[k]) * 4);
+  }
+  if (!ar.base) return GRAPHOP_OK;
+  if (ar.overflow) return GRAPHOP_ERR_WORKSPACE;
+  const unsigned grid0 = grid_for_warps(nt0, kSoftmaxWarps);
+  softmax_tile_kernel<T, H, kBackward><<<grid0, kSoftmaxWarps * 32, 0, st>>>(g.erow, g.eid, in0, in1, out, carry0, rows1,
+                                                                            g.E, hs, h0);
+  GK_LAUNCH_CHECK();
+  rows[0] = rows1;
+  for (int k = 0; k < lv.n; ++k) {
+    SegStatOp<A, !kBackward> op;
+    op.stats = stats; op.carry = (A*)carry[k]; op.carry_in = k ? (const A*)carry[k - 1] : carry0; op.H = H;
+    op.n_nodes = n_nodes;
+    walk_kernel<decltype(op), true><<<grid_for_warps(lv.ntiles[k], kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
+        op, g.hdr, rows[k], nullptr, nullptr, lv.len[k], lv.tile[k], n_nodes, rows[k + 1]);
+    GK_LAUNCH_CHECK();
+  }
+  softmax_finish_kernel<T, H, kBackward><<<grid0, kSoftmaxWarps * 32, 0, st>>>(g.erow, g.eid, in0, in1, out, stats,
+                                                                              n_nodes, g.E, hs, h0);
+  GK_LAUNCH_CHECK();
+  return GRAPHOP_OK;
+}
+
+template <typename T, bool kBackward>
+inline int run_softmax(Arena& ar, const GraphView& g, const T* in0, const T* in1, T* out, long long n_nodes, int H,
+                       cudaStream_t st) {
+  const size_t hb = (size_t)H * sizeof(T);
+  const bool vec_ok = ((uintptr_t)in0 % (hb < 16 ? hb : 16)) == 0 && ((uintptr_t)out % (hb < 16 ? hb : 16)) == 0 &&
+                      (!kBackward || ((uintptr_t)in1 % (hb < 16 ? hb : 16)) == 0);
+  if (vec_ok && H == 1) return run_softmax_heads<T, 1, kBackward>(ar, g, in0, in1, out, n_nodes, 1, 0, st);
+  if (vec_ok && H == 2) return run_softmax_heads<T, 2, kBackward>(ar, g, in0, in1, out, n_nodes, 2, 0, st);
+  if (vec_ok && H == 4) return run_softmax_heads<T, 4, kBackward>(ar, g, in0, in1, out, n_nodes, 4, 0, st);
+  if (vec_ok && H == 8) return run_softmax_heads<T, 8, kBackward>(ar, g, in0, in1, out, n_nodes, 8, 0, st);
+  // any other head count: one head at a time through the H = 1 kernels, scratch reused
+  const size_t mark = ar.used;
+  for (int h = 0; h < H; ++h) {
+    ar.used = mark;
+    GK_TRY((run_softmax_heads<T, 1, kBackward>(ar, g, in0, in1, out, n_nodes, H, h, st)));
+    if (!ar.base) break;
+  }
+  return GRAPHOP_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// argument checks shared by the entry points
+// ---------------------------------------------------------------------------------------
+inline int check_sizes(long long C, long long E, long long n0, long long n1, int H, int D) {
+  if (C < 0 || E < 0 || n0 < 0 || n1 < 0 || H < 1 || D < 1) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (E >= (1LL << 31) || n0 >= (1LL << 31) || n1 >= (1LL << 31)) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if ((long long)H * D >= (1LL << 24)) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  return GRAPHOP_OK;
+}
+inline int check_ws(const void* ws) {
+  if (!ws || ((uintptr_t)ws & (kAlign - 1))) return GRAPHOP_ERR_WORKSPACE;
+  return GRAPHOP_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// the ten operations
+// ---------------------------------------------------------------------------------------
+template <typename T, typename I>
+inline int maskedmm_forward(const I* row, const I* indptr, const I* eid, const I* indices, const T* A_, const T* B_,
+                            T* y, long long C, long long E, long long n_dst, long long n_src, int H, int D, void* ws,
+                            size_t wsb, cudaStream_t st) {
+  GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
+  if (E == 0) return GRAPHOP_OK;
+  if (!row || !indptr || !indices || !A_ || !B_ || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, indices, C, E, st, &g));
+  GK_TRY(zero_uncovered(g, y, (size_t)E * H * sizeof(T), st));
+  return run_edge_dot<T, false>(g, A_, B_, y, H, D, st);
+}
+
+template <typename T, typename I>
+inline int maskedmm_backward(const I* row, const I* indptr_r, const I* eid_r, const I* indices_r, long long Cr,
+                             const I* col, const I* indptr_c, const I* eid_c, const I* indices_c, long long Cc,
+                             const T* A_, const T* B_, const T* dy, T* dA, T* dB, long long E, long long n_dst,
+                             long long n_src, int H, int D, void* ws, size_t wsb, cudaStream_t st) {
+  GK_TRY(check_sizes(Cr, E, n_dst, n_src, H, D));
+  if (Cc < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  const size_t HD = (size_t)H * D;
+  if (E == 0) {
+    if (n_dst) GK_CUDA(cudaMemsetAsync(dA, 0, (size_t)n_dst * HD * sizeof(T), st));
+    if (n_src) GK_CUDA(cudaMemsetAsync(dB, 0, (size_t)n_src * HD * sizeof(T), st));
+    return GRAPHOP_OK;
+  }
+  if (!row || !indptr_r || !indices_r || !col || !indptr_c || !indices_c || !A_ || !B_ || !dy || !dA || !dB)
+    return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  {
+    GraphView g;
+    GK_TRY(prepare_graph<I>(ar, row, indptr_r, eid_r, indices_r, Cr, E, st, &g));
+    GK_TRY((run_aggregate<T, false>(ar, g, dy, B_, dA, n_dst, H, D, st)));
+  }
+  ar.used = 0;  // the second pass runs after the first on the same stream: reuse the scratch
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, col, indptr_c, eid_c, indices_c, Cc, E, st, &g));
+  return run_aggregate<T, false>(ar, g, dy, A_, dB, n_src, H, D, st);
+}
+
+template <typename T, typename I>
+inline int node_mul_edge_forward(const I* row, const I* indptr, const I* eid, const T* A_, const T* B_, T* y,
+                                 long long C, long long E, long long n_dst, int H, int D, void* ws, size_t wsb,
+                                 cudaStream_t st) {
+  GK_TRY(check_sizes(C, E, n_dst, 0, H, D));
+  if (E == 0) return GRAPHOP_OK;
+  if (!row || !indptr || !A_ || !B_ || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, (const I*)nullptr, C, E, st, &g));
+  GK_TRY(zero_uncovered(g, y, (size_t)E * H * sizeof(T), st));
+  return run_edge_dot<T, true>(g, A_, B_, y, H, D, st);
+}
+
+template <typename T, typename I>
+inline int node_mul_edge_backward(const I* row, const I* indptr, const I* eid, const T* A_, const T* B_, const T* dy,
+                                  T* dA, T* dB, long long C, long long E, long long n_dst, int H, int D, void* ws,
+                                  size_t wsb, cudaStream_t st) {
+  GK_TRY(check_sizes(C, E, n_dst, 0, H, D));
+  if (E == 0) {
+    if (n_dst) GK_CUDA(cudaMemsetAsync(dA, 0, (size_t)n_dst * H * D * sizeof(T), st));
+    return GRAPHOP_OK;
+  }
+  if (!row || !indptr || !A_ || !B_ || !dy || !dA || !dB) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, (const I*)nullptr, C, E, st, &g));
+  GK_TRY((run_aggregate<T, true>(ar, g, dy, B_, dA, n_dst, H, D, st)));
+  if (!ar.base) return GRAPHOP_OK;
+  GK_TRY(zero_uncovered(g, dB, (size_t)E * D * sizeof(T), st));
+  return run_edge_mix<T>(g, dy, A_, dB, H, D, st);
+}
+
+template <typename T, typename I, bool kBackward>
+inline int sparse_softmax(const I* row, const I* indptr, const I* eid, const T* in0, const T* in1, T* out,
+                          long long C, long long E, long long n_nodes, int H, void* ws, size_t wsb, cudaStream_t st) {
+  GK_TRY(check_sizes(C, E, n_nodes, 0, H, 1));
+  if (E == 0) return GRAPHOP_OK;
+  if (!row || !indptr || !in0 || !out || (kBackward && !in1)) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, (const I*)nullptr, C, E, st, &g));
+  GK_TRY(zero_uncovered(g, out, (size_t)E * H * sizeof(T), st));
+  return run_softmax<T, kBackward>(ar, g, in0, in1, out, n_nodes, H, st);
+}
+
+template <typename T, typename I>
+inline int spmm_forward(const I* row, const I* indptr, const I* eid, const I* indices, const T* edata, const T* x,
+                        T* y, long long C, long long E, long long n_dst, long long n_src, int H, int D, void* ws,
+                        size_t wsb, cudaStream_t st) {
+  GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
+  if (n_dst == 0) return GRAPHOP_OK;
+  if (E == 0) {
+    GK_CUDA(cudaMemsetAsync(y, 0, (size_t)n_dst * H * D * sizeof(T), st));
+    return GRAPHOP_OK;
+  }
+  if (!row || !indptr || !indices || !edata || !x || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, indices, C, E, st, &g));
+  return run_aggregate<T, false>(ar, g, edata, x, y, n_dst, H, D, st);
+}
+
+template <typename T, typename I>
+inline int spmm_backward(const I* row, const I* indptr, const I* eid, const I* indices, long long C, const I* col,
+                         const I* indptr_t, const I* eid_t, const I* indices_t, long long Ct, const T* edata,
+                         const T* dy, const T* x, T* dedata, T* dx, long long E, long long n_dst, long long n_src,
+                         int H, int D, void* ws, size_t wsb, cudaStream_t st) {
+  GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
+  if (Ct < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (E == 0) {
+    if (n_src) GK_CUDA(cudaMemsetAsync(dx, 0, (size_t)n_src * H * D * sizeof(T), st));
+    return GRAPHOP_OK;
+  }
+  if (!row || !indptr || !indices || !col || !indptr_t || !indices_t || !edata || !dy || !x || !dedata || !dx)
+    return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  {
+    GraphView g;
+    GK_TRY(prepare_graph<I>(ar, row, indptr, eid, indices, C, E, st, &g));
+    if (ar.base) {
+      GK_TRY(zero_uncovered(g, dedata, (size_t)E * H * sizeof(T), st));
+      GK_TRY((run_edge_dot<T, false>(g, dy, x, dedata, H, D, st)));
+    }
+  }
+  ar.used = 0;
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, col, indptr_t, eid_t, indices_t, Ct, E, st, &g));
+  return run_aggregate<T, false>(ar, g, edata, dy, dx, n_src, H, D, st);
+}
+
+template <typename T>
+inline bool attention_shape_ok(int H, int D, bool al, VecShape* s) {
+  *s = pick_shape<T>(H * D, D, al);
+  return s->V == VecMax<T>::value && s->R != 0 && is_pow2(D / s->V);
+}
+
+template <typename T, typename I>
+inline int attention_forward(const I* row, const I* indptr, const I* indices, long long C, const T* q, const T* k,
+                             const T* v, double scale, T* o, void* lse, long long E, long long n_dst, long long n_src,
+                             int H, int D, void* ws, size_t wsb, cudaStream_t st) {
+  using A = typename AccOf<T>::type;
+  GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
+  VecShape s;
+  if (!attention_shape_ok<T>(H, D, aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o), &s))
+    return GRAPHOP_ERR_UNSUPPORTED;
+  if (n_dst == 0) return GRAPHOP_OK;
+  if (!q || !k || !v || !o || !lse) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  GraphView g;
+  const int HD = H * D;
+  if (E == 0) {
+    // no edge anywhere: o = 0 and lse = -inf for every node, written by the gap filler of an empty walk
+    return GRAPHOP_ERR_UNSUPPORTED;
+  }
+  if (!row || !indptr || !indices) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(prepare_graph<I>(ar, row, indptr, (const I*)nullptr, indices, C, E, st, &g));
+  const int tile0 = pick_tile(E);
+  return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
+    constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+    const long long cstride = HD + 2 * s.S;
+    return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, [&](void* cout, void* cin) {
+      AttnFwdOp<T, V, R> op;
+      op.q = q; op.k = k; op.v = v; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout; op.carry_in = (const A*)cin;
+      op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V; op.cstride = cstride;
+      return op;
+    });
+  });
+}
+
+template <typename T, typename I>
+inline int attention_backward(const I* row, const I* indptr, const I* indices, long long C, const I* col,
+                              const I* indptr_t, const I* indices_t, long long Ct, const T* q, const T* k, const T* v,
+                              const T* o, const void* lse, const T* dout, double scale, T* dq, T* dk, T* dv,
+                              long long E, long long n_dst, long long n_src, int H, int D, void* ws, size_t wsb,
+                              cudaStream_t st) {
+  using A = typename AccOf<T>::type;
+  GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
+  if (Ct < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  VecShape s;
+  const bool al = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(dout) && aligned16(dq) &&
+                  aligned16(dk) && aligned16(dv);
+  if (!attention_shape_ok<T>(H, D, al, &s)) return GRAPHOP_ERR_UNSUPPORTED;
+  if (E == 0) return GRAPHOP_ERR_UNSUPPORTED;
+  if (!row || !indptr || !indices || !col || !indptr_t || !indices_t || !q || !k || !v || !o || !lse || !dout || !dq ||
+      !dk || !dv)
+    return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  const int HD = H * D;
+  const int tile0 = pick_tile(E);
+  A* delta = (A*)ar.take((size_t)n_dst * H * sizeof(A));  // survives both passes
+  const size_t mark = ar.used;
+  {
+    GraphView g;
+    GK_TRY(prepare_graph<I>(ar, row, indptr, (const I*)nullptr, indices, C, E, st, &g));
+    GK_TRY((dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
+      constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+      return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, [&](void* cout, void* cin) {
+        AttnBwdDstOp<T, V, R> op;
+        op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dq = dq;
+        op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+        op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+        return op;
+      });
+    })));
+  }
+  ar.used = mark;
+  GraphView g;
+  GK_TRY(prepare_graph<I>(ar, col, indptr_t, (const I*)nullptr, indices_t, Ct, E, st, &g));
+  return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
+    constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+    return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, [&](void* cout, void* cin) {
+      AttnBwdSrcOp<T, V, R> op;
+      op.q = q; op.k = k; op.v = v; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dk = dk; op.dv = dv;
+      op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+      op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+      return op;
+    });
+  });
+}
+
+}  // namespace gk

@@ -1,0 +1,144 @@
+// C ABI entry points that do not depend on the element type: version, error text, the
+// workspace size query and the graph-contract checker.
+#include "gk_host.cuh"
+
+namespace gk {
+namespace {
+
+// Scratch of one row-producing pass: per level 2 slots per tile, each `stride_bytes`, plus the
+// next level's row stream.
+size_t levels_bytes(long long len0, int tile0, size_t stride_bytes) {
+  const Levels lv = make_levels(len0, tile0);
+  size_t total = 0;
+  for (int k = 0; k + 1 < lv.n; ++k) {
+    total += align_up((size_t)(2 * lv.ntiles[k]) * stride_bytes);
+    total += align_up((size_t)(2 * lv.ntiles[k]) * 4);
+  }
+  return total;
+}
+
+size_t graph_bytes(long long E, int index_bytes) {
+  size_t b = align_up(sizeof(PlanHeader)) + align_up((size_t)E * 4);
+  if (index_bytes == 8) b += 2 * align_up((size_t)E * 4);
+  return b;
+}
+
+template <typename I>
+__global__ void check_graph_kernel(const I* __restrict__ row, const I* __restrict__ indptr, const I* __restrict__ eid,
+                                   const I* __restrict__ indices, long long C, long long E, long long n_nodes,
+                                   long long n_other, int* __restrict__ flags) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  int bad = 0;
+  for (long long c = i0; c < C; c += stride) {
+    const long long s = (long long)indptr[c], e = (long long)indptr[c + 1];
+    if (e < s) bad |= 1;
+    if (s < 0 || e > E) bad |= 16;
+    const long long r = (long long)row[c];
+    if (r < 0 || r >= n_nodes) bad |= 2;
+    if (c > 0 && (long long)row[c - 1] > r) bad |= 2;
+  }
+  if (C > 0) {
+    const long long lo = (long long)indptr[0], hi = (long long)indptr[C];
+    for (long long j = i0; j < E; j += stride) {
+      if (j < lo || j >= hi) continue;
+      if (indices) { const long long v = (long long)indices[j]; if (v < 0 || v >= n_other) bad |= 4; }
+      if (eid) { const long long v = (long long)eid[j]; if (v < 0 || v >= E) bad |= 8; }
+    }
+  }
+  if (bad) atomicOr(flags, bad);
+}
+
+template <typename I>
+int check_graph(const I* row, const I* indptr, const I* eid, const I* indices, long long C, long long E,
+                long long n_nodes, long long n_other, int* violations, cudaStream_t st) {
+  if (violations) *violations = 0;
+  if (C < 0 || E < 0 || E >= (1LL << 31) || !indptr || (C > 0 && !row)) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  int* flags = nullptr;
+  GK_CUDA(cudaMallocAsync((void**)&flags, sizeof(int), st));
+  GK_CUDA(cudaMemsetAsync(flags, 0, sizeof(int), st));
+  const long long work = C > E ? C : E;
+  const unsigned grid = (unsigned)((work + 255) / 256 < 4096 ? (work + 255) / 256 : 4096);
+  check_graph_kernel<I><<<grid ? grid : 1, 256, 0, st>>>(row, indptr, eid, indices, C, E, n_nodes, n_other, flags);
+  GK_LAUNCH_CHECK();
+  int host = 0;
+  GK_CUDA(cudaMemcpyAsync(&host, flags, sizeof(int), cudaMemcpyDeviceToHost, st));
+  GK_CUDA(cudaStreamSynchronize(st));
+  GK_CUDA(cudaFreeAsync(flags, st));
+  if (violations) *violations = host;
+  return host ? GRAPHOP_ERR_INVALID_ARGUMENT : GRAPHOP_OK;
+}
+
+}  // namespace
+}  // namespace gk
+
+extern "C" int graphop_version(void) { return 100; }
+
+extern "C" const char* graphop_error_string(int code) {
+  switch (code) {
+    case GRAPHOP_OK: return "ok";
+    case GRAPHOP_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case GRAPHOP_ERR_WORKSPACE: return "workspace too small or misaligned";
+    case GRAPHOP_ERR_UNSUPPORTED: return "shape not supported by this entry point";
+    case GRAPHOP_ERR_CUDA: return "CUDA call failed";
+    default: return "unknown error code";
+  }
+}
+
+extern "C" int graphop_last_cuda_error(void) { return gk::g_last_cuda_error; }
+
+extern "C" size_t graphop_workspace_bytes(int op, int64_t n_edges, int64_t n_nodes, int H, int D, int elem_bytes,
+                                          int index_bytes) {
+  using namespace gk;
+  if (n_edges < 0 || n_nodes < 0 || H < 1 || D < 1) return 0;
+  const long long E = n_edges;
+  const size_t acc = elem_bytes == 8 ? 8 : 4;
+  const size_t HD = (size_t)H * D;
+  const int tile0 = pick_tile(E);
+  const size_t graph = graph_bytes(E, index_bytes);
+  size_t need = graph;
+  switch (op) {
+    case GRAPHOP_OP_MASKEDMM_FWD:
+    case GRAPHOP_OP_NODE_MUL_EDGE_FWD:
+      break;
+    case GRAPHOP_OP_MASKEDMM_BWD:
+    case GRAPHOP_OP_NODE_MUL_EDGE_BWD:
+    case GRAPHOP_OP_SPMM_FWD:
+    case GRAPHOP_OP_SPMM_BWD:
+      need += levels_bytes(E, tile0, HD * acc);
+      break;
+    case GRAPHOP_OP_SOFTMAX_FWD:
+    case GRAPHOP_OP_SOFTMAX_BWD: {
+      // level 0 tiles are 64 or 128 positions; size for 64, and for the widest specialised head count
+      const int hh = H <= 8 ? H : 1;
+      const size_t w = (op == GRAPHOP_OP_SOFTMAX_FWD ? 2 : 1) * (size_t)hh * acc;
+      const long long nt0 = (E + 63) / 64;
+      need += align_up((size_t)(2 * nt0) * w) + align_up((size_t)(2 * nt0) * 4);
+      need += align_up((size_t)n_nodes * w);
+      need += levels_bytes(2 * nt0, kCarryTile, w);
+      break;
+    }
+    case GRAPHOP_OP_ATTENTION_FWD:
+      need += levels_bytes(E, tile0, 3 * HD * acc);
+      break;
+    case GRAPHOP_OP_ATTENTION_BWD:
+      need += align_up((size_t)n_nodes * H * acc) + levels_bytes(E, tile0, 2 * HD * acc);
+      break;
+    default:
+      return 0;
+  }
+  return need + kAlign;
+}
+
+extern "C" int graphop_check_graph_i32(const int32_t* row, const int32_t* indptr, const int32_t* eid,
+                                       const int32_t* indices, int64_t n_chunks, int64_t n_edges, int64_t n_nodes,
+                                       int64_t n_other, int* violations, graphop_stream_t stream) {
+  return gk::check_graph<int32_t>(row, indptr, eid, indices, n_chunks, n_edges, n_nodes, n_other, violations,
+                                  (cudaStream_t)stream);
+}
+extern "C" int graphop_check_graph_i64(const int64_t* row, const int64_t* indptr, const int64_t* eid,
+                                       const int64_t* indices, int64_t n_chunks, int64_t n_edges, int64_t n_nodes,
+                                       int64_t n_other, int* violations, graphop_stream_t stream) {
+  return gk::check_graph<int64_t>(row, indptr, eid, indices, n_chunks, n_edges, n_nodes, n_other, violations,
+                                  (cudaStream_t)stream);
+}

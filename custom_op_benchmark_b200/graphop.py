@@ -1,0 +1,299 @@
+"""The `graphop` module surface: the eight functions the reference extension exports to
+Python (PYBIND11_MODULE at graphop/graphop.cpp:216-225), same names, same positional
+arguments, same return shapes and order, plus the fused attention pair.
+
+Each function checks its tensors the way the reference wrappers do (CHECK_INPUT,
+graphop.cpp:4-6: every tensor must be a CUDA tensor and contiguous, RuntimeError otherwise),
+allocates the outputs and the workspace with torch, and calls the C ABI of
+libgraphop_b200.so on the current CUDA stream under a device guard (the reference calls
+cudaSetDevice and never restores it, graphop_kernel.cu:242).  There is no CPU path.
+
+Differences from the reference, all supersets: index tensors may be int32 as well as int64
+(all of one call's index tensors must share a dtype); bfloat16 is accepted next to float32
+and float64; ``dy`` is made contiguous instead of being read unchecked
+(graphop.cpp:120-130, 148-153); the source and destination node counts may differ.
+"""
+import torch as th
+
+from . import _capi
+
+__all__ = [
+    "maskedmm_csr_forward", "maskedmm_csr_backward", "node_mul_edge_forward", "node_mul_edge_backward",
+    "sparse_softmax_forward", "sparse_softmax_backward", "vector_spmm_forward", "vector_spmm_backward",
+    "attention_forward", "attention_backward", "attention_supported", "check_graph",
+]
+
+_ELEM = {th.float32: ("f32", 4), th.float64: ("f64", 8), th.bfloat16: ("bf16", 2)}
+_INDEX = {th.int32: ("i32", 4), th.int64: ("i64", 8)}
+
+
+def _check_input(t, name):
+    # graphop.cpp:4-6
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+
+
+def _check_all(**tensors):
+    for name, t in tensors.items():
+        _check_input(t, name)
+
+
+def _elem(*ts):
+    dt = ts[0].dtype
+    if dt not in _ELEM:
+        # the text AT_DISPATCH_FLOATING_TYPES raises with (graphop_kernel.cu:254)
+        names = {th.float16: "Half", th.int64: "Long", th.int32: "Int", th.uint8: "Byte", th.bool: "Bool"}
+        raise RuntimeError('"graphop" not implemented for \'%s\'' % names.get(dt, str(dt).replace("torch.", "")))
+    for t in ts:
+        if t.dtype != dt:
+            raise RuntimeError("expected all floating tensors to share dtype %s, got %s" % (dt, t.dtype))
+    return _ELEM[dt]
+
+
+def _index(*ts):
+    dt = ts[0].dtype
+    if dt not in _INDEX:
+        raise RuntimeError("index tensors must be int32 or int64, got %s" % dt)
+    for t in ts:
+        if t.dtype != dt:
+            raise RuntimeError("expected all index tensors to share dtype %s, got %s" % (dt, t.dtype))
+    return _INDEX[dt]
+
+
+def _chunks(row, indptr):
+    c = row.size(0)
+    if indptr.size(0) != c + 1:
+        raise RuntimeError("indptr must hold row.size(0) + 1 entries")
+    return c
+
+
+def _heads(t, node):
+    """(h, d) of a node tensor given as (n, d) / (n, h, d), or h of an edge tensor (e,) / (e, h)."""
+    if node:
+        if t.dim() not in (2, 3):
+            raise RuntimeError("node tensors must be (n, d) or (n, h, d)")
+        return (1 if t.dim() == 2 else t.size(1)), t.size(-1)
+    if t.dim() not in (1, 2):
+        raise RuntimeError("edge tensors must be (e,) or (e, h)")
+    return 1 if t.dim() == 1 else t.size(1)
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _call(name, elem, index, op_id, n_edges, n_nodes, h, d, device, args):
+    """Allocates the workspace, appends (workspace, bytes, stream) and checks the status."""
+    lib = _capi.lib()
+    need = lib.graphop_workspace_bytes(op_id, n_edges, n_nodes, h, d, elem[1], index[1])
+    ws = th.empty(need + 256, dtype=th.uint8, device=device)
+    base = ws.data_ptr()
+    aligned = (base + 255) // 256 * 256
+    fn = getattr(lib, "graphop_%s_%s_%s" % (name, elem[0], index[0]))
+    rc = fn(*args, aligned, need, th.cuda.current_stream(device).cuda_stream)
+    if rc != _capi.OK:
+        raise RuntimeError("graphop_%s: %s" % (name, _capi.error_message(rc)))
+
+
+def maskedmm_csr_forward(row, indptr, eid, indices, A, B):
+    """y[eid[k], h] = A[row(k), h, :] . B[indices[k], h, :]  ->  (e,) if A is 2-D else (e, h)."""
+    _check_all(row=row, indptr=indptr, eid=eid, indices=indices, A=A, B=B)
+    elem, index = _elem(A, B), _index(row, indptr, eid, indices)
+    h, d = _heads(A, True)
+    e, c = eid.size(0), _chunks(row, indptr)
+    y = th.empty((e,) if h == 1 else (e, h), dtype=A.dtype, device=A.device)
+    with th.cuda.device(A.device):
+        _call("maskedmm_csr_forward", elem, index, _capi.OP_MASKEDMM_FWD, e, max(A.size(0), B.size(0)), h, d,
+              A.device, [_p(row), _p(indptr), _p(eid), _p(indices), _p(A), _p(B), _p(y), c, e, A.size(0), B.size(0),
+                         h, d])
+    return y
+
+
+def maskedmm_csr_backward(row, indptr_r, eid_r, indices_r, col, indptr_c, eid_c, indices_c, A, B, dy):
+    """[dA, dB] of maskedmm_csr_forward; the row CSR serves dA, the column CSR dB."""
+    _check_all(row=row, indptr_r=indptr_r, eid_r=eid_r, indices_r=indices_r, col=col, indptr_c=indptr_c,
+               eid_c=eid_c, indices_c=indices_c, A=A, B=B)
+    dy = dy.contiguous()
+    _check_input(dy, "dy")
+    elem = _elem(A, B, dy)
+    index = _index(row, indptr_r, eid_r, indices_r, col, indptr_c, eid_c, indices_c)
+    h, d = _heads(A, True)
+    e, cr, cc = eid_r.size(0), _chunks(row, indptr_r), _chunks(col, indptr_c)
+    dA, dB = th.empty_like(A), th.empty_like(B)
+    with th.cuda.device(A.device):
+        _call("maskedmm_csr_backward", elem, index, _capi.OP_MASKEDMM_BWD, e, max(A.size(0), B.size(0)), h, d,
+              A.device, [_p(row), _p(indptr_r), _p(eid_r), _p(indices_r), cr, _p(col), _p(indptr_c), _p(eid_c),
+                         _p(indices_c), cc, _p(A), _p(B), _p(dy), _p(dA), _p(dB), e, A.size(0), B.size(0), h, d])
+    return [dA, dB]
+
+
+def node_mul_edge_forward(row, indptr, eid, A, B):
+    """y[eid[k], h] = A[row(k), h, :] . B[eid[k], :], B an (e, d) edge tensor shared by the heads."""
+    _check_all(row=row, indptr=indptr, eid=eid, A=A, B=B)
+    elem, index = _elem(A, B), _index(row, indptr, eid)
+    h, d = _heads(A, True)
+    e, c = eid.size(0), _chunks(row, indptr)
+    y = th.empty((e,) if h == 1 else (e, h), dtype=A.dtype, device=A.device)
+    with th.cuda.device(A.device):
+        _call("node_mul_edge_forward", elem, index, _capi.OP_NODE_MUL_EDGE_FWD, e, A.size(0), h, d, A.device,
+              [_p(row), _p(indptr), _p(eid), _p(A), _p(B), _p(y), c, e, A.size(0), h, d])
+    return y
+
+
+def node_mul_edge_backward(row, indptr, eid, A, B, dy):
+    """[dA, dB] of node_mul_edge_forward."""
+    _check_all(row=row, indptr=indptr, eid=eid, A=A, B=B)
+    dy = dy.contiguous()
+    _check_input(dy, "dy")
+    elem, index = _elem(A, B, dy), _index(row, indptr, eid)
+    h, d = _heads(A, True)
+    e, c = eid.size(0), _chunks(row, indptr)
+    dA, dB = th.empty_like(A), th.empty_like(B)
+    with th.cuda.device(A.device):
+        _call("node_mul_edge_backward", elem, index, _capi.OP_NODE_MUL_EDGE_BWD, e, A.size(0), h, d, A.device,
+              [_p(row), _p(indptr), _p(eid), _p(A), _p(B), _p(dy), _p(dA), _p(dB), c, e, A.size(0), h, d])
+    return [dA, dB]
+
+
+def _softmax_nodes(e):
+    # The reference sizes its per-node scratch by the edge count and indexes it by node id
+    # (graphop_kernel.cu:420-427): node ids must stay below the number of edges.
+    return e
+
+
+def sparse_softmax_forward(row, indptr, eid, x):
+    """Softmax of x over the edges of each node, per head; x is (e,) or (e, h)."""
+    _check_all(row=row, indptr=indptr, eid=eid, x=x)
+    elem, index = _elem(x), _index(row, indptr, eid)
+    h = _heads(x, False)
+    e, c = eid.size(0), _chunks(row, indptr)
+    y = th.empty_like(x)
+    with th.cuda.device(x.device):
+        _call("sparse_softmax_forward", elem, index, _capi.OP_SOFTMAX_FWD, e, _softmax_nodes(e), h, 1, x.device,
+              [_p(row), _p(indptr), _p(eid), _p(x), _p(y), c, e, _softmax_nodes(e), h])
+    return y
+
+
+def sparse_softmax_backward(row, indptr, eid, y, dy):
+    """dx = y * (dy - sum over the node of dy * y)."""
+    _check_all(row=row, indptr=indptr, eid=eid, y=y, dy=dy)
+    elem, index = _elem(y, dy), _index(row, indptr, eid)
+    h = _heads(dy, False)
+    e, c = eid.size(0), _chunks(row, indptr)
+    dx = th.empty_like(dy)
+    with th.cuda.device(y.device):
+        _call("sparse_softmax_backward", elem, index, _capi.OP_SOFTMAX_BWD, e, _softmax_nodes(e), h, 1, y.device,
+              [_p(row), _p(indptr), _p(eid), _p(y), _p(dy), _p(dx), c, e, _softmax_nodes(e), h])
+    return dx
+
+
+def vector_spmm_forward(row, indptr, eid, indices, edata, x, num_dst=None):
+    """y[n, h, :] = sum over n's edges of edata[eid[k], h] * x[indices[k], h, :].
+
+    ``y`` has x's shape as in the reference (graphop_kernel.cu:527); ``num_dst`` (an addition)
+    gives it that many rows instead, for a shard that owns fewer destinations than sources."""
+    _check_all(row=row, indptr=indptr, eid=eid, indices=indices, edata=edata, x=x)
+    elem, index = _elem(edata, x), _index(row, indptr, eid, indices)
+    h, d = _heads(x, True)
+    if _heads(edata, False) != h:
+        raise RuntimeError("edata and x disagree on the number of heads")
+    e, c = eid.size(0), _chunks(row, indptr)
+    n_dst = x.size(0) if num_dst is None else int(num_dst)
+    y = th.empty((n_dst,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    with th.cuda.device(x.device):
+        _call("vector_spmm_forward", elem, index, _capi.OP_SPMM_FWD, e, max(n_dst, x.size(0)), h, d, x.device,
+              [_p(row), _p(indptr), _p(eid), _p(indices), _p(edata), _p(x), _p(y), c, e, n_dst, x.size(0), h, d])
+    return y
+
+
+def vector_spmm_backward(row, indptr, eid, indices, col, indptr_t, eid_t, indices_t, edata, dy, x):
+    """[dedata, dx] of vector_spmm_forward (this order: graphop_kernel.cu:599)."""
+    _check_all(row=row, indptr=indptr, eid=eid, indices=indices, col=col, indptr_t=indptr_t, eid_t=eid_t,
+               indices_t=indices_t, edata=edata, dy=dy, x=x)
+    elem = _elem(edata, dy, x)
+    index = _index(row, indptr, eid, indices, col, indptr_t, eid_t, indices_t)
+    h, d = _heads(x, True)
+    e, c, ct = eid.size(0), _chunks(row, indptr), _chunks(col, indptr_t)
+    dedata, dx = th.empty_like(edata), th.empty_like(x)
+    with th.cuda.device(x.device):
+        _call("vector_spmm_backward", elem, index, _capi.OP_SPMM_BWD, e, max(dy.size(0), x.size(0)), h, d, x.device,
+              [_p(row), _p(indptr), _p(eid), _p(indices), c, _p(col), _p(indptr_t), _p(eid_t), _p(indices_t), ct,
+               _p(edata), _p(dy), _p(x), _p(dedata), _p(dx), e, dy.size(0), x.size(0), h, d])
+    return [dedata, dx]
+
+
+# ------------------------------------------------------------------------------------------
+# fused attention (an addition: one call for maskedmm -> scale -> sparse_softmax -> vector_spmm)
+# ------------------------------------------------------------------------------------------
+def attention_supported(q):
+    """Shapes the fused kernels take: D * itemsize a power-of-two multiple of 16 bytes, a node
+    row of at most 4 KiB, 16-byte aligned storage."""
+    if q.dtype not in _ELEM or q.dim() not in (2, 3):
+        return False
+    h, d = _heads(q, True)
+    v = 16 // q.element_size()
+    if d % v or (d // v) & (d // v - 1):
+        return False
+    return h * d // v <= 256 and q.data_ptr() % 16 == 0
+
+
+def _lse_dtype(q):
+    return th.float64 if q.dtype == th.float64 else th.float32
+
+
+def attention_forward(row, indptr, indices, q, k, v, scale):
+    """(o, lse): o[n] = sum_k softmax_k(scale * q[n].k[indices[k]]) v[indices[k]] over n's edges,
+    lse[n, h] the log of the softmax denominator (kept for the backward)."""
+    _check_all(row=row, indptr=indptr, indices=indices, q=q, k=k, v=v)
+    elem, index = _elem(q, k, v), _index(row, indptr, indices)
+    h, d = _heads(q, True)
+    e, c = indices.size(0), _chunks(row, indptr)
+    o = th.empty_like(q)
+    lse = th.empty((q.size(0), h), dtype=_lse_dtype(q), device=q.device)
+    if e == 0:
+        return o.zero_(), lse.fill_(float("-inf"))
+    with th.cuda.device(q.device):
+        _call("attention_forward", elem, index, _capi.OP_ATTENTION_FWD, e, max(q.size(0), k.size(0)), h, d,
+              q.device, [_p(row), _p(indptr), _p(indices), c, _p(q), _p(k), _p(v), float(scale), _p(o), _p(lse), e,
+                         q.size(0), k.size(0), h, d])
+    return o, lse
+
+
+def attention_backward(row, indptr, indices, col, indptr_t, indices_t, q, k, v, o, lse, d_o, scale):
+    """[dq, dk, dv] of attention_forward; probabilities are recomputed from q, k and lse."""
+    d_o = d_o.contiguous()
+    _check_all(row=row, indptr=indptr, indices=indices, col=col, indptr_t=indptr_t, indices_t=indices_t, q=q, k=k,
+               v=v, o=o, lse=lse, d_o=d_o)
+    elem = _elem(q, k, v, o, d_o)
+    index = _index(row, indptr, indices, col, indptr_t, indices_t)
+    h, d = _heads(q, True)
+    e, c, ct = indices.size(0), _chunks(row, indptr), _chunks(col, indptr_t)
+    dq, dk, dv = th.empty_like(q), th.empty_like(k), th.empty_like(v)
+    if e == 0:
+        return [dq.zero_(), dk.zero_(), dv.zero_()]
+    with th.cuda.device(q.device):
+        _call("attention_backward", elem, index, _capi.OP_ATTENTION_BWD, e, max(q.size(0), k.size(0)), h, d,
+              q.device, [_p(row), _p(indptr), _p(indices), c, _p(col), _p(indptr_t), _p(indices_t), ct, _p(q),
+                         _p(k), _p(v), _p(o), _p(lse), _p(d_o), float(scale), _p(dq), _p(dk), _p(dv), e, q.size(0),
+                         k.size(0), h, d])
+    return [dq, dk, dv]
+
+
+def check_graph(row, indptr, eid, indices, n_nodes, n_other):
+    """Debug aid: verifies on the device the graph contract the kernels rely on (monotone
+    indptr and row, indices and edge ids in range) and returns the violation bit mask
+    (0 = fine).  Synchronises the stream."""
+    import ctypes
+    _check_all(row=row, indptr=indptr)
+    index = _index(row, indptr)
+    e = eid.size(0) if eid is not None else (indices.size(0) if indices is not None else 0)
+    flags = ctypes.c_int(0)
+    fn = getattr(_capi.lib(), "graphop_check_graph_%s" % index[0])
+    with th.cuda.device(row.device):
+        rc = fn(_p(row), _p(indptr), _p(eid), _p(indices), row.size(0), e, n_nodes, n_other, ctypes.byref(flags),
+                th.cuda.current_stream(row.device).cuda_stream)
+    if rc not in (_capi.OK, _capi.ERR_INVALID_ARGUMENT):
+        raise RuntimeError("graphop_check_graph: %s" % _capi.error_message(rc))
+    return flags.value

@@ -1,0 +1,108 @@
+"""Autograd wiring of the graphop ops: the four `torch.autograd.Function` classes of the
+reference (wrapper.py:8-55) with the same names, the same positional `apply` signatures and
+the same `None` gradients for every index argument, plus `GraphAttention`, the fused chain.
+"""
+import torch as th
+from torch.autograd import Function
+
+from . import graphop as _g
+from .part_csr import partition_csr  # noqa: F401  (the reference wrapper re-exports it, wrapper.py:4)
+
+__all__ = ["SparseSoftmax", "MaskedMMCSR", "NodeMulEdge", "VectorSPMM", "GraphAttention", "graph_attention",
+           "partition_csr", "chunk_size"]
+
+chunk_size = 32  # wrapper.py:6
+
+
+class SparseSoftmax(Function):
+    """wrapper.py:8-18"""
+
+    @staticmethod
+    def forward(ctx, row, indptr, eid, x):
+        y = _g.sparse_softmax_forward(row, indptr, eid, x)
+        ctx.save_for_backward(row, indptr, eid, y)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        row, indptr, eid, y = ctx.saved_tensors
+        return None, None, None, _g.sparse_softmax_backward(row, indptr, eid, y, dy.contiguous())
+
+
+class MaskedMMCSR(Function):
+    """wrapper.py:20-30"""
+
+    @staticmethod
+    def forward(ctx, row, indptr_r, eid_r, indices_r, col, indptr_c, eid_c, indices_c, A, B):
+        ctx.save_for_backward(row, indptr_r, eid_r, indices_r, col, indptr_c, eid_c, indices_c, A, B)
+        return _g.maskedmm_csr_forward(row, indptr_r, eid_r, indices_r, A, B)
+
+    @staticmethod
+    def backward(ctx, grad):
+        row, indptr_r, eid_r, indices_r, col, indptr_c, eid_c, indices_c, A, B = ctx.saved_tensors
+        dA, dB = _g.maskedmm_csr_backward(row, indptr_r, eid_r, indices_r, col, indptr_c, eid_c, indices_c, A, B,
+                                          grad)
+        return None, None, None, None, None, None, None, None, dA, dB
+
+
+class NodeMulEdge(Function):
+    """wrapper.py:32-42"""
+
+    @staticmethod
+    def forward(ctx, row, indptr, eid, A, B):
+        ctx.save_for_backward(row, indptr, eid, A, B)
+        return _g.node_mul_edge_forward(row, indptr, eid, A, B)
+
+    @staticmethod
+    def backward(ctx, grad):
+        row, indptr, eid, A, B = ctx.saved_tensors
+        dA, dB = _g.node_mul_edge_backward(row, indptr, eid, A, B, grad)
+        return None, None, None, dA, dB
+
+
+class VectorSPMM(Function):
+    """wrapper.py:44-55"""
+
+    @staticmethod
+    def forward(ctx, row, indptr, eid, indices, col, ptr_t, eid_t, indices_t, edata, x):
+        y = _g.vector_spmm_forward(row, indptr, eid, indices, edata, x)
+        ctx.save_for_backward(row, indptr, eid, indices, col, ptr_t, eid_t, indices_t, edata, x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        row, indptr, eid, indices, col, ptr_t, eid_t, indices_t, edata, x = ctx.saved_tensors
+        dedata, dx = _g.vector_spmm_backward(row, indptr, eid, indices, col, ptr_t, eid_t, indices_t, edata,
+                                             dy.contiguous(), x)
+        return None, None, None, None, None, None, None, None, dedata, dx
+
+
+class GraphAttention(Function):
+    """O = VectorSPMM(SparseSoftmax(scale * MaskedMMCSR(Q, K)), V) in one kernel per direction.
+
+    ``apply(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale)``; no edge ids are
+    needed because no edge tensor is materialised.  Only the (n, h) log-sum-exp is saved."""
+
+    @staticmethod
+    def forward(ctx, row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale):
+        o, lse = _g.attention_forward(row, indptr, indices, Q, K, V, scale)
+        ctx.save_for_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse = ctx.saved_tensors
+        dq, dk, dv = _g.attention_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse, d_o,
+                                           ctx.scale)
+        return None, None, None, None, None, None, dq, dk, dv, None
+
+
+def graph_attention(row, indptr, eid, indices, col, indptr_t, eid_t, indices_t, Q, K, V, scale):
+    """The attention chain with the argument list of the unfused ops: the fused kernels when the
+    shape allows, otherwise MaskedMMCSR -> scale -> SparseSoftmax -> VectorSPMM."""
+    if _g.attention_supported(Q):
+        return GraphAttention.apply(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale)
+    s = MaskedMMCSR.apply(row, indptr, eid, indices, col, indptr_t, eid_t, indices_t, Q, K) * scale
+    p = SparseSoftmax.apply(row, indptr, eid, s)
+    return VectorSPMM.apply(row, indptr, eid, indices, col, indptr_t, eid_t, indices_t, p, V)

@@ -1,0 +1,173 @@
+/*
+ * graphop_b200: C ABI of the sparse graph-attention operator set for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host binding links against.  It replaces the host launchers of the
+ * reference extension (graphop/graphop_kernel.cu:235-600, the eight *_cuda_forward /
+ * *_cuda_backward functions that graphop/graphop.cpp:8-214 declares and wraps for Python)
+ * with plain pointers and sizes: no torch types, no allocation, no exceptions.  Every entry
+ * point enqueues its kernels on `stream` and returns at once with a status code; nothing
+ * synchronises the device.
+ *
+ * Graph arguments follow the reference contract (graphop_kernel.cu:20, 41, ...): `row` holds
+ * one owner node per chunk (length n_chunks), `indptr` the n_chunks + 1 chunk boundaries as
+ * CSR positions, `eid` maps a position to an edge id (the row index of every edge tensor;
+ * NULL means the identity), `indices` gives the other endpoint of a position.  Chunks come
+ * from partition_csr (part_csr.py:13-27) or are the plain CSR rows (row = 0..N-1).  Required
+ * of the caller: indptr non-decreasing, chunks of one node consecutive, node ids
+ * non-decreasing along `row`, eid injective, n_edges < 2^31.  Under that contract every
+ * reduction is computed by exactly one owner in a fixed order: results are bit-reproducible
+ * (the reference accumulates with atomics, graphop/atomic.cuh:57-96).
+ *
+ * Tensor layouts are those of the reference: node tensors (n, H, D) row-major, edge tensors
+ * (n_edges, H) row-major; H = 1 covers the reference's 2-D / 1-D spellings.
+ *
+ * Naming: graphop_<op>_<elem>_<index>, elem in {f32, f64, bf16}, index in {i32, i64}.
+ * f32 / f64 with i64 indices is the reference's own type set (AT_DISPATCH_FLOATING_TYPES and
+ * .data<int64_t>(), graphop_kernel.cu:254-258); bf16 (fp32 accumulation) and i32 indices are
+ * additions.  bf16 values are passed as uint16_t bit patterns.
+ *
+ * Workspace: each entry point needs scratch memory in device global memory, passed as
+ * (workspace, workspace_bytes); graphop_workspace_bytes() gives a sufficient size.  The
+ * workspace holds no state between calls.
+ */
+#ifndef GRAPHOP_B200_H_
+#define GRAPHOP_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* graphop_stream_t; /* a cudaStream_t */
+
+enum {
+  GRAPHOP_OK = 0,
+  GRAPHOP_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, n_edges >= 2^31, ... */
+  GRAPHOP_ERR_WORKSPACE = 2,        /* workspace_bytes too small or workspace misaligned */
+  GRAPHOP_ERR_UNSUPPORTED = 3,      /* shape outside what this entry point implements */
+  GRAPHOP_ERR_CUDA = 4              /* a CUDA call failed; see graphop_last_cuda_error() */
+};
+
+/* Operation ids for graphop_workspace_bytes(). */
+enum {
+  GRAPHOP_OP_MASKEDMM_FWD = 0,
+  GRAPHOP_OP_MASKEDMM_BWD = 1,
+  GRAPHOP_OP_NODE_MUL_EDGE_FWD = 2,
+  GRAPHOP_OP_NODE_MUL_EDGE_BWD = 3,
+  GRAPHOP_OP_SOFTMAX_FWD = 4,
+  GRAPHOP_OP_SOFTMAX_BWD = 5,
+  GRAPHOP_OP_SPMM_FWD = 6,
+  GRAPHOP_OP_SPMM_BWD = 7,
+  GRAPHOP_OP_ATTENTION_FWD = 8,
+  GRAPHOP_OP_ATTENTION_BWD = 9
+};
+
+int graphop_version(void);
+const char* graphop_error_string(int code);
+/* cudaError_t of the most recent failed CUDA call made by this library on this thread. */
+int graphop_last_cuda_error(void);
+
+/* Sufficient workspace for one call of `op`.  n_nodes: the largest node count among the
+ * call's node tensors (for the softmax ops: an upper bound on node id + 1).  elem_bytes: 2, 4
+ * or 8; index_bytes: 4 or 8. */
+size_t graphop_workspace_bytes(int op, int64_t n_edges, int64_t n_nodes, int H, int D, int elem_bytes,
+                               int index_bytes);
+
+/* Checks the graph contract stated above on the device and copies the verdict back
+ * (synchronises `stream`).  Returns GRAPHOP_OK, or GRAPHOP_ERR_INVALID_ARGUMENT with
+ * *violations (may be NULL) set to a bit mask: 1 indptr decreases, 2 row decreases,
+ * 4 an index outside [0, n_other), 8 an edge id outside [0, n_edges), 16 a position range
+ * outside [0, n_edges).  `indices` and `eid` may be NULL to skip their checks. */
+int graphop_check_graph_i32(const int32_t* row, const int32_t* indptr, const int32_t* eid, const int32_t* indices,
+                            int64_t n_chunks, int64_t n_edges, int64_t n_nodes, int64_t n_other, int* violations,
+                            graphop_stream_t stream);
+int graphop_check_graph_i64(const int64_t* row, const int64_t* indptr, const int64_t* eid, const int64_t* indices,
+                            int64_t n_chunks, int64_t n_edges, int64_t n_nodes, int64_t n_other, int* violations,
+                            graphop_stream_t stream);
+
+#define GRAPHOP_DECLARE(SUF, T, I)                                                                                   \
+  /* y[eid[k], h] = sum_d A[row(k), h, d] * B[indices[k], h, d]; edge ids no chunk covers get 0.                  \
+   * Replaces maskedmm_csr_cuda_forward (graphop_kernel.cu:269-304; bound at graphop.cpp:16-30, 217). */            \
+  int graphop_maskedmm_csr_forward_##SUF(const I* row, const I* indptr, const I* eid, const I* indices, const T* A, \
+                                         const T* B, T* y, int64_t n_chunks, int64_t n_edges, int64_t n_dst,        \
+                                         int64_t n_src, int H, int D, void* workspace, size_t workspace_bytes,      \
+                                         graphop_stream_t stream);                                                  \
+  /* dA[n] = sum_{k in n} dy[eid_r[k]] * B[indices_r[k]] over the row CSR, dB the same over the column CSR with   \
+   * A in B's place.  Replaces maskedmm_csr_cuda_backward (graphop_kernel.cu:355-409; graphop.cpp:108-131, 218). */ \
+  int graphop_maskedmm_csr_backward_##SUF(const I* row, const I* indptr_r, const I* eid_r, const I* indices_r,      \
+                                          int64_t n_chunks_r, const I* col, const I* indptr_c, const I* eid_c,      \
+                                          const I* indices_c, int64_t n_chunks_c, const T* A, const T* B,           \
+                                          const T* dy, T* dA, T* dB, int64_t n_edges, int64_t n_dst, int64_t n_src, \
+                                          int H, int D, void* workspace, size_t workspace_bytes,                    \
+                                          graphop_stream_t stream);                                                 \
+  /* y[eid[k], h] = sum_d A[row(k), h, d] * B[eid[k], d], B an (n_edges, D) edge tensor shared by the heads.       \
+   * Replaces node_mul_edge_cuda_forward (graphop_kernel.cu:235-266; graphop.cpp:39-51, 219). */                    \
+  int graphop_node_mul_edge_forward_##SUF(const I* row, const I* indptr, const I* eid, const T* A, const T* B,      \
+                                          T* y, int64_t n_chunks, int64_t n_edges, int64_t n_dst, int H, int D,     \
+                                          void* workspace, size_t workspace_bytes, graphop_stream_t stream);        \
+  /* dA[n, h, :] = sum_{k in n} dy[eid[k], h] * B[eid[k], :];  dB[eid[k], :] = sum_h dy[eid[k], h] * A[row(k), h, :]. \
+   * Replaces node_mul_edge_cuda_backward (graphop_kernel.cu:306-351; graphop.cpp:141-154, 220). */                 \
+  int graphop_node_mul_edge_backward_##SUF(const I* row, const I* indptr, const I* eid, const T* A, const T* B,     \
+                                           const T* dy, T* dA, T* dB, int64_t n_chunks, int64_t n_edges,            \
+                                           int64_t n_dst, int H, int D, void* workspace, size_t workspace_bytes,    \
+                                           graphop_stream_t stream);                                                \
+  /* Per (node, head): y = exp(x - max) / sum exp(x - max) over the node's edges; uncovered edge ids get 0.        \
+   * n_nodes bounds node id + 1 (the reference sizes its scratch by n_edges, graphop_kernel.cu:420-427).            \
+   * Replaces sparse_softmax_cuda_forward (graphop_kernel.cu:411-463; graphop.cpp:59-69, 221). */                   \
+  int graphop_sparse_softmax_forward_##SUF(const I* row, const I* indptr, const I* eid, const T* x, T* y,           \
+                                           int64_t n_chunks, int64_t n_edges, int64_t n_nodes, int H,               \
+                                           void* workspace, size_t workspace_bytes, graphop_stream_t stream);       \
+  /* dx = y * (dy - sum_node dy * y).                                                                              \
+   * Replaces sparse_softmax_cuda_backward (graphop_kernel.cu:465-507; graphop.cpp:163-175, 222). */                \
+  int graphop_sparse_softmax_backward_##SUF(const I* row, const I* indptr, const I* eid, const T* y, const T* dy,   \
+                                            T* dx, int64_t n_chunks, int64_t n_edges, int64_t n_nodes, int H,       \
+                                            void* workspace, size_t workspace_bytes, graphop_stream_t stream);      \
+  /* y[n, h, :] = sum_{k in n} edata[eid[k], h] * x[indices[k], h, :]; nodes without edges get 0.  y has n_dst     \
+   * rows (the reference forces n_dst = n_src by y = zeros_like(x), graphop_kernel.cu:527).                         \
+   * Replaces vector_spmm_cuda_forward (graphop_kernel.cu:509-542; graphop.cpp:79-93, 223). */                      \
+  int graphop_vector_spmm_forward_##SUF(const I* row, const I* indptr, const I* eid, const I* indices,              \
+                                        const T* edata, const T* x, T* y, int64_t n_chunks, int64_t n_edges,        \
+                                        int64_t n_dst, int64_t n_src, int H, int D, void* workspace,                \
+                                        size_t workspace_bytes, graphop_stream_t stream);                           \
+  /* dedata[eid[k], h] = sum_d dy[row(k), h, d] * x[indices[k], h, d];                                             \
+   * dx[c, h, :] = sum_{k in c} edata[eid_t[k], h] * dy[indices_t[k], h, :] over the transposed CSR, all of its    \
+   * chunks (the reference's launch drops some, graphop_kernel.cu:566, 588).                                        \
+   * Replaces vector_spmm_cuda_backward (graphop_kernel.cu:544-600; graphop.cpp:190-214, 224). */                   \
+  int graphop_vector_spmm_backward_##SUF(const I* row, const I* indptr, const I* eid, const I* indices,             \
+                                         int64_t n_chunks, const I* col, const I* indptr_t, const I* eid_t,         \
+                                         const I* indices_t, int64_t n_chunks_t, const T* edata, const T* dy,       \
+                                         const T* x, T* dedata, T* dx, int64_t n_edges, int64_t n_dst,              \
+                                         int64_t n_src, int H, int D, void* workspace, size_t workspace_bytes,      \
+                                         graphop_stream_t stream);                                                  \
+  /* Fused chain maskedmm -> *scale -> sparse_softmax -> vector_spmm without the (n_edges, H) intermediates:       \
+   * o[n] = sum_k softmax_k(scale * q[n].k[indices[k]]) v[indices[k]], lse[n, h] = log sum_k exp(score) kept for   \
+   * the backward (float for f32 / bf16, double for f64); nodes without edges get o = 0, lse = -inf.  No reference \
+   * counterpart as one call; it composes graphop_kernel.cu:269-304, 411-463 and 509-542.                           \
+   * GRAPHOP_ERR_UNSUPPORTED unless D * sizeof(T) is a power-of-two multiple of 16 bytes and H * D * sizeof(T)      \
+   * <= 4096 bytes. */                                                                                              \
+  int graphop_attention_forward_##SUF(const I* row, const I* indptr, const I* indices, int64_t n_chunks, const T* q, \
+                                      const T* k, const T* v, double scale, T* o, void* lse, int64_t n_edges,       \
+                                      int64_t n_dst, int64_t n_src, int H, int D, void* workspace,                  \
+                                      size_t workspace_bytes, graphop_stream_t stream);                             \
+  /* Gradients of the fused chain: dq over the row CSR, dk and dv over the transposed CSR, probabilities            \
+   * recomputed from q, k and lse.  Composes graphop_kernel.cu:544-600, 465-507 and 355-409. */                     \
+  int graphop_attention_backward_##SUF(const I* row, const I* indptr, const I* indices, int64_t n_chunks,           \
+                                       const I* col, const I* indptr_t, const I* indices_t, int64_t n_chunks_t,     \
+                                       const T* q, const T* k, const T* v, const T* o, const void* lse,             \
+                                       const T* d_o, double scale, T* dq, T* dk, T* dv, int64_t n_edges,            \
+                                       int64_t n_dst, int64_t n_src, int H, int D, void* workspace,                 \
+                                       size_t workspace_bytes, graphop_stream_t stream);
+
+GRAPHOP_DECLARE(f32_i32, float, int32_t)
+GRAPHOP_DECLARE(f32_i64, float, int64_t)
+GRAPHOP_DECLARE(f64_i32, double, int32_t)
+GRAPHOP_DECLARE(f64_i64, double, int64_t)
+GRAPHOP_DECLARE(bf16_i32, uint16_t, int32_t)
+GRAPHOP_DECLARE(bf16_i64, uint16_t, int64_t)
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRAPHOP_B200_H_ */

@@ -1,0 +1,52 @@
+"""The C-ABI shared library loads and exports every symbol include/graphop_b200.h declares.
+No compute call is made here (no GPU needed)."""
+import os
+import re
+import subprocess
+
+from helpers import ROOT
+from custom_op_benchmark_b200 import _capi
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "graphop_b200.h")).read()
+    body = text[text.index("#define GRAPHOP_DECLARE"):text.index("GRAPHOP_DECLARE(f32_i32")]
+    ops = re.findall(r"int (graphop_\w+)_##SUF", body)
+    suffixes = re.findall(r"^GRAPHOP_DECLARE\((\w+),", text, re.M)
+    names = ["%s_%s" % (op, s) for op in ops for s in suffixes]
+    names += re.findall(r"^(?:int|size_t|const char\*) (graphop_\w+)\(", text, re.M)
+    return sorted(set(names))
+
+
+def test_header_and_binding_agree():
+    assert _header_symbols() == sorted(_capi.exported_symbols())
+    assert len(_header_symbols()) == 10 * 6 + 6
+
+
+def test_library_exports_every_declared_symbol():
+    assert os.path.exists(_capi.LIB_PATH), "build with python -m custom_op_benchmark_b200.build"
+    out = subprocess.run(["nm", "-D", "--defined-only", _capi.LIB_PATH], capture_output=True, text=True).stdout
+    exported = set(re.findall(r" T (graphop_\w+)", out))
+    missing = [s for s in _header_symbols() if s not in exported]
+    assert not missing, missing
+
+
+def test_library_loads_and_answers_host_only_queries():
+    lib = _capi.lib()
+    assert lib.graphop_version() >= 100
+    assert lib.graphop_error_string(0) == b"ok"
+    assert b"workspace" in lib.graphop_error_string(_capi.ERR_WORKSPACE)
+    small = lib.graphop_workspace_bytes(_capi.OP_SPMM_FWD, 1000, 100, 4, 32, 4, 4)
+    big = lib.graphop_workspace_bytes(_capi.OP_SPMM_FWD, 1_000_000, 100, 4, 32, 4, 4)
+    assert 0 < small < big
+    # int64 indices need room for the 32-bit copies
+    assert lib.graphop_workspace_bytes(_capi.OP_SPMM_FWD, 1000, 100, 4, 32, 4, 8) > small
+    assert lib.graphop_workspace_bytes(99, 1000, 100, 4, 32, 4, 4) == 0
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    import pytest
+    monkeypatch.setattr(_capi, "_lib", None)
+    monkeypatch.setattr(_capi, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _capi.lib()
