@@ -35,6 +35,8 @@ def test_fused_attention_matches_oracle_chain(name, g, cs, h, d, dtype, idt, mag
     o, lse = graphop.attention_forward(rc[0], rc[1], rc[3], Q.to(DEV), K.to(DEV), V.to(DEV), scale)
     want_o, want_dq, want_dk, want_dv = orc.attention_chain(r, c, Q, K, V, scale, dO)
     rt, at = TOL[dtype]
+    # logits grow with mag**2 and the softmax amplifies their rounding error by their size
+    rt, at = rt * mag ** 2, at * mag ** 2
     assert_close(o, want_o, rt, at, "o")
     # lse against the scores themselves
     s = orc.maskedmm_csr_forward(*r, Q, K) * scale
@@ -86,7 +88,7 @@ def test_fused_attention_is_bit_reproducible_and_matches_unfused_ops():
         assert th.equal(a, b)
     s = graphop.maskedmm_csr_forward(*rc, Q, K) * scale
     p = graphop.sparse_softmax_forward(*rc[:3], s)
-    o3 = graphop.vector_spmm_forward(*rc, p, V)
+    o3 = graphop.vector_spmm_forward(*rc, p, V, num_dst=g.n_dst)
     assert_close(o1, o3, 1e-5, 1e-6, "fused vs unfused")
 
 

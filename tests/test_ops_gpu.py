@@ -41,6 +41,15 @@ def _cuda(ts):
     return [t.to(DEV) for t in ts]
 
 
+def _atol(g, dtype):
+    """Absolute tolerance of a per-node sum: the stated one up to 256 edges per node; beyond
+    that fp32 round-off of a sum grows with sqrt(degree) and the tolerance follows it."""
+    at = TOL[dtype][1]
+    deg = int((g.indptr[1:] - g.indptr[:-1]).max()) if g.n_edges else 1
+    degt = int((g.indptr_t[1:] - g.indptr_t[:-1]).max()) if g.n_edges else 1
+    return at * max(1.0, (max(deg, degt) / 256.0) ** 0.5)
+
+
 def _row_weights(g, h, dtype, seed):
     """U(0,1) edge weights divided by the in-degree of the edge's node: sums stay O(1)."""
     deg = (g.indptr[1:] - g.indptr[:-1]).to(th.float64).clamp(min=1)
@@ -69,7 +78,7 @@ def test_vector_spmm(name, g, cs, h, d, dtype, idt):
     w = _row_weights(g, h, dtype, 1)
     x = _nodes(g.n_src, h, d, dtype, 2)
     dy = _nodes(g.n_src, h, d, dtype, 3)
-    rt, at = TOL[dtype]
+    rt, at = TOL[dtype][0], _atol(g, dtype)
     y = graphop.vector_spmm_forward(*_cuda(r), w.to(DEV), x.to(DEV))
     assert_close(y, orc.vector_spmm_forward(*r, w, x), rt, at, "y")
     ded, dx = graphop.vector_spmm_backward(*_cuda(r), *_cuda(c), w.to(DEV), dy.to(DEV), x.to(DEV))
