@@ -41,6 +41,9 @@ UNTYPED = {
     "graphop_error_string": ([_INT], ctypes.c_char_p),
     "graphop_last_cuda_error": ([], _INT),
     "graphop_workspace_bytes": ([_INT, _I64, _I64, _INT, _INT, _INT, _INT], _SZ),
+    "graphop_launch_count": ([], ctypes.c_longlong),
+    "graphop_profile_begin": ([_P], _INT),
+    "graphop_profile_end": ([_P, _SZ, _P, _INT], _INT),
     "graphop_check_graph_i32": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
     "graphop_check_graph_i64": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
 }
@@ -87,3 +90,21 @@ def error_message(code):
     if code == ERR_CUDA:
         msg += " (cudaError %d)" % handle.graphop_last_cuda_error()
     return msg
+
+
+def profile(fn, stream, max_entries=4096):
+    """Runs fn() with per-kernel timing on; returns [(kernel name, milliseconds), ...]."""
+    handle = lib()
+    rc = handle.graphop_profile_begin(stream)
+    if rc != OK:
+        raise RuntimeError("graphop_profile_begin: " + error_message(rc))
+    try:
+        fn()
+    finally:
+        names = ctypes.create_string_buffer(64 * max_entries)
+        ms = (ctypes.c_float * max_entries)()
+        n = handle.graphop_profile_end(ctypes.cast(names, ctypes.c_void_p), len(names),
+                                       ctypes.cast(ms, ctypes.c_void_p), max_entries)
+    if n < 0:
+        raise RuntimeError("graphop_profile_end failed")
+    return list(zip(names.value.decode().split("\n")[:n], [float(v) for v in ms[:n]]))

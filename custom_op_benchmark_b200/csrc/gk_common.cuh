@@ -291,6 +291,8 @@ walk_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __restrict
     const int my_other = (!kCarryLevel && inb && other) ? __ldg(other + j) : 0;
     const int my_eid = (!kCarryLevel && inb && eid) ? __ldg(eid + j) : (int)j;
     const int n = (int)(j1 - jb < 32 ? j1 - jb : 32);
+    // 32 positions without a node and no segment open: nothing to do (most slots of a carry level)
+    if (cur < 0 && __ballot_sync(kFull, my_row >= 0) == 0u) continue;
     for (int k = 0; k < n; k += U) {
       typename Op::Fetched f[U];
       typename Op::CarryIn ci[U];

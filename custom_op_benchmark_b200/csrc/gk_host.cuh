@@ -3,11 +3,14 @@
 #pragma once
 #include <cstdio>
 #include <type_traits>
+#include <utility>
+#include <vector>
 
 #include "../../include/graphop_b200.h"
 #include "gk_common.cuh"
 #include "gk_ops.cuh"
 #include "gk_softmax.cuh"
+#include "gk_staged.cuh"
 
 namespace gk {
 
@@ -17,11 +20,41 @@ inline thread_local int g_last_cuda_error = 0;
   do {                                                  \
     cudaError_t err__ = (expr);                         \
     if (err__ != cudaSuccess) {                         \
-      g_last_cuda_error = (int)err__;                   \
+      gk::g_last_cuda_error = (int)err__;                 \
       return GRAPHOP_ERR_CUDA;                          \
     }                                                   \
   } while (0)
 #define GK_LAUNCH_CHECK() GK_CUDA(cudaGetLastError())
+
+// Launch accounting and optional per-kernel timing.  Every kernel launch of the library goes
+// through GK_LAUNCHED(name): it checks the launch, counts it and, while a profile is open
+// (graphop_profile_begin), records a CUDA event behind the kernel on the caller's stream, so
+// the time between two consecutive events is the device time of the later kernel.
+struct Profiler {
+  bool enabled = false;
+  long long launches = 0;
+  std::vector<std::pair<const char*, cudaEvent_t>> marks;
+};
+inline Profiler& profiler() {
+  static Profiler p;
+  return p;
+}
+inline void mark(const char* name, cudaStream_t st) {
+  Profiler& p = profiler();
+  ++p.launches;
+  if (p.enabled) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) == cudaSuccess) {
+      cudaEventRecord(e, st);
+      p.marks.emplace_back(name, e);
+    }
+  }
+}
+#define GK_LAUNCHED(name)  \
+  do {                     \
+    GK_LAUNCH_CHECK();     \
+    gk::mark(name, st);    \
+  } while (0)
 #define GK_TRY(expr)                    \
   do {                                  \
     int rc__ = (expr);                  \
@@ -112,7 +145,7 @@ inline int prepare_graph(Arena& ar, const I* row, const I* indptr, const I* eid,
   if (ar.overflow) return GRAPHOP_ERR_WORKSPACE;
   const long long warps = (E + kExpandTile - 1) / kExpandTile;
   expand_rows_kernel<I><<<grid_for_warps(warps, kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(row, indptr, C, E, erow, hdr);
-  GK_LAUNCH_CHECK();
+  GK_LAUNCHED("expand_rows");
   g->hdr = hdr;
   g->erow = erow;
   g->E = E;
@@ -120,11 +153,11 @@ inline int prepare_graph(Arena& ar, const I* row, const I* indptr, const I* eid,
     const unsigned grid = (unsigned)((E + 1023) / 1024 < 4096 ? (E + 1023) / 1024 : 4096);
     if (indices) {
       narrow_index_kernel<I><<<grid ? grid : 1, 256, 0, st>>>(indices, other32, E);
-      GK_LAUNCH_CHECK();
+      GK_LAUNCHED("narrow_index");
     }
     if (eid) {
       narrow_index_kernel<I><<<grid ? grid : 1, 256, 0, st>>>(eid, eid32, E);
-      GK_LAUNCH_CHECK();
+      GK_LAUNCHED("narrow_index");
     }
     g->other = other32;
     g->eid = eid32;
@@ -140,7 +173,7 @@ inline int zero_uncovered(const GraphView& g, void* out, size_t bytes, cudaStrea
   if (words == 0) return GRAPHOP_OK;
   const unsigned grid = (unsigned)((words + 1023) / 1024 < 2048 ? (words + 1023) / 1024 : 2048);
   zero_uncovered_kernel<uint32_t><<<grid, 256, 0, st>>>(g.hdr, g.E, (uint32_t*)out, words);
-  GK_LAUNCH_CHECK();
+  GK_LAUNCHED("zero_uncovered");
   return GRAPHOP_OK;
 }
 
@@ -182,9 +215,49 @@ inline int dispatch_shape(const VecShape& s, F&& f) {
   return GRAPHOP_ERR_UNSUPPORTED;
 }
 
+// Calls f(integral_constant<int, LPH>) with the compile-time lanes-per-head the staged dot-product
+// ops are specialised for (8, 16, 32), or 0 for "read it at run time".
+template <class F>
+inline int dispatch_lph(int lph, F&& f) {
+  using std::integral_constant;
+  switch (lph) {
+    case 8: return f(integral_constant<int, 8>{});
+    case 16: return f(integral_constant<int, 16>{});
+    case 32: return f(integral_constant<int, 32>{});
+    default: return f(integral_constant<int, 0>{});
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // level-0 + carry-level launch sequence of a row-producing op
 // ---------------------------------------------------------------------------------------
+template <class Op>
+inline size_t staged_smem_bytes(int tile) {
+  return (size_t)kWarpsPerCta * ((size_t)3 * (tile + kMetaPad) * 4 + (size_t)Op::kDepth * Op::kEdgeBytes);
+}
+
+// Launches the staged level-0 walker; raises the kernel's dynamic shared memory limit once per device.
+template <class Op>
+inline int launch_staged(const Op& op, const GraphView& g, int tile, long long n_rows, int32_t* rows_next,
+                         cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  GK_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    GK_CUDA(cudaFuncSetAttribute(walk_staged_kernel<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)staged_smem_bytes<Op>(256)));
+    configured[dev] = true;
+  }
+  const long long nt = (g.E + tile - 1) / tile;
+  walk_staged_kernel<Op><<<grid_for_warps(nt, kWarpsPerCta), kWarpsPerCta * 32, staged_smem_bytes<Op>(tile), st>>>(
+      op, g.hdr, g.erow, g.other, g.eid, g.E, tile, n_rows, rows_next);
+  GK_LAUNCHED(Op::kName);
+  return GRAPHOP_OK;
+}
+
+template <class Op, class = void> struct IsStaged : std::false_type {};
+template <class Op> struct IsStaged<Op, std::void_t<decltype(Op::kEdgeBytes)>> : std::true_type {};
+
 // `make_op(carry_out, carry_in)` returns the op bound to one level's carry buffers.
 template <class MakeOp>
 inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_rows, size_t carry_elem_bytes,
@@ -204,13 +277,18 @@ inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_
     auto op = make_op(carry[k], k ? carry[k - 1] : nullptr);
     using Op = decltype(op);
     const unsigned grid = grid_for_warps(lv.ntiles[k], kWarpsPerCta);
-    if (k == 0)
-      walk_kernel<Op, false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E, lv.tile[0],
-                                                                n_rows, rows[1]);
-    else
+    if (k == 0) {
+      if constexpr (IsStaged<Op>::value) {
+        GK_TRY(launch_staged(op, g, lv.tile[0], n_rows, rows[1], st));
+        continue;
+      } else {
+        walk_kernel<Op, false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E,
+                                                                  lv.tile[0], n_rows, rows[1]);
+      }
+    } else
       walk_kernel<Op, true><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, rows[k], nullptr, nullptr, lv.len[k],
                                                                lv.tile[k], n_rows, rows[k + 1]);
-    GK_LAUNCH_CHECK();
+    GK_LAUNCHED(k == 0 ? Op::kName : "carry_level");
   }
   return GRAPHOP_OK;
 }
@@ -235,8 +313,10 @@ inline int run_aggregate(Arena& ar, const GraphView& g, const T* w, const T* x, 
     const size_t mark = ar.used;
     GK_TRY((dispatch_shape<T>(b, [&](auto Vc, auto Rc) -> int {
       constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+      using OpT = typename std::conditional<(V > 1 || sizeof(T) == 16), AggregateStaged<T, V, R, kEdgeFeat>,
+                                            AggregateOp<T, V, R, kEdgeFeat>>::type;
       return run_row_levels(ar, g, tile0, n_rows, sizeof(A), HD, st, [&](void* cout, void* cin) {
-        AggregateOp<T, V, R, kEdgeFeat> op;
+        OpT op;
         op.w = w; op.x = x; op.y = y; op.carry = (A*)cout; op.carry_in = (const A*)cin;
         op.H = H; op.D = D; op.HD = HD; op.S = b.S; op.feat0 = feat0;
         return op;
@@ -262,17 +342,25 @@ inline int run_edge_dot(const GraphView& g, const T* a, const T* b, T* y, int H,
     op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD;
     walk_kernel<decltype(op), false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E, tile0, 0,
                                                                         nullptr);
-    GK_LAUNCH_CHECK();
+    GK_LAUNCHED("edge_dot_any");
     return GRAPHOP_OK;
   }
   return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
-    EdgeDotOp<T, V, R, kEdgeFeat> op;
-    op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = lph;
-    walk_kernel<decltype(op), false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E, tile0, 0,
-                                                                        nullptr);
-    GK_LAUNCH_CHECK();
-    return (int)GRAPHOP_OK;
+    if constexpr (V > 1) {
+      return dispatch_lph(lph, [&](auto Lc) -> int {
+        EdgeDotStaged<T, V, R, kEdgeFeat, decltype(Lc)::value> op;
+        op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = lph;
+        return launch_staged(op, g, tile0, 0, nullptr, st);
+      });
+    } else {
+      EdgeDotOp<T, V, R, kEdgeFeat> op;
+      op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = lph;
+      walk_kernel<decltype(op), false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E,
+                                                                          tile0, 0, nullptr);
+      GK_LAUNCHED("edge_dot");
+      return (int)GRAPHOP_OK;
+    }
   });
 }
 
@@ -285,7 +373,7 @@ inline int run_edge_mix(const GraphView& g, const T* dy, const T* a, T* db, int 
   const unsigned grid = (unsigned)((total + 255) / 256 < (1 << 20) ? (total + 255) / 256 : (1 << 20));
   if (vec) edge_mix_heads_kernel<T, VM><<<grid ? grid : 1, 256, 0, st>>>(g.erow, g.eid, dy, a, db, g.E, H, D);
   else edge_mix_heads_kernel<T, 1><<<grid ? grid : 1, 256, 0, st>>>(g.erow, g.eid, dy, a, db, g.E, H, D);
-  GK_LAUNCH_CHECK();
+  GK_LAUNCHED("edge_mix_heads");
   return GRAPHOP_OK;
 }
 
@@ -316,7 +404,7 @@ inline int run_softmax_heads(Arena& ar, const GraphView& g, const T* in0, const 
   const unsigned grid0 = grid_for_warps(nt0, kSoftmaxWarps);
   softmax_tile_kernel<T, H, kBackward><<<grid0, kSoftmaxWarps * 32, 0, st>>>(g.erow, g.eid, in0, in1, out, carry0, rows1,
                                                                             g.E, hs, h0);
-  GK_LAUNCH_CHECK();
+  GK_LAUNCHED(kBackward ? "softmax_bwd_tile" : "softmax_fwd_tile");
   rows[0] = rows1;
   for (int k = 0; k < lv.n; ++k) {
     SegStatOp<A, !kBackward> op;
@@ -324,11 +412,11 @@ inline int run_softmax_heads(Arena& ar, const GraphView& g, const T* in0, const 
     op.n_nodes = n_nodes;
     walk_kernel<decltype(op), true><<<grid_for_warps(lv.ntiles[k], kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
         op, g.hdr, rows[k], nullptr, nullptr, lv.len[k], lv.tile[k], n_nodes, rows[k + 1]);
-    GK_LAUNCH_CHECK();
+    GK_LAUNCHED("carry_level");
   }
   softmax_finish_kernel<T, H, kBackward><<<grid0, kSoftmaxWarps * 32, 0, st>>>(g.erow, g.eid, in0, in1, out, stats,
                                                                               n_nodes, g.E, hs, h0);
-  GK_LAUNCH_CHECK();
+  GK_LAUNCHED(kBackward ? "softmax_bwd_finish" : "softmax_fwd_finish");
   return GRAPHOP_OK;
 }
 
@@ -539,11 +627,14 @@ inline int attention_forward(const I* row, const I* indptr, const I* indices, lo
   return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
     const long long cstride = HD + 2 * s.S;
-    return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, [&](void* cout, void* cin) {
-      AttnFwdOp<T, V, R> op;
-      op.q = q; op.k = k; op.v = v; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout; op.carry_in = (const A*)cin;
-      op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V; op.cstride = cstride;
-      return op;
+    if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
+    else return dispatch_lph(D / V, [&](auto Lc) -> int {
+      return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, [&](void* cout, void* cin) {
+        AttnFwdStaged<T, V, R, decltype(Lc)::value> op;
+        op.q = q; op.k = k; op.v = v; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout; op.carry_in = (const A*)cin;
+        op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V; op.cstride = cstride;
+        return op;
+      });
     });
   });
 }
@@ -576,12 +667,15 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
     GK_TRY(prepare_graph<I>(ar, row, indptr, (const I*)nullptr, indices, C, E, st, &g));
     GK_TRY((dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
       constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
-      return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, [&](void* cout, void* cin) {
-        AttnBwdDstOp<T, V, R> op;
-        op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dq = dq;
-        op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
-        op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
-        return op;
+      if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
+      else return dispatch_lph(D / V, [&](auto Lc) -> int {
+        return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, [&](void* cout, void* cin) {
+          AttnBwdDstStaged<T, V, R, decltype(Lc)::value> op;
+          op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.delta = delta;
+          op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+          op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+          return op;
+        });
       });
     })));
   }
@@ -590,12 +684,15 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
   GK_TRY(prepare_graph<I>(ar, col, indptr_t, (const I*)nullptr, indices_t, Ct, E, st, &g));
   return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
-    return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, [&](void* cout, void* cin) {
-      AttnBwdSrcOp<T, V, R> op;
-      op.q = q; op.k = k; op.v = v; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dk = dk; op.dv = dv;
-      op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
-      op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
-      return op;
+    if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
+    else return dispatch_lph(D / V, [&](auto Lc) -> int {
+      return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, [&](void* cout, void* cin) {
+        AttnBwdSrcStaged<T, V, R, decltype(Lc)::value> op;
+        op.q = q; op.k = k; op.v = v; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dk = dk;
+        op.dv = dv; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+        op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+        return op;
+      });
     });
   });
 }

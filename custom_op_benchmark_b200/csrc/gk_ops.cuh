@@ -20,6 +20,7 @@ namespace gk {
 template <typename T, int V, int R, bool kEdgeFeat>
 struct AggregateOp {
   using A = typename AccOf<T>::type;
+  static constexpr const char* kName = kEdgeFeat ? "aggregate_edge_feat" : "aggregate";
   static constexpr bool kRowOut = true;
   static constexpr int kUnroll = (R * V * (int)sizeof(A) <= 16) ? 8 : (R * V * (int)sizeof(A) <= 32 ? 4 : 2);
   const T* __restrict__ w;    // (E, H)
@@ -113,6 +114,7 @@ struct AggregateOp {
 template <typename T, int V, int R, bool kEdgeFeat>
 struct EdgeDotOp {
   using A = typename AccOf<T>::type;
+  static constexpr const char* kName = "edge_dot";
   static constexpr bool kRowOut = false;
   static constexpr int kUnroll = (R * V * (int)sizeof(A) <= 16) ? 8 : (R * V * (int)sizeof(A) <= 32 ? 4 : 2);
   const T* __restrict__ a;  // (n_dst, H, D)
@@ -246,6 +248,7 @@ edge_mix_heads_kernel(const int32_t* __restrict__ erow, const int32_t* __restric
 template <typename T, int V, int R>
 struct AttnFwdOp {
   using A = typename AccOf<T>::type;
+  static constexpr const char* kName = "attention_fwd";
   static constexpr bool kRowOut = true;
   static constexpr int kUnroll = (R * V * (int)sizeof(A) <= 16) ? 4 : 2;
   const T* __restrict__ q;   // (n_dst, H, D)
@@ -400,6 +403,7 @@ struct AttnFwdOp {
 template <typename T, int V, int R>
 struct AttnBwdDstOp {
   using A = typename AccOf<T>::type;
+  static constexpr const char* kName = "attention_bwd_dst";
   static constexpr bool kRowOut = true;
   static constexpr int kUnroll = (R * V * (int)sizeof(A) <= 16) ? 4 : 2;
   const T* __restrict__ q;
@@ -536,6 +540,7 @@ struct AttnBwdDstOp {
 template <typename T, int V, int R>
 struct AttnBwdSrcOp {
   using A = typename AccOf<T>::type;
+  static constexpr const char* kName = "attention_bwd_src";
   static constexpr bool kRowOut = true;
   static constexpr int kUnroll = (R * V * (int)sizeof(A) <= 16) ? 4 : 2;
   const T* __restrict__ q;

@@ -1,0 +1,602 @@
+// Level-0 walker with shared-memory staging, and the ops written for it.
+//
+// Same decomposition and the same carry / gap-fill rules as walk_kernel (gk_common.cuh); what
+// changes is how the gathered rows reach the math:
+//   * each warp owns a ring of kDepth edge entries in shared memory and keeps it full with
+//     cp.async (16 bytes per lane per operand row, straight from global memory to shared
+//     memory, no registers held while the load is in flight), so a warp has kDepth edges of
+//     gathers outstanding at all times whatever its register budget;
+//   * the tile's (node, other endpoint, edge id) triples are loaded once, coalesced, into
+//     shared memory, and row starts are a bit mask per 32 positions, so finding how many of
+//     the next edges belong to the current node is two bit operations;
+//   * up to kBatch consecutive edges of one node are folded together, which gives the
+//     scheduler kBatch independent dot-product / shuffle chains instead of one.
+// A lane only ever reads back the bytes it copied itself, so no barrier is needed between the
+// asynchronous copies and their use beyond cp.async.wait_group.
+#pragma once
+#include <type_traits>
+
+#include "gk_ops.cuh"
+
+namespace gk {
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* g) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(g) : "memory");
+}
+template <int BYTES>
+__device__ __forceinline__ void cp_async_small(void* smem, const void* g) {
+  static_assert(BYTES == 4 || BYTES == 8, "cp.async.ca moves 4, 8 or 16 bytes");
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(s), "l"(g), "n"(BYTES) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// 2^x.  float: the hardware approximation (relative error about 2^-22); double: exp2().
+__device__ __forceinline__ float gk_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ double gk_exp2(double x) { return exp2(x); }
+__device__ __forceinline__ float gk_log2(float x) { return log2f(x); }
+__device__ __forceinline__ double gk_log2(double x) { return log2(x); }
+constexpr double kLog2e = 1.4426950408889634074;
+constexpr double kLn2 = 0.69314718055994530942;
+
+// V elements of T from shared memory (16 bytes), widened to the accumulation type.
+template <typename T, int V>
+__device__ __forceinline__ void lds_acc(typename AccOf<T>::type (&dst)[V], const void* p) {
+  static_assert(sizeof(T) * V == 16, "staged slots are 16 bytes");
+  union { uint4 m; T t[V]; } u;
+  u.m = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+  for (int i = 0; i < V; ++i) dst[i] = to_acc<T>(u.t[i]);
+}
+
+// Staged op interface, on top of the walk_kernel interface (the carry levels of a staged op run
+// through walk_kernel<Op, true>):
+//   static constexpr int kBatch, kDepth, kEdgeBytes, kMinCtas;
+//   void stage(const State&, unsigned char* entry, int other, int edge, int lane)   cp.async the edge's operands
+//   template <bool kFullBatch>
+//   void consume_batch(State&, const unsigned char* ring, int i, int cnt, const int* eids, int lane)
+//        fold ring entries i .. i+cnt-1 (entry of position p at ring + (p & (kDepth-1)) * kEdgeBytes);
+//        kFullBatch: cnt == kBatch, known at compile time
+// Lanes whose slot does not exist (slot >= S) are not masked in stage / consume_batch: their slot map
+// points at slot 0, so their copies and arithmetic are harmless duplicates, their node-resident
+// operand is zero, and only stores test `ok`.
+constexpr int kMetaPad = 32;  // metadata entries past the tile that the prefetcher may read
+
+template <class Op>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, Op::kMinCtas)
+walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ erow,
+                   const int32_t* __restrict__ other, const int32_t* __restrict__ eid, long long E, int tile,
+                   long long n_rows, int32_t* __restrict__ rows_next) {
+  constexpr int U = Op::kBatch;
+  constexpr int DEPTH = Op::kDepth;
+  constexpr int EB = Op::kEdgeBytes;
+  constexpr bool kOut = Op::kRowOut;
+  static_assert((DEPTH & (DEPTH - 1)) == 0 && DEPTH >= U && U <= 32, "ring depth: a power of two >= batch");
+  extern __shared__ uint4 gk_smem[];
+  const int lane = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5;
+  const long long t = (long long)blockIdx.x * kWarpsPerCta + w;
+  const long long j0 = t * tile;
+  if (j0 >= E) return;
+  const int nt = (int)(j0 + tile < E ? tile : E - j0);
+  const long long j1 = j0 + nt;
+
+  if constexpr (kOut) {
+    if (t == 0 && hdr->cover_hi <= hdr->cover_lo) {  // no covered position at all
+      op.zero_rows(0, n_rows, lane);
+      if (rows_next && lane == 0) { rows_next[0] = -1; rows_next[1] = -1; }
+      return;
+    }
+  }
+
+  // per warp: three metadata arrays of tile + kMetaPad ints, then the ring
+  const int cap = tile + kMetaPad;
+  unsigned char* mine = reinterpret_cast<unsigned char*>(gk_smem) + (size_t)w * ((size_t)3 * cap * 4 + (size_t)DEPTH * EB);
+  int* m_row = reinterpret_cast<int*>(mine);
+  int* m_oth = m_row + cap;
+  int* m_eid = m_oth + cap;
+  unsigned char* ring = reinterpret_cast<unsigned char*>(m_eid + cap);
+
+  // Tile metadata -> shared memory; row-start bit masks, lane b keeps the mask of block b.
+  // Positions past the tile get node -2, and every position without a node points at node 0 /
+  // edge 0, so that the prefetcher can issue its copies without looking at the node.
+  const int before = j0 > 0 ? __ldg(erow + j0 - 1) : -1;
+  unsigned bm_mine = 0;
+  {
+    int carry_last = before;
+    for (int b = 0; b * 32 < cap; ++b) {
+      const int i = b * 32 + lane;
+      const bool inb = i < nt;
+      const int r = inb ? __ldg(erow + j0 + i) : -2;
+      if (i < cap) {
+        m_row[i] = r;
+        m_oth[i] = (r >= 0 && other) ? __ldg(other + j0 + i) : 0;
+        m_eid[i] = r >= 0 ? (eid ? __ldg(eid + j0 + i) : (int)(j0 + i)) : 0;
+      }
+      int up = __shfl_up_sync(kFull, r, 1);
+      if (lane == 0) up = carry_last;
+      const unsigned mask = __ballot_sync(kFull, inb && (r != up || i == 0));
+      if (lane == b) bm_mine = mask;
+      carry_last = __shfl_sync(kFull, r, 31);
+    }
+  }
+  __syncwarp();
+
+  typename Op::State st;
+  op.setup(st, lane);
+  const int first = m_row[0];
+  const bool head_open = before >= 0 && before == first;
+  bool first_seg = true;
+  int cur = -1;
+  int last_valid = before;
+  int head_row = -1;
+
+  // one commit group per position, copies issued whether or not the position carries an edge
+  auto issue = [&](int i) {
+    op.stage(st, ring + (size_t)(i & (DEPTH - 1)) * EB, m_oth[i], m_eid[i], lane);
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < DEPTH; ++i) issue(i);
+
+  for (int blk = 0; blk * 32 < nt; ++blk) {
+    const unsigned mask = __shfl_sync(kFull, bm_mine, blk);
+    const int nb = nt - blk * 32 < 32 ? nt - blk * 32 : 32;
+    int k = 0;
+    while (k < nb) {
+      const int i = blk * 32 + k;
+      const int r = m_row[i];
+      const unsigned rest = k == 31 ? 0u : (mask >> (k + 1));
+      int cnt = rest ? __ffs(rest) : 32;  // edges from k up to the next row start
+      cnt = cnt < nb - k ? cnt : nb - k;
+      if ((mask >> k) & 1u) {  // a segment starts here
+        if (cur >= 0) {
+          if constexpr (kOut) {
+            if (first_seg && head_open) { op.store_carry(st, 2 * t, lane); head_row = cur; }
+            else op.store_row(st, cur, lane);
+            if (r < 0) op.zero_rows((long long)cur + 1, n_rows, lane);  // coverage ended
+          }
+          first_seg = false;
+        }
+        if (r >= 0) {
+          if constexpr (kOut) {
+            if (!(first_seg && head_open)) op.zero_rows((long long)last_valid + 1, r, lane);
+          }
+          op.begin(st, r, lane);
+          last_valid = r;
+        }
+        cur = r;
+      }
+      cp_async_wait<DEPTH - U>();
+      if (cnt >= U) {  // the common case: a full batch of one node's edges
+        if (r >= 0) op.template consume_batch<true>(st, ring, i, U, m_eid + i, lane);
+#pragma unroll
+        for (int u = 0; u < U; ++u) issue(i + u + DEPTH);
+        k += U;
+      } else {
+        if (r >= 0) op.template consume_batch<false>(st, ring, i, cnt, m_eid + i, lane);
+        for (int u = 0; u < cnt; ++u) issue(i + u + DEPTH);
+        k += cnt;
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  if constexpr (kOut) {
+    int tail_row = -1;
+    if (cur >= 0) {
+      const int next = j1 < E ? __ldg(erow + j1) : -1;
+      const bool tail_open = next == cur;
+      if (first_seg && head_open) {  // the whole tile lies inside one node that started earlier
+        op.store_carry(st, 2 * t, lane);
+        head_row = cur;
+        if (tail_open) { op.store_identity(st, 2 * t + 1, lane); tail_row = cur; }
+      } else if (tail_open) {
+        op.store_carry(st, 2 * t + 1, lane);
+        tail_row = cur;
+      } else {
+        op.store_row(st, cur, lane);
+      }
+      if (next < 0) op.zero_rows((long long)cur + 1, n_rows, lane);  // last covered position
+    }
+    if (rows_next && lane == 0) { rows_next[2 * t] = head_row; rows_next[2 * t + 1] = tail_row; }
+  }
+}
+
+// Ring geometry shared by the staged ops: entries of `kOperands` feature rows (32*R slots of
+// 16 bytes each) plus `kScalars` per-lane scalars of the accumulation type per register.
+// Ring depth: the largest power of two (<= 16) whose ring, next to the tile metadata, lets
+// `min_ctas` blocks of kWarpsPerCta warps share one SM's shared memory.
+constexpr int pick_depth(int edge_bytes, int min_ctas) {
+  const int budget = (min_ctas >= 2 ? 100 : 208) * 1024 / kWarpsPerCta - 3 * (256 + kMetaPad) * 4;
+  int d = 16;
+  while (d > 2 && d * edge_bytes > budget) d >>= 1;
+  return d;
+}
+// Edges folded together; at most half the ring, so that the other half is in flight meanwhile.
+constexpr int pick_batch(int r, int depth) {
+  const int b = r == 1 ? 8 : (r == 2 ? 4 : 2);
+  const int half = depth / 2 > 1 ? depth / 2 : 1;
+  return b < half ? b : half;
+}
+
+template <typename T, int R, int kOperands, int kScalars>
+struct RingShape {
+  using A = typename AccOf<T>::type;
+  static constexpr int kRowBytes = 32 * R * 16;
+  static constexpr int kScalarBytes = 32 * R * (int)sizeof(A);
+  static constexpr int kEdgeBytes = kOperands * kRowBytes + kScalars * kScalarBytes;
+  static constexpr int kMinCtas = R <= 2 ? 2 : 1;
+  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas);
+  static constexpr int kBatch = pick_batch(R, kDepth);
+};
+
+// Sum of per-register partial dot products over the lanes of one head, lanes-per-head known at
+// compile time (LPH = 1, 2, 4, 8, 16 or 32; LPH = 0: read it from `lph`, any power of two).
+template <int LPH, typename A, int R>
+__device__ __forceinline__ void reduce_heads_ct(A (&p)[R], int lph) {
+  if constexpr (LPH == 0) {
+    reduce_heads<A, R>(p, lph);
+  } else {
+#pragma unroll
+    for (int o = LPH >> 1; o; o >>= 1)
+#pragma unroll
+      for (int i = 0; i < R; ++i) p[i] += __shfl_xor_sync(kFull, p[i], o);
+  }
+}
+
+#define GK_RING_ENTRY(pos) (ring + (size_t)((pos) & (kDepth - 1)) * kEdgeBytes)
+#define GK_BATCH_LOOP(u) _Pragma("unroll") for (int u = 0; u < kBatch; ++u) if (kFullBatch || u < cnt)
+
+// ---------------------------------------------------------------------------------------
+// AggregateOp, staged: ring entry = [feature row][weights]
+// ---------------------------------------------------------------------------------------
+template <typename T, int V, int R, bool kEdgeFeat>
+struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
+  using Base = AggregateOp<T, V, R, kEdgeFeat>;
+  using A = typename Base::A;
+  using State = typename Base::State;
+  using Ring = RingShape<T, R, 1, 0>;
+  // weights: one 4- or 8-byte word per lane and register (2-byte elements travel as the aligned
+  // 4-byte word that contains them; the word's last 2 bytes may lie past an odd-sized tensor's end,
+  // inside the allocation's padding)
+  using WWord = typename std::conditional<sizeof(T) == 8, double, uint32_t>::type;
+  static constexpr int kEdgeBytes = Ring::kRowBytes + 32 * R * (int)sizeof(WWord);
+  static constexpr int kMinCtas = R <= 2 ? 2 : 1;
+  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas);
+  static constexpr int kBatch = pick_batch(R, kDepth);
+
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const T* src = kEdgeFeat ? this->x + (long long)e * this->D + st.sm.efeat[i]
+                               : this->x + (long long)c * this->HD + st.sm.feat[i];
+      cp_async16(entry + (lane + 32 * i) * 16, src);
+      const T* wsrc = this->w + (long long)e * this->H + st.sm.head[i];
+      WWord* wdst = reinterpret_cast<WWord*>(entry + Ring::kRowBytes) + lane + 32 * i;
+      if constexpr (sizeof(T) == 2)
+        cp_async_small<4>(wdst, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(wsrc) & ~uintptr_t(3)));
+      else
+        cp_async_small<sizeof(T)>(wdst, wsrc);
+    }
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt,
+                                                const int* eids, int lane) const {
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        A xv[V];
+        lds_acc<T, V>(xv, entry + (lane + 32 * i) * 16);
+        const WWord word = reinterpret_cast<const WWord*>(entry + Ring::kRowBytes)[lane + 32 * i];
+        A wv;
+        if constexpr (sizeof(T) == 2) {
+          const bool hi = (((long long)eids[u] * this->H + st.sm.head[i]) & 1) != 0;
+          union { uint16_t b; T t; } cvt;
+          cvt.b = (uint16_t)(hi ? (word >> 16) : (word & 0xffffu));
+          wv = to_acc<T>(cvt.t);
+        } else {
+          union { WWord wd; T t; } cvt;
+          cvt.wd = word;
+          wv = to_acc<T>(cvt.t);
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) st.acc[i][v] += wv * xv[v];
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// EdgeDotOp, staged: ring entry = [gathered row]
+// ---------------------------------------------------------------------------------------
+template <typename T, int V, int R, bool kEdgeFeat, int LPH>
+struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
+  using Base = EdgeDotOp<T, V, R, kEdgeFeat>;
+  using A = typename Base::A;
+  using State = typename Base::State;
+  using Ring = RingShape<T, R, 1, 0>;
+  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
+                       kMinCtas = Ring::kMinCtas;
+
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const T* src = kEdgeFeat ? this->b + (long long)e * this->D + st.sm.efeat[i]
+                               : this->b + (long long)c * this->HD + st.sm.feat[i];
+      cp_async16(entry + (lane + 32 * i) * 16, src);
+    }
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt,
+                                                const int* eids, int lane) const {
+    A p[kBatch][R];
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        A bv[V];
+        lds_acc<T, V>(bv, entry + (lane + 32 * i) * 16);
+        p[u][i] = A(0);
+#pragma unroll
+        for (int v = 0; v < V; ++v) p[u][i] += st.a[i][v] * bv[v];
+      }
+    }
+    GK_BATCH_LOOP(u) reduce_heads_ct<LPH, A, R>(p[u], this->lph);
+    const int lph = LPH ? LPH : this->lph;
+    const int rph = lph >= 32 ? lph >> 5 : 1;
+    const bool writer = lph >= 32 ? lane == 0 : (lane & (lph - 1)) == 0;
+    if (writer) {
+      GK_BATCH_LOOP(u) {
+        const long long e = eids[u];
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+          if (st.sm.ok[i] && (i % rph) == 0) this->y[e * this->H + st.sm.head[i]] = from_acc<T>(p[u][i]);
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// Fused attention forward, staged.  Scores are kept in base-2 units: q is multiplied by
+// scale * log2(e) when a node starts, so a probability is one ex2 of a difference.
+// ring entry = [k row][v row]
+// ---------------------------------------------------------------------------------------
+template <typename T, int V, int R, int LPH>
+struct AttnFwdStaged : AttnFwdOp<T, V, R> {
+  using Base = AttnFwdOp<T, V, R>;
+  using A = typename Base::A;
+  using State = typename Base::State;
+  using CarryIn = typename Base::CarryIn;
+  using Ring = RingShape<T, R, 2, 0>;
+  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
+                       kMinCtas = Ring::kMinCtas;
+
+  __device__ __forceinline__ void begin(State& st, int node, int lane) const {
+    Base::begin(st, node, lane);
+    const A c = this->scale * A(kLog2e);
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+      for (int e = 0; e < V; ++e) st.q[i][e] *= c;
+  }
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      cp_async16(entry + (lane + 32 * i) * 16, this->k + (long long)c * this->HD + st.sm.feat[i]);
+      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->v + (long long)c * this->HD + st.sm.feat[i]);
+    }
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+                                                int lane) const {
+    A s[kBatch][R];
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        A kv[V];
+        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
+        s[u][i] = A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) s[u][i] += st.q[i][e] * kv[e];
+      }
+    }
+    GK_BATCH_LOOP(u) reduce_heads_ct<LPH, A, R>(s[u], this->lph);
+    // one rescale per batch: new maximum over the batch, then the batch's terms
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      A mn = st.m[i];
+      GK_BATCH_LOOP(u) mn = s[u][i] > mn ? s[u][i] : mn;
+      const A corr = gk_exp2(st.m[i] - mn);  // m = -inf at a node's first batch: 2^-inf = 0
+      st.m[i] = mn;
+      st.l[i] *= corr;
+#pragma unroll
+      for (int e = 0; e < V; ++e) st.acc[i][e] *= corr;
+    }
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u) + Ring::kRowBytes;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const A p = gk_exp2(s[u][i] - st.m[i]);
+        st.l[i] += p;
+        A vv[V];
+        lds_acc<T, V>(vv, entry + (lane + 32 * i) * 16);
+#pragma unroll
+        for (int e = 0; e < V; ++e) st.acc[i][e] += p * vv[e];
+      }
+    }
+  }
+  // m is a base-2 exponent here: lse = (m + log2 l) * ln 2, and partials merge with ex2
+  __device__ __forceinline__ void store_row(const State& st, int node, int) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      if (st.sm.ok[i]) {
+        const A inv = A(1) / st.l[i];
+        A out[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) out[e] = st.acc[i][e] * inv;
+        store_acc<T, V>(this->o + (long long)node * this->HD + st.sm.feat[i], out);
+        if (st.sm.efeat[i] == 0)
+          this->lse[(long long)node * this->H + st.sm.head[i]] = (st.m[i] + gk_log2(st.l[i])) * A(kLn2);
+      }
+    }
+  }
+  __device__ __forceinline__ void merge_carry(State& st, const CarryIn& ci, int) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (st.sm.ok[i]) {
+        const A mc = ci.m[i];
+        const A mn = mc > st.m[i] ? mc : st.m[i];
+        const A wa = st.m[i] == neg_inf<A>() ? A(0) : gk_exp2(st.m[i] - mn);
+        const A wb = mc == neg_inf<A>() ? A(0) : gk_exp2(mc - mn);
+        st.l[i] = st.l[i] * wa + ci.l[i] * wb;
+#pragma unroll
+        for (int e = 0; e < V; ++e) st.acc[i][e] = st.acc[i][e] * wa + ci.acc[i][e] * wb;
+        st.m[i] = mn;
+      }
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// Fused attention backward, destination side, staged.  ring entry = [k row][v row]
+// ---------------------------------------------------------------------------------------
+template <typename T, int V, int R, int LPH>
+struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
+  using Base = AttnBwdDstOp<T, V, R>;
+  using A = typename Base::A;
+  using State = typename Base::State;
+  using Ring = RingShape<T, R, 2, 0>;
+  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
+                       kMinCtas = Ring::kMinCtas;
+
+  // after Base::begin: q scaled to base-2 score units, lse converted to base 2
+  __device__ __forceinline__ void begin(State& st, int node, int lane) const {
+    Base::begin(st, node, lane);
+    const A c = this->scale * A(kLog2e);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      st.lse[i] *= A(kLog2e);
+#pragma unroll
+      for (int e = 0; e < V; ++e) st.q[i][e] *= c;
+    }
+  }
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      cp_async16(entry + (lane + 32 * i) * 16, this->k + (long long)c * this->HD + st.sm.feat[i]);
+      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->v + (long long)c * this->HD + st.sm.feat[i]);
+    }
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+                                                int lane) const {
+    A s[kBatch][R], dp[kBatch][R];
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        A kv[V], vv[V];
+        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
+        lds_acc<T, V>(vv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+        s[u][i] = A(0);
+        dp[u][i] = A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) { s[u][i] += st.q[i][e] * kv[e]; dp[u][i] += st.g[i][e] * vv[e]; }
+      }
+    }
+    GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const A p = gk_exp2(s[u][i] - st.lse[i]);
+        const A ds = p * (dp[u][i] - st.delta[i]) * this->scale;
+        A kv[V];
+        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
+#pragma unroll
+        for (int e = 0; e < V; ++e) st.acc[i][e] += ds * kv[e];
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// Fused attention backward, source side, staged.
+// ring entry = [q row of the destination][dO row][lse][delta]
+// ---------------------------------------------------------------------------------------
+template <typename T, int V, int R, int LPH>
+struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
+  using Base = AttnBwdSrcOp<T, V, R>;
+  using A = typename Base::A;
+  using State = typename Base::State;
+  using Ring = RingShape<T, R, 2, 2>;
+  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
+                       kMinCtas = Ring::kMinCtas;
+
+  // after Base::begin: k scaled to base-2 score units
+  __device__ __forceinline__ void begin(State& st, int node, int lane) const {
+    Base::begin(st, node, lane);
+    const A c = this->scale * A(kLog2e);
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+      for (int e = 0; e < V; ++e) st.k[i][e] *= c;
+  }
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
+    A* sc = reinterpret_cast<A*>(entry + 2 * Ring::kRowBytes);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      cp_async16(entry + (lane + 32 * i) * 16, this->q + (long long)c * this->HD + st.sm.feat[i]);
+      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->dout + (long long)c * this->HD + st.sm.feat[i]);
+      cp_async_small<sizeof(A)>(sc + lane + 32 * i, this->lse + (long long)c * this->H + st.sm.head[i]);
+      cp_async_small<sizeof(A)>(sc + 32 * R + lane + 32 * i, this->delta + (long long)c * this->H + st.sm.head[i]);
+    }
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+                                                int lane) const {
+    A s[kBatch][R], dp[kBatch][R];
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        A qv[V], gv[V];
+        lds_acc<T, V>(qv, entry + (lane + 32 * i) * 16);
+        lds_acc<T, V>(gv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+        s[u][i] = A(0);
+        dp[u][i] = A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) { s[u][i] += qv[e] * st.k[i][e]; dp[u][i] += gv[e] * st.v[i][e]; }
+      }
+    }
+    GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const A* sc = reinterpret_cast<const A*>(entry + 2 * Ring::kRowBytes);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const A p = gk_exp2(s[u][i] - sc[lane + 32 * i] * A(kLog2e));
+        const A ds = p * (dp[u][i] - sc[32 * R + lane + 32 * i]) * this->scale;
+        A qv[V], gv[V];
+        lds_acc<T, V>(qv, entry + (lane + 32 * i) * 16);
+        lds_acc<T, V>(gv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+#pragma unroll
+        for (int e = 0; e < V; ++e) { st.av[i][e] += p * gv[e]; st.ak[i][e] += ds * qv[e]; }
+      }
+    }
+  }
+  // dk accumulated against k in base-2 units would be wrong: ak sums ds * q, which does not involve k,
+  // so nothing to undo at store time.
+};
+
+}  // namespace gk

@@ -1,0 +1,4 @@
+// C ABI entry points of the fused attention pair, f32 element type.
+#include "graphop_capi_impl.cuh"
+GRAPHOP_DEFINE_ATTENTION(f32_i32, float, float, int32_t)
+GRAPHOP_DEFINE_ATTENTION(f32_i64, float, float, int64_t)

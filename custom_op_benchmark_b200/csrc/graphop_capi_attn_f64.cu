@@ -1,0 +1,4 @@
+// C ABI entry points of the fused attention pair, f64 element type.
+#include "graphop_capi_impl.cuh"
+GRAPHOP_DEFINE_ATTENTION(f64_i32, double, double, int32_t)
+GRAPHOP_DEFINE_ATTENTION(f64_i64, double, double, int64_t)

@@ -1,4 +1,4 @@
-// C ABI entry points, bfloat16 element type (fp32 accumulation).
+// C ABI entry points of the eight reference ops, bf16 element type.
 #include "graphop_capi_impl.cuh"
-GRAPHOP_DEFINE(bf16_i32, uint16_t, __nv_bfloat16, int32_t)
-GRAPHOP_DEFINE(bf16_i64, uint16_t, __nv_bfloat16, int64_t)
+GRAPHOP_DEFINE_OPS(bf16_i32, uint16_t, __nv_bfloat16, int32_t)
+GRAPHOP_DEFINE_OPS(bf16_i64, uint16_t, __nv_bfloat16, int64_t)

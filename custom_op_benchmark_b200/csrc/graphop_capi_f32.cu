@@ -1,4 +1,4 @@
-// C ABI entry points, float32 element type.
+// C ABI entry points of the eight reference ops, f32 element type.
 #include "graphop_capi_impl.cuh"
-GRAPHOP_DEFINE(f32_i32, float, float, int32_t)
-GRAPHOP_DEFINE(f32_i64, float, float, int64_t)
+GRAPHOP_DEFINE_OPS(f32_i32, float, float, int32_t)
+GRAPHOP_DEFINE_OPS(f32_i64, float, float, int64_t)

@@ -2,7 +2,7 @@
 #pragma once
 #include "gk_host.cuh"
 
-#define GRAPHOP_DEFINE(SUF, CT, T, I)                                                                                \
+#define GRAPHOP_DEFINE_OPS(SUF, CT, T, I)                                                                               \
   extern "C" int graphop_maskedmm_csr_forward_##SUF(                                                                 \
       const I* row, const I* indptr, const I* eid, const I* indices, const CT* A, const CT* B, CT* y,                \
       int64_t n_chunks, int64_t n_edges, int64_t n_dst, int64_t n_src, int H, int D, void* ws, size_t wsb,           \
@@ -61,7 +61,9 @@
     return gk::spmm_backward<T, I>(row, indptr, eid, indices, n_chunks, col, indptr_t, eid_t, indices_t, n_chunks_t, \
                                    (const T*)edata, (const T*)dy, (const T*)x, (T*)dedata, (T*)dx, n_edges, n_dst,   \
                                    n_src, H, D, ws, wsb, (cudaStream_t)stream);                                      \
-  }                                                                                                                  \
+  }
+
+#define GRAPHOP_DEFINE_ATTENTION(SUF, CT, T, I)                                                                      \
   extern "C" int graphop_attention_forward_##SUF(const I* row, const I* indptr, const I* indices, int64_t n_chunks,  \
                                                  const CT* q, const CT* k, const CT* v, double scale, CT* o,         \
                                                  void* lse, int64_t n_edges, int64_t n_dst, int64_t n_src, int H,    \

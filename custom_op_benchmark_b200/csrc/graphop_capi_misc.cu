@@ -1,5 +1,7 @@
 // C ABI entry points that do not depend on the element type: version, error text, the
 // workspace size query and the graph-contract checker.
+#include <cstring>
+
 #include "gk_host.cuh"
 
 namespace gk {
@@ -86,6 +88,46 @@ extern "C" const char* graphop_error_string(int code) {
 }
 
 extern "C" int graphop_last_cuda_error(void) { return gk::g_last_cuda_error; }
+
+extern "C" long long graphop_launch_count(void) { return gk::profiler().launches; }
+
+extern "C" int graphop_profile_begin(graphop_stream_t stream) {
+  gk::Profiler& p = gk::profiler();
+  for (auto& m : p.marks) cudaEventDestroy(m.second);
+  p.marks.clear();
+  p.enabled = true;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaEvent_t e;
+  GK_CUDA(cudaEventCreate(&e));
+  GK_CUDA(cudaEventRecord(e, st));
+  p.marks.emplace_back("begin", e);
+  return GRAPHOP_OK;
+}
+
+extern "C" int graphop_profile_end(char* names, size_t names_bytes, float* ms, int max_entries) {
+  gk::Profiler& p = gk::profiler();
+  p.enabled = false;
+  int n = 0;
+  size_t used = 0;
+  if (names && names_bytes) names[0] = 0;
+  if (!p.marks.empty()) {
+    if (cudaEventSynchronize(p.marks.back().second) != cudaSuccess) n = -1;
+    for (size_t i = 1; n >= 0 && i < p.marks.size() && n < max_entries; ++i) {
+      float t = 0.f;
+      if (cudaEventElapsedTime(&t, p.marks[i - 1].second, p.marks[i].second) != cudaSuccess) { n = -1; break; }
+      const size_t len = strlen(p.marks[i].first);
+      if (!names || used + len + 2 > names_bytes) break;
+      memcpy(names + used, p.marks[i].first, len);
+      used += len;
+      names[used++] = '\n';
+      names[used] = 0;
+      ms[n++] = t;
+    }
+  }
+  for (auto& m : p.marks) cudaEventDestroy(m.second);
+  p.marks.clear();
+  return n;
+}
 
 extern "C" size_t graphop_workspace_bytes(int op, int64_t n_edges, int64_t n_nodes, int H, int D, int elem_bytes,
                                           int index_bytes) {

@@ -69,6 +69,18 @@ const char* graphop_error_string(int code);
 /* cudaError_t of the most recent failed CUDA call made by this library on this thread. */
 int graphop_last_cuda_error(void);
 
+/* Number of kernels this library has launched in this process so far. */
+long long graphop_launch_count(void);
+
+/* Per-kernel device timing, for benchmarks.  Between graphop_profile_begin(stream) and
+ * graphop_profile_end() every kernel the library launches is followed by a CUDA event on its
+ * stream (all calls must use that one stream).  graphop_profile_end() waits for the last event
+ * and returns the number n of kernels timed (-1 on a CUDA error): ms[i] is the device time of
+ * the i-th kernel and `names` receives the n kernel names, one per line.  Not thread-safe.  The
+ * reference has no counterpart; it times whole calls with time.time() (wrapper.py:154-160). */
+int graphop_profile_begin(graphop_stream_t stream);
+int graphop_profile_end(char* names, size_t names_bytes, float* ms, int max_entries);
+
 /* Sufficient workspace for one call of `op`.  n_nodes: the largest node count among the
  * call's node tensors (for the softmax ops: an upper bound on node id + 1).  elem_bytes: 2, 4
  * or 8; index_bytes: 4 or 8. */

@@ -14,13 +14,13 @@ def _header_symbols():
     ops = re.findall(r"int (graphop_\w+)_##SUF", body)
     suffixes = re.findall(r"^GRAPHOP_DECLARE\((\w+),", text, re.M)
     names = ["%s_%s" % (op, s) for op in ops for s in suffixes]
-    names += re.findall(r"^(?:int|size_t|const char\*) (graphop_\w+)\(", text, re.M)
+    names += re.findall(r"^(?:int|size_t|long long|const char\*) (graphop_\w+)\(", text, re.M)
     return sorted(set(names))
 
 
 def test_header_and_binding_agree():
     assert _header_symbols() == sorted(_capi.exported_symbols())
-    assert len(_header_symbols()) == 10 * 6 + 6
+    assert len(_header_symbols()) == 10 * 6 + 9
 
 
 def test_library_exports_every_declared_symbol():
