@@ -8,7 +8,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libgraphop_b200.so")
+# GRAPHOP_B200_LIBRARY points at another build of the same library (kernel tuning experiments)
+LIB_PATH = os.environ.get("GRAPHOP_B200_LIBRARY") or os.path.join(HERE, "libgraphop_b200.so")
 
 OK, ERR_INVALID_ARGUMENT, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_CUDA = range(5)
 

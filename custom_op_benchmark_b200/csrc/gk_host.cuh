@@ -11,6 +11,7 @@
 #include "gk_ops.cuh"
 #include "gk_softmax.cuh"
 #include "gk_staged.cuh"
+#include "gk_attn3.cuh"
 
 namespace gk {
 
@@ -82,14 +83,14 @@ struct Arena {
 // ---------------------------------------------------------------------------------------
 // tiling
 // ---------------------------------------------------------------------------------------
-constexpr int kCarryTile = 256;
+constexpr int kCarryTile = 32;
 constexpr int kMaxLevels = 12;
 
 // Positions per warp at level 0: small graphs get small tiles so that every SM has work,
 // large graphs get 256 so that carries stay a fraction of a percent of the traffic.
 inline int pick_tile(long long n_edges) {
   long long t = 32;
-  while (t < 256 && n_edges / t > 16384) t <<= 1;
+  while (t < GK_TUNE_TILE && n_edges / t > 16384) t <<= 1;
   return (int)t;
 }
 
@@ -233,7 +234,7 @@ inline int dispatch_lph(int lph, F&& f) {
 // ---------------------------------------------------------------------------------------
 template <class Op>
 inline size_t staged_smem_bytes(int tile) {
-  return (size_t)kWarpsPerCta * ((size_t)3 * (tile + kMetaPad) * 4 + (size_t)Op::kDepth * Op::kEdgeBytes);
+  return (size_t)Op::kWarps * staged_warp_bytes<Op>(tile);
 }
 
 // Launches the staged level-0 walker; raises the kernel's dynamic shared memory limit once per device.
@@ -245,11 +246,11 @@ inline int launch_staged(const Op& op, const GraphView& g, int tile, long long n
   GK_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     GK_CUDA(cudaFuncSetAttribute(walk_staged_kernel<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)staged_smem_bytes<Op>(256)));
+                                 (int)staged_smem_bytes<Op>(GK_TUNE_TILE)));
     configured[dev] = true;
   }
   const long long nt = (g.E + tile - 1) / tile;
-  walk_staged_kernel<Op><<<grid_for_warps(nt, kWarpsPerCta), kWarpsPerCta * 32, staged_smem_bytes<Op>(tile), st>>>(
+  walk_staged_kernel<Op><<<grid_for_warps(nt, Op::kWarps), Op::kWarps * 32, staged_smem_bytes<Op>(tile), st>>>(
       op, g.hdr, g.erow, g.other, g.eid, g.E, tile, n_rows, rows_next);
   GK_LAUNCHED(Op::kName);
   return GRAPHOP_OK;
@@ -258,10 +259,12 @@ inline int launch_staged(const Op& op, const GraphView& g, int tile, long long n
 template <class Op, class = void> struct IsStaged : std::false_type {};
 template <class Op> struct IsStaged<Op, std::void_t<decltype(Op::kEdgeBytes)>> : std::true_type {};
 
-// `make_op(carry_out, carry_in)` returns the op bound to one level's carry buffers.
-template <class MakeOp>
+// `make_op(carry_out, carry_in)` returns the op bound to one level's carry buffers; `make_op0`
+// does the same for level 0 when that level runs a different (staged) op that writes the same
+// carry format.
+template <class MakeOp, class MakeOp0>
 inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_rows, size_t carry_elem_bytes,
-                          long long carry_stride, cudaStream_t st, MakeOp&& make_op) {
+                          long long carry_stride, cudaStream_t st, MakeOp&& make_op, MakeOp0&& make_op0) {
   const Levels lv = make_levels(g.E, tile0);
   void* carry[kMaxLevels];
   int32_t* rows[kMaxLevels + 1];
@@ -273,24 +276,30 @@ inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_
   }
   if (!ar.base) return GRAPHOP_OK;
   if (ar.overflow) return GRAPHOP_ERR_WORKSPACE;
-  for (int k = 0; k < lv.n; ++k) {
-    auto op = make_op(carry[k], k ? carry[k - 1] : nullptr);
+  {
+    auto op = make_op0(carry[0], nullptr);
     using Op = decltype(op);
-    const unsigned grid = grid_for_warps(lv.ntiles[k], kWarpsPerCta);
-    if (k == 0) {
-      if constexpr (IsStaged<Op>::value) {
-        GK_TRY(launch_staged(op, g, lv.tile[0], n_rows, rows[1], st));
-        continue;
-      } else {
-        walk_kernel<Op, false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E,
-                                                                  lv.tile[0], n_rows, rows[1]);
-      }
-    } else
-      walk_kernel<Op, true><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, rows[k], nullptr, nullptr, lv.len[k],
-                                                               lv.tile[k], n_rows, rows[k + 1]);
-    GK_LAUNCHED(k == 0 ? Op::kName : "carry_level");
+    if constexpr (IsStaged<Op>::value) {
+      GK_TRY(launch_staged(op, g, lv.tile[0], n_rows, rows[1], st));
+    } else {
+      walk_kernel<Op, false><<<grid_for_warps(lv.ntiles[0], kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
+          op, g.hdr, g.erow, g.other, g.eid, g.E, lv.tile[0], n_rows, rows[1]);
+      GK_LAUNCHED(Op::kName);
+    }
+  }
+  for (int k = 1; k < lv.n; ++k) {
+    auto op = make_op(carry[k], carry[k - 1]);
+    using Op = decltype(op);
+    walk_kernel<Op, true><<<grid_for_warps(lv.ntiles[k], kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
+        op, g.hdr, rows[k], nullptr, nullptr, lv.len[k], lv.tile[k], n_rows, rows[k + 1]);
+    GK_LAUNCHED("carry_level");
   }
   return GRAPHOP_OK;
+}
+template <class MakeOp>
+inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_rows, size_t carry_elem_bytes,
+                          long long carry_stride, cudaStream_t st, MakeOp&& make_op) {
+  return run_row_levels(ar, g, tile0, n_rows, carry_elem_bytes, carry_stride, st, make_op, make_op);
 }
 
 // out[node] = sum_k w[eid[k]] * feat(k): picks the vector shape, splits very wide rows into
@@ -596,6 +605,15 @@ inline int spmm_backward(const I* row, const I* indptr, const I* eid, const I* i
   return run_aggregate<T, false>(ar, g, edata, dy, dx, n_src, H, D, st);
 }
 
+// level-0 tile of the 512-byte-row attention kernels: at most 128 positions, which keeps the tile
+// metadata small enough for five blocks of four warps per SM
+#ifdef GK_DISABLE_ATTN3
+constexpr bool kUseAttn3 = false;
+#else
+constexpr bool kUseAttn3 = true;
+#endif
+inline int tile3(int tile0) { return tile0 < 128 ? tile0 : 128; }
+
 template <typename T>
 inline bool attention_shape_ok(int H, int D, bool al, VecShape* s) {
   *s = pick_shape<T>(H * D, D, al);
@@ -629,12 +647,23 @@ inline int attention_forward(const I* row, const I* indptr, const I* indices, lo
     const long long cstride = HD + 2 * s.S;
     if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
     else return dispatch_lph(D / V, [&](auto Lc) -> int {
-      return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, [&](void* cout, void* cin) {
-        AttnFwdStaged<T, V, R, decltype(Lc)::value> op;
+      constexpr int LPH = decltype(Lc)::value;
+      auto generic = [&](void* cout, void* cin) {
+        AttnFwdStaged<T, V, R, LPH> op;
         op.q = q; op.k = k; op.v = v; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout; op.carry_in = (const A*)cin;
         op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V; op.cstride = cstride;
         return op;
-      });
+      };
+      if constexpr (R == 1 && LPH != 0 && sizeof(A) == 4 && kUseAttn3) {
+        if (s.S == 32)  // a 512-byte row: the two-mapping kernel at level 0, the generic op for the carries
+          return run_row_levels(ar, g, tile3(tile0), n_dst, sizeof(A), cstride, st, generic, [&](void* cout, void*) {
+            AttnFwd3<T, V, LPH> op;
+            op.q = q; op.k = k; op.v = v; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout; op.scale = (A)scale;
+            op.cstride = cstride;
+            return op;
+          });
+      }
+      return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, generic);
     });
   });
 }
@@ -669,13 +698,24 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
       constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
       if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
       else return dispatch_lph(D / V, [&](auto Lc) -> int {
-        return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, [&](void* cout, void* cin) {
-          AttnBwdDstStaged<T, V, R, decltype(Lc)::value> op;
+        constexpr int LPH = decltype(Lc)::value;
+        auto generic = [&](void* cout, void* cin) {
+          AttnBwdDstStaged<T, V, R, LPH> op;
           op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.delta = delta;
           op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
           op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
           return op;
-        });
+        };
+        if constexpr (R == 1 && LPH != 0 && sizeof(A) == 4 && kUseAttn3) {
+          if (s.S == 32)
+            return run_row_levels(ar, g, tile3(tile0), n_dst, sizeof(A), HD, st, generic, [&](void* cout, void*) {
+              AttnBwdDst3<T, V, LPH> op;
+              op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.delta = delta;
+              op.dq = dq; op.carry = (A*)cout; op.scale = (A)scale;
+              return op;
+            });
+        }
+        return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, generic);
       });
     })));
   }
@@ -686,13 +726,24 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
     if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
     else return dispatch_lph(D / V, [&](auto Lc) -> int {
-      return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, [&](void* cout, void* cin) {
-        AttnBwdSrcStaged<T, V, R, decltype(Lc)::value> op;
+      constexpr int LPH = decltype(Lc)::value;
+      auto generic = [&](void* cout, void* cin) {
+        AttnBwdSrcStaged<T, V, R, LPH> op;
         op.q = q; op.k = k; op.v = v; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dk = dk;
         op.dv = dv; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
         op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
         return op;
-      });
+      };
+      if constexpr (R == 1 && LPH != 0 && sizeof(A) == 4 && kUseAttn3) {
+        if (s.S == 32)
+          return run_row_levels(ar, g, tile3(tile0), n_src, sizeof(A), 2 * HD, st, generic, [&](void* cout, void*) {
+            AttnBwdSrc3<T, V, LPH> op;
+            op.q = q; op.k = k; op.v = v; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dk = dk;
+            op.dv = dv; op.carry = (A*)cout; op.scale = (A)scale;
+            return op;
+          });
+      }
+      return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, generic);
     });
   });
 }

@@ -7,8 +7,8 @@
 //     memory, no registers held while the load is in flight), so a warp has kDepth edges of
 //     gathers outstanding at all times whatever its register budget;
 //   * the tile's (node, other endpoint, edge id) triples are loaded once, coalesced, into
-//     shared memory, and row starts are a bit mask per 32 positions, so finding how many of
-//     the next edges belong to the current node is two bit operations;
+//     shared memory together with one byte per position that says how many of the following
+//     positions belong to the same node;
 //   * up to kBatch consecutive edges of one node are folded together, which gives the
 //     scheduler kBatch independent dot-product / shuffle chains instead of one.
 // A lane only ever reads back the bytes it copied itself, so no barrier is needed between the
@@ -59,7 +59,7 @@ __device__ __forceinline__ void lds_acc(typename AccOf<T>::type (&dst)[V], const
 
 // Staged op interface, on top of the walk_kernel interface (the carry levels of a staged op run
 // through walk_kernel<Op, true>):
-//   static constexpr int kBatch, kDepth, kEdgeBytes, kMinCtas;
+//   static constexpr int kBatch, kDepth, kEdgeBytes, kWarps (per block), kMinCtas (blocks per SM aimed at);
 //   void stage(const State&, unsigned char* entry, int other, int edge, int lane)   cp.async the edge's operands
 //   template <bool kFullBatch>
 //   void consume_batch(State&, const unsigned char* ring, int i, int cnt, const int* eids, int lane)
@@ -70,8 +70,15 @@ __device__ __forceinline__ void lds_acc(typename AccOf<T>::type (&dst)[V], const
 // operand is zero, and only stores test `ok`.
 constexpr int kMetaPad = 32;  // metadata entries past the tile that the prefetcher may read
 
+// Shared memory of one warp: metadata of tile + kMetaPad positions (node, other endpoint, edge id if
+// the op uses it, one run-length byte), rounded to 16 bytes, then kDepth ring entries.
 template <class Op>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, Op::kMinCtas)
+__host__ __device__ constexpr size_t staged_warp_bytes(int tile) {
+  return (((size_t)(tile + kMetaPad) * (Op::kUsesEid ? 13 : 9)) + 15) / 16 * 16 + (size_t)Op::kDepth * Op::kEdgeBytes;
+}
+
+template <class Op>
+__global__ void __launch_bounds__(Op::kWarps * 32, Op::kMinCtas)
 walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ erow,
                    const int32_t* __restrict__ other, const int32_t* __restrict__ eid, long long E, int tile,
                    long long n_rows, int32_t* __restrict__ rows_next) {
@@ -83,7 +90,7 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
   extern __shared__ uint4 gk_smem[];
   const int lane = threadIdx.x & 31;
   const int w = threadIdx.x >> 5;
-  const long long t = (long long)blockIdx.x * kWarpsPerCta + w;
+  const long long t = (long long)blockIdx.x * Op::kWarps + w;
   const long long j0 = t * tile;
   if (j0 >= E) return;
   const int nt = (int)(j0 + tile < E ? tile : E - j0);
@@ -97,35 +104,43 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
     }
   }
 
-  // per warp: three metadata arrays of tile + kMetaPad ints, then the ring
+  // per warp: node and other-endpoint (and, for ops that use it, edge id) of tile + kMetaPad
+  // positions, one byte of run length per position, then the ring
   const int cap = tile + kMetaPad;
-  unsigned char* mine = reinterpret_cast<unsigned char*>(gk_smem) + (size_t)w * ((size_t)3 * cap * 4 + (size_t)DEPTH * EB);
+  unsigned char* mine = reinterpret_cast<unsigned char*>(gk_smem) + (size_t)w * staged_warp_bytes<Op>(tile);
   int* m_row = reinterpret_cast<int*>(mine);
   int* m_oth = m_row + cap;
-  int* m_eid = m_oth + cap;
-  unsigned char* ring = reinterpret_cast<unsigned char*>(m_eid + cap);
+  int* m_eid = m_oth + cap;  // present only when Op::kUsesEid
+  unsigned char* m_rem = reinterpret_cast<unsigned char*>(m_oth + (Op::kUsesEid ? 2 : 1) * cap);
+  unsigned char* ring = mine + staged_warp_bytes<Op>(tile) - (size_t)DEPTH * EB;
 
-  // Tile metadata -> shared memory; row-start bit masks, lane b keeps the mask of block b.
-  // Positions past the tile get node -2, and every position without a node points at node 0 /
-  // edge 0, so that the prefetcher can issue its copies without looking at the node.
+  // Tile metadata -> shared memory.  m_rem[i] = number of consecutive positions from i on that have
+  // the same node as i (at most 255, never past the tile): blocks of 32 are filled from the last to
+  // the first so that a run that continues into the next block can add that block's first count.
+  // Positions past the tile get node -2, and every position without a node points at node 0 / edge 0,
+  // so that the prefetcher can issue its copies without looking at the node.
   const int before = j0 > 0 ? __ldg(erow + j0 - 1) : -1;
-  unsigned bm_mine = 0;
   {
-    int carry_last = before;
-    for (int b = 0; b * 32 < cap; ++b) {
+    int next_first_row = -3, next_first_rem = 0;  // node and run length of the first position of block b + 1
+    for (int b = (cap - 1) / 32; b >= 0; --b) {
       const int i = b * 32 + lane;
-      const bool inb = i < nt;
-      const int r = inb ? __ldg(erow + j0 + i) : -2;
+      const int r = i < nt ? __ldg(erow + j0 + i) : -2;
       if (i < cap) {
         m_row[i] = r;
         m_oth[i] = (r >= 0 && other) ? __ldg(other + j0 + i) : 0;
-        m_eid[i] = r >= 0 ? (eid ? __ldg(eid + j0 + i) : (int)(j0 + i)) : 0;
+        if constexpr (Op::kUsesEid) m_eid[i] = r >= 0 ? (eid ? __ldg(eid + j0 + i) : (int)(j0 + i)) : 0;
       }
-      int up = __shfl_up_sync(kFull, r, 1);
-      if (lane == 0) up = carry_last;
-      const unsigned mask = __ballot_sync(kFull, inb && (r != up || i == 0));
-      if (lane == b) bm_mine = mask;
-      carry_last = __shfl_sync(kFull, r, 31);
+      int down = __shfl_down_sync(kFull, r, 1);
+      if (lane == 31) down = next_first_row;
+      const unsigned ends = __ballot_sync(kFull, r != down);   // bit l: the run ends at lane l
+      const unsigned at_or_after = ends >> lane;                // bit 0 <-> this lane
+      int rem;
+      if (at_or_after) rem = __ffs(at_or_after);               // run ends inside this block
+      else rem = (32 - lane) + next_first_rem;                  // runs on into block b + 1
+      rem = rem > 255 ? 255 : rem;
+      if (i < cap) m_rem[i] = (unsigned char)(i < nt ? rem : 1);
+      next_first_row = __shfl_sync(kFull, r, 0);
+      next_first_rem = __shfl_sync(kFull, rem, 0);
     }
   }
   __syncwarp();
@@ -141,51 +156,47 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
 
   // one commit group per position, copies issued whether or not the position carries an edge
   auto issue = [&](int i) {
-    op.stage(st, ring + (size_t)(i & (DEPTH - 1)) * EB, m_oth[i], m_eid[i], lane);
+    op.stage(st, ring + (size_t)(i & (DEPTH - 1)) * EB, m_oth[i], Op::kUsesEid ? m_eid[i] : 0, lane);
     cp_async_commit();
   };
 #pragma unroll
   for (int i = 0; i < DEPTH; ++i) issue(i);
 
-  for (int blk = 0; blk * 32 < nt; ++blk) {
-    const unsigned mask = __shfl_sync(kFull, bm_mine, blk);
-    const int nb = nt - blk * 32 < 32 ? nt - blk * 32 : 32;
-    int k = 0;
-    while (k < nb) {
-      const int i = blk * 32 + k;
-      const int r = m_row[i];
-      const unsigned rest = k == 31 ? 0u : (mask >> (k + 1));
-      int cnt = rest ? __ffs(rest) : 32;  // edges from k up to the next row start
-      cnt = cnt < nb - k ? cnt : nb - k;
-      if ((mask >> k) & 1u) {  // a segment starts here
-        if (cur >= 0) {
-          if constexpr (kOut) {
-            if (first_seg && head_open) { op.store_carry(st, 2 * t, lane); head_row = cur; }
-            else op.store_row(st, cur, lane);
-            if (r < 0) op.zero_rows((long long)cur + 1, n_rows, lane);  // coverage ended
-          }
-          first_seg = false;
+  bool new_seg = true;
+  int i = 0;
+  while (i < nt) {
+    const int r = m_row[i];
+    const int rem = m_rem[i];
+    if (new_seg) {  // a segment starts here
+      if (cur >= 0) {
+        if constexpr (kOut) {
+          if (first_seg && head_open) { op.store_carry(st, 2 * t, lane); head_row = cur; }
+          else op.store_row(st, cur, lane);
+          if (r < 0) op.zero_rows((long long)cur + 1, n_rows, lane);  // coverage ended
         }
-        if (r >= 0) {
-          if constexpr (kOut) {
-            if (!(first_seg && head_open)) op.zero_rows((long long)last_valid + 1, r, lane);
-          }
-          op.begin(st, r, lane);
-          last_valid = r;
-        }
-        cur = r;
+        first_seg = false;
       }
-      cp_async_wait<DEPTH - U>();
-      if (cnt >= U) {  // the common case: a full batch of one node's edges
-        if (r >= 0) op.template consume_batch<true>(st, ring, i, U, m_eid + i, lane);
+      if (r >= 0) {
+        if constexpr (kOut) {
+          if (!(first_seg && head_open)) op.zero_rows((long long)last_valid + 1, r, lane);
+        }
+        op.begin(st, r, lane);
+        last_valid = r;
+      }
+      cur = r;
+    }
+    cp_async_wait<DEPTH - U>();
+    if (rem >= U) {  // the common case: a full batch of one node's edges
+      if (r >= 0) op.template consume_batch<true>(st, ring, i, U, Op::kUsesEid ? m_eid + i : nullptr, lane);
 #pragma unroll
-        for (int u = 0; u < U; ++u) issue(i + u + DEPTH);
-        k += U;
-      } else {
-        if (r >= 0) op.template consume_batch<false>(st, ring, i, cnt, m_eid + i, lane);
-        for (int u = 0; u < cnt; ++u) issue(i + u + DEPTH);
-        k += cnt;
-      }
+      for (int u = 0; u < U; ++u) issue(i + u + DEPTH);
+      new_seg = rem == U;
+      i += U;
+    } else {
+      if (r >= 0) op.template consume_batch<false>(st, ring, i, rem, Op::kUsesEid ? m_eid + i : nullptr, lane);
+      for (int u = 0; u < rem; ++u) issue(i + u + DEPTH);
+      new_seg = true;
+      i += rem;
     }
   }
   cp_async_wait<0>();
@@ -215,8 +226,14 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
 // 16 bytes each) plus `kScalars` per-lane scalars of the accumulation type per register.
 // Ring depth: the largest power of two (<= 16) whose ring, next to the tile metadata, lets
 // `min_ctas` blocks of kWarpsPerCta warps share one SM's shared memory.
-constexpr int pick_depth(int edge_bytes, int min_ctas) {
-  const int budget = (min_ctas >= 2 ? 100 : 208) * 1024 / kWarpsPerCta - 3 * (256 + kMetaPad) * 4;
+#ifndef GK_TUNE_CTAS_NARROW
+#define GK_TUNE_CTAS_NARROW 3   // resident blocks per SM aimed at when a node row fits one slot per lane
+#endif
+#ifndef GK_TUNE_TILE
+#define GK_TUNE_TILE 256        // largest level-0 tile of the staged walker
+#endif
+constexpr int pick_depth(int edge_bytes, int min_ctas, bool uses_eid) {
+  const int budget = 216 * 1024 / min_ctas / kWarpsPerCta - (GK_TUNE_TILE + kMetaPad) * (uses_eid ? 13 : 9) - 16;
   int d = 16;
   while (d > 2 && d * edge_bytes > budget) d >>= 1;
   return d;
@@ -228,15 +245,20 @@ constexpr int pick_batch(int r, int depth) {
   return b < half ? b : half;
 }
 
-template <typename T, int R, int kOperands, int kScalars>
+template <typename T, int R, int kOperands, int kScalars, bool kEid>
 struct RingShape {
   using A = typename AccOf<T>::type;
   static constexpr int kRowBytes = 32 * R * 16;
   static constexpr int kScalarBytes = 32 * R * (int)sizeof(A);
   static constexpr int kEdgeBytes = kOperands * kRowBytes + kScalars * kScalarBytes;
-  static constexpr int kMinCtas = R <= 2 ? 2 : 1;
-  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas);
+  static constexpr int kMinCtas = R == 1 ? GK_TUNE_CTAS_NARROW : (R == 2 ? 2 : 1);
+#if defined(GK_TUNE_DEPTH2) && defined(GK_TUNE_BATCH2)
+  static constexpr int kDepth = R == 1 ? GK_TUNE_DEPTH2 : pick_depth(kEdgeBytes, kMinCtas, kEid);
+  static constexpr int kBatch = R == 1 ? GK_TUNE_BATCH2 : pick_batch(R, kDepth);
+#else
+  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, kEid);
   static constexpr int kBatch = pick_batch(R, kDepth);
+#endif
 };
 
 // Sum of per-register partial dot products over the lanes of one head, lanes-per-head known at
@@ -264,14 +286,16 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   using Base = AggregateOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
   using State = typename Base::State;
-  using Ring = RingShape<T, R, 1, 0>;
+  using Ring = RingShape<T, R, 1, 0, true>;
   // weights: one 4- or 8-byte word per lane and register (2-byte elements travel as the aligned
   // 4-byte word that contains them; the word's last 2 bytes may lie past an odd-sized tensor's end,
   // inside the allocation's padding)
   using WWord = typename std::conditional<sizeof(T) == 8, double, uint32_t>::type;
   static constexpr int kEdgeBytes = Ring::kRowBytes + 32 * R * (int)sizeof(WWord);
-  static constexpr int kMinCtas = R <= 2 ? 2 : 1;
-  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas);
+  static constexpr int kMinCtas = Ring::kMinCtas;
+  static constexpr int kWarps = kWarpsPerCta;
+  static constexpr bool kUsesEid = true;
+  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, true);
   static constexpr int kBatch = pick_batch(R, kDepth);
 
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
@@ -324,9 +348,10 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
   using Base = EdgeDotOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
   using State = typename Base::State;
-  using Ring = RingShape<T, R, 1, 0>;
+  using Ring = RingShape<T, R, 1, 0, true>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
-                       kMinCtas = Ring::kMinCtas;
+                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr bool kUsesEid = true;
 
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
 #pragma unroll
@@ -377,9 +402,10 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
   using A = typename Base::A;
   using State = typename Base::State;
   using CarryIn = typename Base::CarryIn;
-  using Ring = RingShape<T, R, 2, 0>;
+  using Ring = RingShape<T, R, 2, 0, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
-                       kMinCtas = Ring::kMinCtas;
+                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr bool kUsesEid = false;
 
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
     Base::begin(st, node, lane);
@@ -475,9 +501,10 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   using Base = AttnBwdDstOp<T, V, R>;
   using A = typename Base::A;
   using State = typename Base::State;
-  using Ring = RingShape<T, R, 2, 0>;
+  using Ring = RingShape<T, R, 2, 0, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
-                       kMinCtas = Ring::kMinCtas;
+                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr bool kUsesEid = false;
 
   // after Base::begin: q scaled to base-2 score units, lse converted to base 2
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
@@ -539,9 +566,10 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   using Base = AttnBwdSrcOp<T, V, R>;
   using A = typename Base::A;
   using State = typename Base::State;
-  using Ring = RingShape<T, R, 2, 2>;
+  using Ring = RingShape<T, R, 2, 2, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
-                       kMinCtas = Ring::kMinCtas;
+                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr bool kUsesEid = false;
 
   // after Base::begin: k scaled to base-2 score units
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
