@@ -11,7 +11,6 @@
 #include "gk_ops.cuh"
 #include "gk_softmax.cuh"
 #include "gk_staged.cuh"
-#include "gk_attn3.cuh"
 
 namespace gk {
 
@@ -605,15 +604,6 @@ inline int spmm_backward(const I* row, const I* indptr, const I* eid, const I* i
   return run_aggregate<T, false>(ar, g, edata, dy, dx, n_src, H, D, st);
 }
 
-// level-0 tile of the 512-byte-row attention kernels: at most 128 positions, which keeps the tile
-// metadata small enough for five blocks of four warps per SM
-#ifdef GK_DISABLE_ATTN3
-constexpr bool kUseAttn3 = false;
-#else
-constexpr bool kUseAttn3 = true;
-#endif
-inline int tile3(int tile0) { return tile0 < 128 ? tile0 : 128; }
-
 template <typename T>
 inline bool attention_shape_ok(int H, int D, bool al, VecShape* s) {
   *s = pick_shape<T>(H * D, D, al);
@@ -654,15 +644,6 @@ inline int attention_forward(const I* row, const I* indptr, const I* indices, lo
         op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V; op.cstride = cstride;
         return op;
       };
-      if constexpr (R == 1 && LPH != 0 && sizeof(A) == 4 && kUseAttn3) {
-        if (s.S == 32)  // a 512-byte row: the two-mapping kernel at level 0, the generic op for the carries
-          return run_row_levels(ar, g, tile3(tile0), n_dst, sizeof(A), cstride, st, generic, [&](void* cout, void*) {
-            AttnFwd3<T, V, LPH> op;
-            op.q = q; op.k = k; op.v = v; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout; op.scale = (A)scale;
-            op.cstride = cstride;
-            return op;
-          });
-      }
       return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, generic);
     });
   });
@@ -706,15 +687,6 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
           op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
           return op;
         };
-        if constexpr (R == 1 && LPH != 0 && sizeof(A) == 4 && kUseAttn3) {
-          if (s.S == 32)
-            return run_row_levels(ar, g, tile3(tile0), n_dst, sizeof(A), HD, st, generic, [&](void* cout, void*) {
-              AttnBwdDst3<T, V, LPH> op;
-              op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.delta = delta;
-              op.dq = dq; op.carry = (A*)cout; op.scale = (A)scale;
-              return op;
-            });
-        }
         return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, generic);
       });
     })));
@@ -734,15 +706,6 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
         op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
         return op;
       };
-      if constexpr (R == 1 && LPH != 0 && sizeof(A) == 4 && kUseAttn3) {
-        if (s.S == 32)
-          return run_row_levels(ar, g, tile3(tile0), n_src, sizeof(A), 2 * HD, st, generic, [&](void* cout, void*) {
-            AttnBwdSrc3<T, V, LPH> op;
-            op.q = q; op.k = k; op.v = v; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dk = dk;
-            op.dv = dv; op.carry = (A*)cout; op.scale = (A)scale;
-            return op;
-          });
-      }
       return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, generic);
     });
   });

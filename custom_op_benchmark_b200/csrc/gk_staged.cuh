@@ -18,6 +18,14 @@
 
 #include "gk_ops.cuh"
 
+// Build-time tunables.
+#ifndef GK_TUNE_CTAS_NARROW
+#define GK_TUNE_CTAS_NARROW 3   // resident blocks per SM aimed at when a node row fits one slot per lane
+#endif
+#ifndef GK_TUNE_TILE
+#define GK_TUNE_TILE 256        // largest level-0 tile of the staged walker
+#endif
+
 namespace gk {
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* g) {
@@ -61,6 +69,7 @@ __device__ __forceinline__ void lds_acc(typename AccOf<T>::type (&dst)[V], const
 // through walk_kernel<Op, true>):
 //   static constexpr int kBatch, kDepth, kEdgeBytes, kWarps (per block), kMinCtas (blocks per SM aimed at);
 //   void stage(const State&, unsigned char* entry, int other, int edge, int lane)   cp.async the edge's operands
+//   void prefetch_node(State&, int node, int lane)   start loading what begin(node) will need (may be a no-op)
 //   template <bool kFullBatch>
 //   void consume_batch(State&, const unsigned char* ring, int i, int cnt, const int* eids, int lane)
 //        fold ring entries i .. i+cnt-1 (entry of position p at ring + (p & (kDepth-1)) * kEdgeBytes);
@@ -121,14 +130,27 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
   // so that the prefetcher can issue its copies without looking at the node.
   const int before = j0 > 0 ? __ldg(erow + j0 - 1) : -1;
   {
-    int next_first_row = -3, next_first_rem = 0;  // node and run length of the first position of block b + 1
-    for (int b = (cap - 1) / 32; b >= 0; --b) {
+    // all global loads of the tile's metadata are issued before any is used: one memory latency
+    // per tile instead of one per 32 positions
+    constexpr int kMaxBlocks = (GK_TUNE_TILE + kMetaPad) / 32;
+    int r_[kMaxBlocks], o_[kMaxBlocks], e_[kMaxBlocks];
+#pragma unroll
+    for (int b = 0; b < kMaxBlocks; ++b) {
       const int i = b * 32 + lane;
-      const int r = i < nt ? __ldg(erow + j0 + i) : -2;
+      const bool inb = i < nt;
+      r_[b] = inb ? __ldg(erow + j0 + i) : -2;
+      o_[b] = (inb && other) ? __ldg(other + j0 + i) : 0;
+      e_[b] = (Op::kUsesEid && inb) ? (eid ? __ldg(eid + j0 + i) : (int)(j0 + i)) : 0;
+    }
+    int next_first_row = -3, next_first_rem = 0;  // node and run length of the first position of block b + 1
+#pragma unroll
+    for (int b = kMaxBlocks - 1; b >= 0; --b) {
+      const int i = b * 32 + lane;
+      const int r = r_[b];
       if (i < cap) {
         m_row[i] = r;
-        m_oth[i] = (r >= 0 && other) ? __ldg(other + j0 + i) : 0;
-        if constexpr (Op::kUsesEid) m_eid[i] = r >= 0 ? (eid ? __ldg(eid + j0 + i) : (int)(j0 + i)) : 0;
+        m_oth[i] = r >= 0 ? o_[b] : 0;
+        if constexpr (Op::kUsesEid) m_eid[i] = r >= 0 ? e_[b] : 0;
       }
       int down = __shfl_down_sync(kFull, r, 1);
       if (lane == 31) down = next_first_row;
@@ -182,6 +204,12 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
         }
         op.begin(st, r, lane);
         last_valid = r;
+        // the node that starts next in this tile: fetch its resident rows while this one is processed
+        const int nx = i + rem;
+        if (nx < nt) {
+          const int rn = m_row[nx];
+          if (rn >= 0 && rn != r) op.prefetch_node(st, rn, lane);
+        }
       }
       cur = r;
     }
@@ -226,12 +254,6 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
 // 16 bytes each) plus `kScalars` per-lane scalars of the accumulation type per register.
 // Ring depth: the largest power of two (<= 16) whose ring, next to the tile metadata, lets
 // `min_ctas` blocks of kWarpsPerCta warps share one SM's shared memory.
-#ifndef GK_TUNE_CTAS_NARROW
-#define GK_TUNE_CTAS_NARROW 3   // resident blocks per SM aimed at when a node row fits one slot per lane
-#endif
-#ifndef GK_TUNE_TILE
-#define GK_TUNE_TILE 256        // largest level-0 tile of the staged walker
-#endif
 constexpr int pick_depth(int edge_bytes, int min_ctas, bool uses_eid) {
   const int budget = 216 * 1024 / min_ctas / kWarpsPerCta - (GK_TUNE_TILE + kMetaPad) * (uses_eid ? 13 : 9) - 16;
   int d = 16;
@@ -252,13 +274,8 @@ struct RingShape {
   static constexpr int kScalarBytes = 32 * R * (int)sizeof(A);
   static constexpr int kEdgeBytes = kOperands * kRowBytes + kScalars * kScalarBytes;
   static constexpr int kMinCtas = R == 1 ? GK_TUNE_CTAS_NARROW : (R == 2 ? 2 : 1);
-#if defined(GK_TUNE_DEPTH2) && defined(GK_TUNE_BATCH2)
-  static constexpr int kDepth = R == 1 ? GK_TUNE_DEPTH2 : pick_depth(kEdgeBytes, kMinCtas, kEid);
-  static constexpr int kBatch = R == 1 ? GK_TUNE_BATCH2 : pick_batch(R, kDepth);
-#else
   static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, kEid);
   static constexpr int kBatch = pick_batch(R, kDepth);
-#endif
 };
 
 // Sum of per-register partial dot products over the lanes of one head, lanes-per-head known at
@@ -312,6 +329,7 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
         cp_async_small<sizeof(T)>(wdst, wsrc);
     }
   }
+  __device__ __forceinline__ void prefetch_node(State&, int, int) const {}
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt,
                                                 const int* eids, int lane) const {
@@ -347,12 +365,28 @@ template <typename T, int V, int R, bool kEdgeFeat, int LPH>
 struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
   using Base = EdgeDotOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
-  using State = typename Base::State;
+  struct State : Base::State { A an[R][V]; int next_node; };
   using Ring = RingShape<T, R, 1, 0, true>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = true;
 
+  __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
+  __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) load_acc<T, V>(st.an[i], this->a + (long long)node * this->HD + st.sm.feat[i]);
+    st.next_node = node;
+  }
+  __device__ __forceinline__ void begin(State& st, int node, int lane) const {
+    if (st.next_node == node) {
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int v = 0; v < V; ++v) st.a[i][v] = st.sm.ok[i] ? st.an[i][v] : A(0);
+    } else {
+      Base::begin(st, node, lane);
+    }
+  }
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -400,16 +434,32 @@ template <typename T, int V, int R, int LPH>
 struct AttnFwdStaged : AttnFwdOp<T, V, R> {
   using Base = AttnFwdOp<T, V, R>;
   using A = typename Base::A;
-  using State = typename Base::State;
+  struct State : Base::State { A qn[R][V]; int next_node; };
   using CarryIn = typename Base::CarryIn;
   using Ring = RingShape<T, R, 2, 0, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = false;
 
+  __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
+  __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) load_acc<T, V>(st.qn[i], this->q + (long long)node * this->HD + st.sm.feat[i]);
+    st.next_node = node;
+  }
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
-    Base::begin(st, node, lane);
     const A c = this->scale * A(kLog2e);
+    if (st.next_node == node) {
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        st.m[i] = neg_inf<A>();
+        st.l[i] = A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) { st.acc[i][e] = A(0); st.q[i][e] = st.sm.ok[i] ? st.qn[i][e] * c : A(0); }
+      }
+      return;
+    }
+    Base::begin(st, node, lane);
 #pragma unroll
     for (int i = 0; i < R; ++i)
 #pragma unroll
@@ -500,16 +550,50 @@ template <typename T, int V, int R, int LPH>
 struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   using Base = AttnBwdDstOp<T, V, R>;
   using A = typename Base::A;
-  using State = typename Base::State;
+  struct State : Base::State { A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node; };
   using Ring = RingShape<T, R, 2, 0, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = false;
 
-  // after Base::begin: q scaled to base-2 score units, lse converted to base 2
+  __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
+  __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const long long off = (long long)node * this->HD + st.sm.feat[i];
+      load_acc<T, V>(st.qn[i], this->q + off);
+      load_acc<T, V>(st.gn[i], this->dout + off);
+      load_acc<T, V>(st.on[i], this->o + off);
+      st.lsen[i] = __ldg(this->lse + (long long)node * this->H + st.sm.head[i]);
+    }
+    st.next_node = node;
+  }
+  // q scaled to base-2 score units, lse converted to base 2
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
-    Base::begin(st, node, lane);
     const A c = this->scale * A(kLog2e);
+    if (st.next_node == node) {
+      A dl[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        dl[i] = A(0);
+        st.lse[i] = st.sm.ok[i] ? st.lsen[i] * A(kLog2e) : A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          st.acc[i][e] = A(0);
+          st.q[i][e] = st.sm.ok[i] ? st.qn[i][e] * c : A(0);
+          st.g[i][e] = st.sm.ok[i] ? st.gn[i][e] : A(0);
+          dl[i] += st.g[i][e] * st.on[i][e];
+        }
+      }
+      reduce_heads_ct<LPH, A, R>(dl, this->lph);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        st.delta[i] = dl[i];
+        if (st.sm.ok[i] && st.sm.efeat[i] == 0) this->delta[(long long)node * this->H + st.sm.head[i]] = dl[i];
+      }
+      return;
+    }
+    Base::begin(st, node, lane);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       st.lse[i] *= A(kLog2e);
@@ -565,16 +649,38 @@ template <typename T, int V, int R, int LPH>
 struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   using Base = AttnBwdSrcOp<T, V, R>;
   using A = typename Base::A;
-  using State = typename Base::State;
+  struct State : Base::State { A kn[R][V]; A vn[R][V]; int next_node; };
   using Ring = RingShape<T, R, 2, 2, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = false;
 
-  // after Base::begin: k scaled to base-2 score units
+  __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
+  __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const long long off = (long long)node * this->HD + st.sm.feat[i];
+      load_acc<T, V>(st.kn[i], this->k + off);
+      load_acc<T, V>(st.vn[i], this->v + off);
+    }
+    st.next_node = node;
+  }
+  // k scaled to base-2 score units
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
-    Base::begin(st, node, lane);
     const A c = this->scale * A(kLog2e);
+    if (st.next_node == node) {
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          st.ak[i][e] = A(0);
+          st.av[i][e] = A(0);
+          st.k[i][e] = st.sm.ok[i] ? st.kn[i][e] * c : A(0);
+          st.v[i][e] = st.sm.ok[i] ? st.vn[i][e] : A(0);
+        }
+      return;
+    }
+    Base::begin(st, node, lane);
 #pragma unroll
     for (int i = 0; i < R; ++i)
 #pragma unroll

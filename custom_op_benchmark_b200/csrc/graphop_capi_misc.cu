@@ -161,10 +161,10 @@ extern "C" size_t graphop_workspace_bytes(int op, int64_t n_edges, int64_t n_nod
       break;
     }
     case GRAPHOP_OP_ATTENTION_FWD:
-      need += levels_bytes(E, tile3(tile0), 3 * HD * acc);
+      need += levels_bytes(E, tile0, 3 * HD * acc);
       break;
     case GRAPHOP_OP_ATTENTION_BWD:
-      need += align_up((size_t)n_nodes * H * acc) + levels_bytes(E, tile3(tile0), 2 * HD * acc);
+      need += align_up((size_t)n_nodes * H * acc) + levels_bytes(E, tile0, 2 * HD * acc);
       break;
     default:
       return 0;

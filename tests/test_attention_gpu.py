@@ -55,6 +55,9 @@ def test_fused_attention_matches_oracle_chain(name, g, cs, h, d, dtype, idt, mag
     if dtype == th.bfloat16:
         # o was rounded to bf16 before the backward read it: compare with a looser absolute floor
         at = 5e-2
+    # gradients are sums over a node's edges: fp32 round-off grows with sqrt(degree) beyond 256 edges
+    deg_max = max(int((g.indptr[1:] - g.indptr[:-1]).max()), int((g.indptr_t[1:] - g.indptr_t[:-1]).max()))
+    at = at * max(1.0, (deg_max / 256.0) ** 0.5)
     for got, want, what in ((dq, want_dq, "dq"), (dk, want_dk, "dk"), (dv, want_dv, "dv")):
         assert_close(got, want, rt * 5, at * max(1.0, float(want.abs().max())), what)
 
