@@ -172,6 +172,22 @@ int graphop_check_graph_i64(const int64_t* row, const int64_t* indptr, const int
                                        int64_t n_dst, int64_t n_src, int H, int D, void* workspace,                 \
                                        size_t workspace_bytes, graphop_stream_t stream);
 
+/* Scratch-free variant of graphop_vector_spmm_forward_f32_i32 for callers that cannot allocate
+ * device memory (a plugin living inside another program's memory plan, a loop that must not take
+ * the allocator's lock).  It has no counterpart in the reference.  Same arguments minus the
+ * workspace: the scratch is a fixed array of GRAPHOP_STATIC_SCRATCH_BYTES inside the library, held
+ * by every GPU that loads it.  Returns GRAPHOP_ERR_UNSUPPORTED, launching nothing, when
+ * graphop_workspace_bytes(GRAPHOP_OP_SPMM_FWD, ...) for the sizes exceeds that.  Calls no cudaMalloc
+ * / cudaFree or any allocating routine.  The first call on each device resolves the array's device
+ * address (make it before any stream capture).  All calls on a GPU share the array: calls that
+ * overlap on the device race; stale contents are harmless, every scratch word is rewritten. */
+#define GRAPHOP_STATIC_SCRATCH_BYTES (32u << 20)
+size_t graphop_static_scratch_bytes(void);
+int graphop_vector_spmm_forward_f32_i32_static(const int32_t* row, const int32_t* indptr, const int32_t* eid,
+                                               const int32_t* indices, const float* edata, const float* x, float* y,
+                                               int64_t n_chunks, int64_t n_edges, int64_t n_dst, int64_t n_src,
+                                               int H, int D, graphop_stream_t stream);
+
 GRAPHOP_DECLARE(f32_i32, float, int32_t)
 GRAPHOP_DECLARE(f32_i64, float, int64_t)
 GRAPHOP_DECLARE(f64_i32, double, int32_t)
