@@ -266,6 +266,8 @@ def run_gpu(args):
     # -- per-kernel times of the same step, CUDA events behind every kernel ---------------------
     per_kernel = {}
     prof_steps = max(2, min(args.steps, 5))
+    step_device()            # the e2e loop left the allocator in another state: settle it before timing
+    th.cuda.synchronize()
     recs = _capi.profile(lambda: [step_device() for _ in range(prof_steps)], th.cuda.current_stream().cuda_stream)
     for name, ms in recs:
         per_kernel.setdefault(name, []).append(ms)
