@@ -39,11 +39,17 @@ UNIT = "edges*heads/s"
 # workloads
 # --------------------------------------------------------------------------------------------
 WORKLOADS = {
-    # name: (graph maker, heads, dim, dtype)
-    "rmat21_attention": dict(kind="rmat", scale=21, edge_factor=16, heads=4, dim=32, dtype="f32"),
-    "er_small_attention": dict(kind="er", n=4096, k=15, heads=8, dim=64, dtype="f32"),
-    "banded_attention": dict(kind="banded", batch=4, length=8192, window=128, heads=8, dim=64, dtype="bf16"),
-    "zipf_attention": dict(kind="zipf", n=1_000_000, total=50_000_000, heads=2, dim=64, dtype="f32"),
+    # the fused chain (maskedmm -> scale -> sparse_softmax -> vector_spmm), forward + backward
+    "rmat21_attention": dict(kind="rmat", scale=21, edge_factor=16, heads=4, dim=32, dtype="f32", ops="attention"),
+    "er_small_attention": dict(kind="er", n=4096, k=15, heads=8, dim=64, dtype="f32", ops="attention"),
+    "banded_attention": dict(kind="banded", batch=4, length=8192, window=128, heads=8, dim=64, dtype="bf16",
+                             ops="attention"),
+    "zipf_attention": dict(kind="zipf", n=1_000_000, total=50_000_000, heads=2, dim=64, dtype="f32", ops="attention"),
+    # node_mul_edge + vector_spmm, forward + backward, softmax-normalised edge weights (GAT style)
+    "rmat21_gat": dict(kind="rmat", scale=21, edge_factor=16, heads=4, dim=32, dtype="f32", ops="gat"),
+    # maskedmm + sparse_softmax, forward + backward, inputs scaled by 3 (max-subtraction stress)
+    "zipf_sddmm_softmax": dict(kind="zipf", n=1_000_000, total=50_000_000, heads=2, dim=64, dtype="f32",
+                               ops="sddmm_softmax"),
 }
 DTYPES = {"f32": th.float32, "bf16": th.bfloat16, "f64": th.float64}
 
@@ -71,22 +77,189 @@ def describe(spec):
     return "rank-size (Zipf 1.1) in-degrees n=%d, %d edges" % (spec["n"], spec["total"])
 
 
-def algorithmic_bytes(n_dst, n_src, e, h, d, s, i):
-    """Compulsory bytes (every input read once, every output written once, no intermediate)."""
-    f_dst, f_src = n_dst * h * d * s, n_src * h * d * s
-    idx = (e + n_dst + 1) * i
-    idx_t = (e + n_src + 1) * i
-    stat = n_dst * h * 4
-    return {
-        # q, k, v read, o written, indices, lse written
-        "attention_fwd": f_dst + 2 * f_src + f_dst + idx + stat,
-        # q, o, dO, k, v read, dq written, indices, lse read, delta written
-        "attention_bwd_dst": 3 * f_dst + 2 * f_src + f_dst + idx + 2 * stat,
-        # k, v, q, dO read, dk, dv written, transposed indices, lse and delta read
-        "attention_bwd_src": 2 * f_src + 2 * f_dst + 2 * f_src + idx_t + 2 * stat,
-        # whole step with every tensor touched once: forward 4F + I + 4NH, backward 8F + 2I + P + 4NH
-        "step": (2 * f_dst + 2 * f_src + idx + stat) + (4 * f_dst + 4 * f_src + idx + idx_t + e * i + stat),
-    }
+def _nbytes(ts):
+    return sum(t.numel() * t.element_size() for t in ts)
+
+
+class Workload:
+    """One rank's inputs and its step.  `host` tensors are pinned (the e2e leg copies them in every
+    step), `alg` maps a kernel name of the library's profile to its compulsory bytes per launch."""
+
+    def __init__(self, spec, rank, dev):
+        from custom_op_benchmark_b200.part_csr import partition_csr
+        self.spec, self.dev = spec, dev
+        self.h, self.d, self.dtype = spec["heads"], spec["dim"], DTYPES[spec["dtype"]]
+        g = make_graph(spec, seed=rank, device=dev)
+        row, ptr = partition_csr(g.indptr, 32)
+        col, ptr_t = partition_csr(g.indptr_t, 32)
+        self.R = [row.to(th.int32), ptr.to(th.int32), g.eid, g.indices]
+        self.C = [col.to(th.int32), ptr_t.to(th.int32), g.eid_t, g.indices_t]
+        self.g, self.e, self.n_dst, self.n_src = g, g.n_edges, g.n_dst, g.n_src
+        self.gen = th.Generator().manual_seed(1000 + rank)
+
+    def _host(self, *shape, mag=1.0):
+        return (th.randn(*shape, generator=self.gen) * mag).to(self.dtype).pin_memory()
+
+    def _release(self, leaves):
+        for t in leaves:
+            t.requires_grad_(False)
+            t.grad = None
+
+    def units(self):
+        return float(self.e) * self.h
+
+    def sizes(self):
+        s, i = th.empty(0, dtype=self.dtype).element_size(), 4
+        f_dst, f_src = self.n_dst * self.h * self.d * s, self.n_src * self.h * self.d * s
+        return dict(s=s, i=i, F_dst=f_dst, F_src=f_src, S=self.e * self.h * s, I=(self.e + self.n_dst + 1) * i,
+                    I_t=(self.e + self.n_src + 1) * i, stat=self.n_dst * self.h * 4, Be=self.e * self.d * s,
+                    P=self.e * i)
+
+    def e2e_bytes(self):
+        return _nbytes(self.host), _nbytes(self.outs)
+
+
+class AttentionWorkload(Workload):
+    name = "fused attention forward + backward"
+    resident = "graph structure; e2e copies Q, K, V, dO in and O, dQ, dK, dV out every step"
+
+    def __init__(self, spec, rank, dev):
+        super().__init__(spec, rank, dev)
+        n, m, h, d = self.n_dst, self.n_src, self.h, self.d
+        self.host = [self._host(n, h, d), self._host(m, h, d), self._host(m, h, d), self._host(n, h, d)]
+        self.Q, self.K, self.V, self.dO = (t.to(dev) for t in self.host)
+        self.scale = d ** -0.5
+        self.outs = [th.empty_like(t).pin_memory() for t in (self.host[0], self.host[0], self.host[1], self.host[2])]
+        self.stage = [th.empty_like(t) for t in (self.Q, self.K, self.V, self.dO)]
+        z = self.sizes()
+        self.alg = {
+            # q, k, v read, o written, indices, lse written
+            "attention_fwd": z["F_dst"] + 2 * z["F_src"] + z["F_dst"] + z["I"] + z["stat"],
+            # q, o, dO, k, v read, dq written, indices, lse read, delta written
+            "attention_bwd_dst": 3 * z["F_dst"] + 2 * z["F_src"] + z["F_dst"] + z["I"] + 2 * z["stat"],
+            # k, v, q, dO read, dk, dv written, transposed indices, lse and delta read
+            "attention_bwd_src": 2 * z["F_src"] + 2 * z["F_dst"] + 2 * z["F_src"] + z["I_t"] + 2 * z["stat"],
+        }
+        # every tensor once: forward 4F + I + 4NH, backward 8F + 2I + P + 4NH
+        self.alg_step = (2 * z["F_dst"] + 2 * z["F_src"] + z["I"] + z["stat"]) + \
+                        (4 * z["F_dst"] + 4 * z["F_src"] + z["I"] + z["I_t"] + z["P"] + z["stat"])
+
+    def forward(self):
+        from custom_op_benchmark_b200 import graphop
+        R = self.R
+        self.o, self.lse = graphop.attention_forward(R[0], R[1], R[3], self.Q, self.K, self.V, self.scale)
+
+    def backward(self):
+        from custom_op_benchmark_b200 import graphop
+        R, C = self.R, self.C
+        return graphop.attention_backward(R[0], R[1], R[3], C[0], C[1], C[3], self.Q, self.K, self.V, self.o, self.lse,
+                                          self.dO, self.scale)
+
+    def e2e_step(self):
+        from custom_op_benchmark_b200 import wrapper
+        R, C = self.R, self.C
+        q, k, v = (b.copy_(hst, non_blocking=True).requires_grad_(True)
+                   for b, hst in zip(self.stage[:3], self.host[:3]))
+        go = self.stage[3].copy_(self.host[3], non_blocking=True)
+        out = wrapper.GraphAttention.apply(R[0], R[1], R[3], C[0], C[1], C[3], q, k, v, self.scale)
+        out.backward(go)
+        for dst, src in zip(self.outs, (out.detach(), q.grad, k.grad, v.grad)):
+            dst.copy_(src, non_blocking=True)
+        self._release(self.stage[:3])
+
+
+class GatWorkload(Workload):
+    name = "node_mul_edge + vector_spmm, forward + backward"
+    resident = "graph structure; e2e copies X, B_edge, the edge weights and both upstream gradients in, both " \
+               "outputs and the three gradients out every step"
+
+    def __init__(self, spec, rank, dev):
+        from custom_op_benchmark_b200 import graphop
+        super().__init__(spec, rank, dev)
+        n, h, d, e = self.n_dst, self.h, self.d, self.e
+        raw = th.rand(e, h, generator=self.gen).to(self.dtype).to(dev)
+        w = graphop.sparse_softmax_forward(*self.R[:3], raw)          # sparse_softmax-normalised weights
+        self.host = [self._host(n, h, d), self._host(e, d), w.cpu().pin_memory(), self._host(e, h), self._host(n, h, d)]
+        self.X, self.Be, self.w, self.dY1, self.dY2 = (t.to(dev) for t in self.host)
+        self.stage = [th.empty_like(t) for t in (self.X, self.Be, self.w, self.dY1, self.dY2)]
+        self.outs = [th.empty(s, dtype=self.dtype).pin_memory() for s in ((e, h), (n, h, d), (e, d), (n, h, d), (e, h))]
+        z = self.sizes()
+        gather = 2 * z["F_dst"] + z["S"] + z["I"]
+        self.alg = {"edge_dot": gather, "aggregate": gather,
+                    "aggregate_edge_feat": z["F_dst"] + z["Be"] + z["S"] + z["I"],
+                    "edge_mix_heads": z["F_dst"] + 2 * z["Be"] + z["S"]}
+        # node_mul_edge fwd F + Be + S, bwd 2F + 2Be + S; spmm fwd 2F + S + I, bwd 3F + 2S + 2I + P
+        self.alg_step = (z["F_dst"] + z["Be"] + z["S"]) + (2 * z["F_dst"] + 2 * z["Be"] + z["S"]) + \
+                        (2 * z["F_dst"] + z["S"] + z["I"]) + (3 * z["F_dst"] + 2 * z["S"] + 2 * z["I"] + z["P"])
+
+    def forward(self):
+        from custom_op_benchmark_b200 import graphop
+        self.y1 = graphop.node_mul_edge_forward(*self.R[:3], self.X, self.Be)
+        self.y2 = graphop.vector_spmm_forward(*self.R, self.w, self.X)
+
+    def backward(self):
+        from custom_op_benchmark_b200 import graphop
+        a = graphop.node_mul_edge_backward(*self.R[:3], self.X, self.Be, self.dY1)
+        b = graphop.vector_spmm_backward(*self.R, *self.C, self.w, self.dY2, self.X)
+        return a + b
+
+    def e2e_step(self):
+        from custom_op_benchmark_b200 import wrapper
+        x, be, w = (b.copy_(hst, non_blocking=True).requires_grad_(True)
+                    for b, hst in zip(self.stage[:3], self.host[:3]))
+        g1 = self.stage[3].copy_(self.host[3], non_blocking=True)
+        g2 = self.stage[4].copy_(self.host[4], non_blocking=True)
+        y1 = wrapper.NodeMulEdge.apply(*self.R[:3], x, be)
+        y2 = wrapper.VectorSPMM.apply(*self.R, *self.C, w, x)
+        th.autograd.backward([y1, y2], [g1, g2])
+        for dst, src in zip(self.outs, (y1.detach(), y2.detach(), be.grad, x.grad, w.grad)):
+            dst.copy_(src, non_blocking=True)
+        self._release(self.stage[:3])
+
+
+class SddmmSoftmaxWorkload(Workload):
+    name = "maskedmm + sparse_softmax, forward + backward"
+    resident = "graph structure; e2e copies Q, K and the upstream gradient in, the probabilities and dQ, dK out"
+
+    def __init__(self, spec, rank, dev):
+        super().__init__(spec, rank, dev)
+        n, m, h, d, e = self.n_dst, self.n_src, self.h, self.d, self.e
+        self.host = [self._host(n, h, d, mag=3.0), self._host(m, h, d, mag=3.0), self._host(e, h)]
+        self.Q, self.K, self.dP = (t.to(dev) for t in self.host)
+        self.stage = [th.empty_like(t) for t in (self.Q, self.K, self.dP)]
+        self.outs = [th.empty(s, dtype=self.dtype).pin_memory() for s in ((e, h), (n, h, d), (m, h, d))]
+        z = self.sizes()
+        gather = z["F_dst"] + z["F_src"] + z["S"] + z["I"]
+        self.alg = {"edge_dot": gather, "aggregate": gather,
+                    "softmax_fwd_tile": 2 * z["S"] + (self.n_dst + 1) * z["i"],
+                    "softmax_bwd_tile": 3 * z["S"] + (self.n_dst + 1) * z["i"]}
+        # SDDMM fwd 2F + S + I, bwd 4F + S + 2I + P; softmax fwd 2S + (N+1)i, bwd 3S + (N+1)i
+        self.alg_step = (2 * z["F_dst"] + z["S"] + z["I"]) + (4 * z["F_dst"] + z["S"] + 2 * z["I"] + z["P"]) + \
+                        5 * z["S"] + 2 * (self.n_dst + 1) * z["i"]
+
+    def forward(self):
+        from custom_op_benchmark_b200 import graphop
+        self.s = graphop.maskedmm_csr_forward(*self.R, self.Q, self.K)
+        self.p = graphop.sparse_softmax_forward(*self.R[:3], self.s)
+
+    def backward(self):
+        from custom_op_benchmark_b200 import graphop
+        ds = graphop.sparse_softmax_backward(*self.R[:3], self.p, self.dP)
+        return graphop.maskedmm_csr_backward(*self.R, *self.C, self.Q, self.K, ds)
+
+    def e2e_step(self):
+        from custom_op_benchmark_b200 import wrapper
+        q, k = (b.copy_(hst, non_blocking=True).requires_grad_(True) for b, hst in zip(self.stage[:2], self.host[:2]))
+        gp = self.stage[2].copy_(self.host[2], non_blocking=True)
+        s = wrapper.MaskedMMCSR.apply(*self.R, *self.C, q, k)
+        p = wrapper.SparseSoftmax.apply(*self.R[:3], s)
+        p.backward(gp)
+        for dst, src in zip(self.outs, (p.detach(), q.grad, k.grad)):
+            dst.copy_(src, non_blocking=True)
+        self._release(self.stage[:2])
+
+
+WORKLOAD_CLASSES = {"attention": AttentionWorkload, "gat": GatWorkload, "sddmm_softmax": SddmmSoftmaxWorkload}
 
 
 # --------------------------------------------------------------------------------------------
@@ -157,8 +330,7 @@ def traffic_for(kernel, workload):
 
 
 def run_gpu(args):
-    from custom_op_benchmark_b200 import _capi, graphop, wrapper
-    from custom_op_benchmark_b200.part_csr import partition_csr
+    from custom_op_benchmark_b200 import _capi
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -170,23 +342,12 @@ def run_gpu(args):
     spec = dict(WORKLOADS[args.workload])
     if args.scale and spec["kind"] == "rmat":
         spec["scale"] = args.scale
-    h, d, dtype = spec["heads"], spec["dim"], DTYPES[spec["dtype"]]
-    scale = d ** -0.5
-
-    # -- inputs: graph resident on the device, features drawn on the host (pinned) -----------
-    g = make_graph(spec, seed=rank, device=dev)
-    row, ptr = partition_csr(g.indptr, 32)
-    col, ptr_t = partition_csr(g.indptr_t, 32)
-    row, ptr, col, ptr_t = (t.to(th.int32) for t in (row, ptr, col, ptr_t))
-    e, n_dst, n_src = g.n_edges, g.n_dst, g.n_src
-    gen = th.Generator().manual_seed(1000 + rank)
-    host = [th.randn(n, h, d, generator=gen).to(dtype).pin_memory() for n in (n_dst, n_src, n_src, n_dst)]
-    Q, K, V, dO = (t.to(dev) for t in host)
+    wl = WORKLOAD_CLASSES[spec["ops"]](spec, rank, dev)
     lib = _capi.lib()
 
     def step_device():
-        o, lse = graphop.attention_forward(row, ptr, g.indices, Q, K, V, scale)
-        return o, graphop.attention_backward(row, ptr, g.indices, col, ptr_t, g.indices_t, Q, K, V, o, lse, dO, scale)
+        wl.forward()
+        return wl.backward()
 
     warmup = args.warmup if args.lean else max(args.warmup, 3)
     for _ in range(warmup):
@@ -200,8 +361,8 @@ def run_gpu(args):
             step_device()
         b.record()
         th.cuda.synchronize()
-        print(json.dumps({"lean": True, "workload": args.workload, "edges": e, "nodes": n_dst, "heads": h, "dim": d,
-                          "ms_per_step": a.elapsed_time(b) / args.steps}))
+        print(json.dumps({"lean": True, "workload": args.workload, "edges": wl.e, "nodes": wl.n_dst, "heads": wl.h,
+                          "dim": wl.d, "ms_per_step": a.elapsed_time(b) / args.steps}))
         return
 
     # -- timed region: K steps, inputs resident, CUDA events on the launching stream ----------
@@ -216,9 +377,9 @@ def run_gpu(args):
     t_wall0 = time.time()
     ev[0].record()
     for i in range(args.steps):
-        o, lse = graphop.attention_forward(row, ptr, g.indices, Q, K, V, scale)
+        wl.forward()
         ev[2 * i + 1].record()
-        graphop.attention_backward(row, ptr, g.indices, col, ptr_t, g.indices_t, Q, K, V, o, lse, dO, scale)
+        wl.backward()
         ev[2 * i + 2].record()
     th.cuda.synchronize()
     t_wall1 = time.time()
@@ -228,47 +389,39 @@ def run_gpu(args):
     total_ms = ev[0].elapsed_time(ev[-1])
     fwd_ms = statistics.mean(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps))
     bwd_ms = statistics.mean(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps))
+    if t_wall1 - t_wall0 < 0.6:   # a short timed region: keep the same load up until the sampler has a few rows
+        t_end = time.time() + 0.7
+        while time.time() < t_end:
+            step_device()
+        th.cuda.synchronize()
+        t_wall1 = time.time()
+    sampler.stop()
+    clocks = sampler.summary(t_wall0, t_wall1)
 
-    # -- end to end: the autograd Function a user calls, host buffers copied in and out every step
-    outs = [th.empty_like(t).pin_memory() for t in (host[0], host[0], host[1], host[2])]
-    dQ_, dK_, dV_, dO_ = (th.empty_like(t) for t in (Q, K, V, dO))
-
-    def step_e2e():
-        q = dQ_.copy_(host[0], non_blocking=True).requires_grad_(True)
-        k = dK_.copy_(host[1], non_blocking=True).requires_grad_(True)
-        v = dV_.copy_(host[2], non_blocking=True).requires_grad_(True)
-        go = dO_.copy_(host[3], non_blocking=True)
-        out = wrapper.GraphAttention.apply(row, ptr, g.indices, col, ptr_t, g.indices_t, q, k, v, scale)
-        out.backward(go)
-        outs[0].copy_(out.detach(), non_blocking=True)
-        outs[1].copy_(q.grad, non_blocking=True)
-        outs[2].copy_(k.grad, non_blocking=True)
-        outs[3].copy_(v.grad, non_blocking=True)
-        for t in (dQ_, dK_, dV_):
-            t.requires_grad_(False)
-            t.grad = None
-
+    # -- end to end: the autograd Functions a user calls, host buffers copied in and out every step
     e2e_steps = max(2, min(args.steps, 5))
-    step_e2e()
+    wl.e2e_step()
     th.cuda.synchronize()
     if world > 1:
         dist.barrier()
     a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(e2e_steps):
-        step_e2e()
+        wl.e2e_step()
     b.record()
     th.cuda.synchronize()
     e2e_ms = a.elapsed_time(b) / e2e_steps
-    sampler.stop()
-    clocks = sampler.summary(t_wall0, t_wall1)
 
     # -- per-kernel times of the same step, CUDA events behind every kernel ---------------------
     per_kernel = {}
     prof_steps = max(2, min(args.steps, 5))
     step_device()            # the e2e loop left the allocator in another state: settle it before timing
     th.cuda.synchronize()
-    recs = _capi.profile(lambda: [step_device() for _ in range(prof_steps)], th.cuda.current_stream().cuda_stream)
+    def profiled():
+        for _ in range(prof_steps):   # results dropped at once: kept alive they would force fresh cudaMallocs
+            step_device()
+
+    recs = _capi.profile(profiled, th.cuda.current_stream().cuda_stream)
     for name, ms in recs:
         per_kernel.setdefault(name, []).append(ms)
     kernels = {k: {"launches_per_step": len(v) / prof_steps, "ms_per_step": sum(v) / prof_steps}
@@ -276,7 +429,7 @@ def run_gpu(args):
 
     # -- reduce over ranks ---------------------------------------------------------------------
     stats = th.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], dtype=th.float64, device=dev)
-    work = th.tensor([float(e) * h], dtype=th.float64, device=dev)
+    work = th.tensor([wl.units()], dtype=th.float64, device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(work, op=dist.ReduceOp.SUM)
@@ -284,33 +437,35 @@ def run_gpu(args):
     units = work.item()  # edges*heads of all ranks, per step
 
     if rank == 0:
-        s_bytes, i_bytes = Q.element_size(), 4
-        alg = algorithmic_bytes(n_dst, n_src, e, h, d, s_bytes, i_bytes)
+        alg = wl.alg
         top = max((k for k in kernels if k in alg), key=lambda k: kernels[k]["ms_per_step"])
         top_ms = kernels[top]["ms_per_step"] / max(1.0, kernels[top]["launches_per_step"])
         peak, peak_kind = measured_peak()
         achieved = alg[top] / (top_ms * 1e-3) / 1e9
         ms_per_step = total_ms / args.steps
-        feat_bytes = sum(t.numel() * t.element_size() for t in host)
+        h2d, d2h = wl.e2e_bytes()
+        in_bytes = _nbytes(wl.host)
         out = {
             "metric": METRIC, "value": units / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": spec["dtype"],
             "data": "synthetic",
-            "config": {"workload": args.workload, "graph": describe(spec), "nodes": n_dst, "edges": e, "heads": h,
-                       "dim": d, "index": "int32 CSR, chunk tables of partition_csr(32)", "per_rank": "own graph",
-                       "l2": "inputs (%.1f GB of node features) larger than the 126 MB L2" % (feat_bytes / 1e9),
-                       "resident": "graph structure; e2e copies Q, K, V, dO in and O, dQ, dK, dV out every step"},
+            "config": {"workload": args.workload, "ops": wl.name, "graph": describe(spec), "nodes": wl.n_dst,
+                       "edges": wl.e, "heads": wl.h, "dim": wl.d,
+                       "index": "int32 CSR, chunk tables of partition_csr(32)", "per_rank": "own graph",
+                       "l2": "inputs (%.2f GB) %s the 126 MB L2" % (
+                           in_bytes / 1e9, "larger than" if in_bytes > 2 * 126e6 else "NOT larger than"),
+                       "resident": wl.resident},
             "e2e": {"value": units / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": feat_bytes, "d2h_bytes_per_step": feat_bytes},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "phases": {"forward_ms": fwd_ms, "backward_ms": bwd_ms},
             "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": peak_kind, "algorithmic_bytes": alg[top],
                          "ms": top_ms, "traffic": traffic_for(top, args.workload),
-                         "step_algorithmic_bytes": alg["step"],
-                         "step_frac": alg["step"] / (ms_per_step * 1e-3) / 1e9 / peak},
+                         "step_algorithmic_bytes": wl.alg_step,
+                         "step_frac": wl.alg_step / (ms_per_step * 1e-3) / 1e9 / peak},
             "kernels": kernels,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -324,7 +479,7 @@ def run_gpu(args):
 # the CPU baseline and the reference arm
 # --------------------------------------------------------------------------------------------
 def cpu_baseline(spec, sample_scale):
-    """The torch CPU chain (oracle/cpu_baseline.py) timed on a bounded sample of the workload."""
+    """The torch CPU port of the workload's ops (oracle/cpu_baseline.py) timed on a bounded sample."""
     from custom_op_benchmark_b200 import graphs
     from oracle import cpu_baseline as cb
     h, d = spec["heads"], spec["dim"]
@@ -341,12 +496,10 @@ def cpu_baseline(spec, sample_scale):
     else:
         g = graphs.zipf_graph(spec["n"] // 25, spec["total"] // 25, cap=spec["total"] // 25, seed=0)
         sample = "the same degree law at 1/25 of the nodes and edges"
-    gen = th.Generator().manual_seed(1)
-    Q, K, V, dO = (th.randn(n, h, d, generator=gen) for n in (g.n_dst, g.n_src, g.n_src, g.n_dst))
-    sec = cb.time_chain(g.indptr, g.indices, Q, K, V, d ** -0.5, dO, repeats=1)
+    sec = cb.time_workload(spec["ops"], g, h, d)
     return {"value": g.n_edges * h / sec, "unit": UNIT, "cores": th.get_num_threads(), "host_cpus": os.cpu_count(),
             "kind": "port", "seconds": sec,
-            "sample": sample + "; torch CPU fp32 chain, forward + backward through autograd"}
+            "sample": sample + "; torch CPU fp32, forward + backward through autograd"}
 
 
 def run_reference(args):

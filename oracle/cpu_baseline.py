@@ -53,3 +53,52 @@ def time_chain(indptr, indices, Q, K, V, scale, dO, repeats=1):
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     return best
+
+
+def _edge_list(indptr, indices):
+    ip = indptr.to("cpu", th.int64)
+    dst = th.repeat_interleave(th.arange(ip.numel() - 1), ip[1:] - ip[:-1])
+    return dst, indices.to("cpu", th.int64)
+
+
+def gat_cpu(indptr, indices, X, Be, w, dY1, dY2):
+    """node_mul_edge(X, Be) and vector_spmm(w, X), forward and backward, on the CPU in float32."""
+    dst, src = _edge_list(indptr, indices)
+    x = X.detach().float().requires_grad_(True)
+    be = Be.detach().float().requires_grad_(True)
+    ww = w.detach().float().requires_grad_(True)
+    y1 = (x.index_select(0, dst) * be.unsqueeze(1)).sum(-1)
+    y2 = th.zeros_like(x).index_add(0, dst, ww.unsqueeze(-1) * x.index_select(0, src))
+    th.autograd.backward([y1, y2], [dY1.float(), dY2.float()])
+    return y1.detach(), y2.detach(), x.grad, be.grad, ww.grad
+
+
+def sddmm_softmax_cpu(indptr, indices, Q, K, dP):
+    """maskedmm(Q, K) then sparse softmax per destination, forward and backward, on the CPU in float32."""
+    dst, src = _edge_list(indptr, indices)
+    q = Q.detach().float().requires_grad_(True)
+    k = K.detach().float().requires_grad_(True)
+    h = q.shape[1]
+    s = (q.index_select(0, dst) * k.index_select(0, src)).sum(-1)
+    m = th.full((q.shape[0], h), -float("inf")).scatter_reduce(0, dst.view(-1, 1).expand(-1, h), s.detach(), reduce="amax")
+    ex = th.exp(s - m.index_select(0, dst))
+    p = ex / th.zeros(q.shape[0], h).index_add(0, dst, ex).index_select(0, dst)
+    p.backward(dP.float())
+    return p.detach(), q.grad, k.grad
+
+
+def time_workload(ops, g, h, d, seed=1):
+    """Seconds of one forward + backward of the named op group on graph `g`."""
+    gen = th.Generator().manual_seed(seed)
+    r = lambda *s: th.randn(*s, generator=gen)
+    n, m, e = g.n_dst, g.n_src, g.n_edges
+    if ops == "attention":
+        return time_chain(g.indptr, g.indices, r(n, h, d), r(m, h, d), r(m, h, d), d ** -0.5, r(n, h, d))
+    t0 = time.perf_counter()
+    if ops == "gat":
+        gat_cpu(g.indptr, g.indices, r(n, h, d), r(e, d), th.rand(e, h, generator=gen), r(e, h), r(n, h, d))
+    elif ops == "sddmm_softmax":
+        sddmm_softmax_cpu(g.indptr, g.indices, r(n, h, d) * 3, r(m, h, d) * 3, r(e, h))
+    else:
+        raise ValueError(ops)
+    return time.perf_counter() - t0
