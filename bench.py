@@ -50,6 +50,9 @@ WORKLOADS = {
     # maskedmm + sparse_softmax, forward + backward, inputs scaled by 3 (max-subtraction stress)
     "zipf_sddmm_softmax": dict(kind="zipf", n=1_000_000, total=50_000_000, heads=2, dim=64, dtype="f32",
                                ops="sddmm_softmax"),
+    # vector_spmm forward + backward on ONE graph cut by destination rows over the ranks (strong scaling):
+    # source features all-gathered forward, dy all-gathered backward
+    "rmat24_spmm": dict(kind="rmat", scale=24, edge_factor=32, heads=1, dim=128, dtype="f32", ops="sharded_spmm"),
 }
 DTYPES = {"f32": th.float32, "bf16": th.bfloat16, "f64": th.float64}
 
@@ -79,6 +82,14 @@ def describe(spec):
 
 def _nbytes(ts):
     return sum(t.numel() * t.element_size() for t in ts)
+
+
+def _pinned(t):
+    """Page-locked copy of a host tensor; the pageable tensor itself if the host refuses to pin that much."""
+    try:
+        return t.pin_memory()
+    except RuntimeError:
+        return t
 
 
 class Workload:
@@ -259,7 +270,69 @@ class SddmmSoftmaxWorkload(Workload):
         self._release(self.stage[:2])
 
 
-WORKLOAD_CLASSES = {"attention": AttentionWorkload, "gat": GatWorkload, "sddmm_softmax": SddmmSoftmaxWorkload}
+class ShardedSpmmWorkload:
+    """vector_spmm forward + backward over a graph row-partitioned across the ranks (sharding.py).
+    Every rank generates the same seeded graph and keeps its own shard."""
+    name = "vector_spmm forward + backward, destination rows sharded over the ranks"
+    resident = "graph shard and edge weights; e2e copies this rank's x shard and dy rows in, y rows and dx rows out"
+    scaling = "strong"
+
+    def __init__(self, spec, rank, dev, world):
+        from custom_op_benchmark_b200 import sharding
+        self.spec, self.dev, self.world, self.rank = spec, dev, world, rank
+        self.h, self.d, self.dtype = spec["heads"], spec["dim"], DTYPES[spec["dtype"]]
+        g = make_graph(spec, seed=0, device=dev)          # the same graph on every rank
+        self.e, self.n_dst, self.n_src = g.n_edges, g.n_dst, g.n_src
+        self.sh = sh = sharding.shard_graph(g, rank, world, chunk_size=32)
+        del g
+        th.cuda.empty_cache()
+        gen = th.Generator(device=dev).manual_seed(7)     # edge weights by global edge id, same on every rank
+        self.w_all = th.rand(self.e, generator=gen, device=dev)
+        lo = sh.edge_lo
+        self.w_local = self.w_all[lo:lo + sh.indices.numel()].contiguous()
+        xb = sharding.even_bounds(self.n_src, world)
+        rows_x = int(xb[rank + 1] - xb[rank])
+        hgen = th.Generator().manual_seed(1000 + rank)
+        self.host = [_pinned(th.randn(rows_x, self.d, generator=hgen)), _pinned(th.randn(sh.rows, self.d, generator=hgen))]
+        self.x_shard, self.dy_local = (t.to(dev) for t in self.host)
+        self.stage = [th.empty_like(self.x_shard), th.empty_like(self.dy_local)]
+        self.outs = [_pinned(th.empty(sh.rows, self.d)), _pinned(th.empty(sh.cols, self.d))]
+        s, i = 4, 4
+        e_loc, e_t = sh.indices.numel(), sh.eid_t.numel()
+        F = lambda n: n * self.h * self.d * s
+        # per rank: gathered source rows read once, owned rows written once, weights, indices
+        self.alg = {"aggregate": F(self.n_src) + F(sh.rows) + e_loc * s + (e_loc + sh.rows + 1) * i,
+                    "edge_dot": F(self.n_src) + F(sh.rows) + e_loc * s + (e_loc + sh.rows + 1) * i}
+        self.alg_step = (F(self.n_src) + F(sh.rows) + e_loc * s + (e_loc + sh.rows + 1) * i) + \
+                        (F(self.n_src) + F(self.n_dst) + F(sh.rows) + F(sh.cols) + 2 * e_loc * s + e_t * s +
+                         (e_loc + e_t + sh.rows + sh.cols + 2) * i + e_t * i)
+
+    def units(self):
+        return float(self.sh.indices.numel()) * self.h   # this rank's edges: the sum over ranks is E * H
+
+    def forward(self):
+        from custom_op_benchmark_b200 import sharding
+        self.y, self.x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, self.x_shard)
+
+    def backward(self):
+        from custom_op_benchmark_b200 import sharding
+        return sharding.sharded_spmm_backward(self.sh, self.w_local, self.dy_local, self.x_all, self.w_all)
+
+    def e2e_step(self):
+        from custom_op_benchmark_b200 import sharding
+        x = self.stage[0].copy_(self.host[0], non_blocking=True)
+        dy = self.stage[1].copy_(self.host[1], non_blocking=True)
+        y, x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, x)
+        _, dx = sharding.sharded_spmm_backward(self.sh, self.w_local, dy, x_all, self.w_all)
+        self.outs[0].copy_(y, non_blocking=True)
+        self.outs[1].copy_(dx, non_blocking=True)
+
+    def e2e_bytes(self):
+        return _nbytes(self.host), _nbytes(self.outs)
+
+
+WORKLOAD_CLASSES = {"attention": AttentionWorkload, "gat": GatWorkload, "sddmm_softmax": SddmmSoftmaxWorkload,
+                    "sharded_spmm": ShardedSpmmWorkload}
 
 
 # --------------------------------------------------------------------------------------------
@@ -336,13 +409,18 @@ def run_gpu(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=th.device("cuda", local))
     dev = th.device("cuda", local)
     th.cuda.set_device(dev)
     spec = dict(WORKLOADS[args.workload])
     if args.scale and spec["kind"] == "rmat":
         spec["scale"] = args.scale
-    wl = WORKLOAD_CLASSES[spec["ops"]](spec, rank, dev)
+    if spec["ops"] == "sharded_spmm":
+        wl = ShardedSpmmWorkload(spec, rank, dev, world)
+    else:
+        wl = WORKLOAD_CLASSES[spec["ops"]](spec, rank, dev)
     lib = _capi.lib()
 
     def step_device():
@@ -448,11 +526,12 @@ def run_gpu(args):
         out = {
             "metric": METRIC, "value": units / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": spec["dtype"],
-            "data": "synthetic",
+            "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None,
+            "dtype": spec["dtype"], "data": "synthetic",
             "config": {"workload": args.workload, "ops": wl.name, "graph": describe(spec), "nodes": wl.n_dst,
                        "edges": wl.e, "heads": wl.h, "dim": wl.d,
-                       "index": "int32 CSR, chunk tables of partition_csr(32)", "per_rank": "own graph",
+                       "index": "int32 CSR, chunk tables of partition_csr(32)",
+                       "per_rank": "a row shard of one graph" if spec["ops"] == "sharded_spmm" else "own graph",
                        "l2": "inputs (%.2f GB) %s the 126 MB L2" % (
                            in_bytes / 1e9, "larger than" if in_bytes > 2 * 126e6 else "NOT larger than"),
                        "resident": wl.resident},

@@ -102,10 +102,9 @@ def all_gather_rows(local, bounds, group=None):
     parts = bounds.numel() - 1
     counts = (bounds[1:] - bounds[:-1]).tolist()
     total = int(bounds[-1])
-    out = th.empty((total,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     if parts == 1:
-        out.copy_(local)
-        return out
+        return local
+    out = th.empty((total,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     if len(set(counts)) == 1:
         dist.all_gather_into_tensor(out, local.contiguous(), group=group)
         return out
