@@ -670,7 +670,8 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
   Arena ar(ws, wsb);
   const int HD = H * D;
   const int tile0 = pick_tile(E);
-  A* delta = (A*)ar.take((size_t)n_dst * H * sizeof(A));  // survives both passes
+  const int Hp = stat_heads(H, (int)sizeof(A));
+  StatPair<A>* stat = (StatPair<A>*)ar.take((size_t)n_dst * Hp * sizeof(StatPair<A>));  // survives both passes
   const size_t mark = ar.used;
   {
     GraphView g;
@@ -682,9 +683,9 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
         constexpr int LPH = decltype(Lc)::value;
         auto generic = [&](void* cout, void* cin) {
           AttnBwdDstStaged<T, V, R, LPH> op;
-          op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.delta = delta;
+          op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.stat = stat;
           op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
-          op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+          op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
           return op;
         };
         return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, generic);
@@ -701,9 +702,9 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
       constexpr int LPH = decltype(Lc)::value;
       auto generic = [&](void* cout, void* cin) {
         AttnBwdSrcStaged<T, V, R, LPH> op;
-        op.q = q; op.k = k; op.v = v; op.dout = dout; op.lse = (const A*)lse; op.delta = delta; op.dk = dk;
+        op.q = q; op.k = k; op.v = v; op.dout = dout; op.stat = stat; op.dk = dk;
         op.dv = dv; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
-        op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+        op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
         return op;
       };
       return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, generic);

@@ -399,6 +399,12 @@ struct AttnFwdOp {
 // which is sparse_softmax backward (graphop_kernel.cu:214-228) composed with the dA half of
 // maskedmm backward (:105-110), probabilities recomputed instead of stored.  delta is also
 // written out for the source-side pass.
+// (lse, delta) of one (destination node, head), written side by side by the destination pass so that the
+// source pass fetches both with one load.  Rows hold `stat_heads(H)` pairs: H rounded up so that a row is
+// a whole number of 16-byte pieces.
+template <typename A> struct alignas(2 * sizeof(A)) StatPair { A lse, delta; };
+__host__ __device__ constexpr int stat_heads(int H, int acc_bytes) { return acc_bytes >= 8 ? H : ((H + 1) & ~1); }
+
 // ---------------------------------------------------------------------------------------
 template <typename T, int V, int R>
 struct AttnBwdDstOp {
@@ -412,12 +418,12 @@ struct AttnBwdDstOp {
   const T* __restrict__ o;
   const T* __restrict__ dout;
   const A* __restrict__ lse;
-  A* __restrict__ delta;     // (n_dst, H) out
+  StatPair<A>* __restrict__ stat;  // (n_dst, Hp) out: lse copied, delta computed; Hp = stat_heads(H)
   T* __restrict__ dq;        // (n_dst, H, D) out
   A* __restrict__ carry;     // (2 * n_tiles, HD) partials written by this level
   const A* carry_in;         // partials of the level below (carry levels only)
   A scale;
-  int H, D, HD, S, lph;
+  int H, Hp, D, HD, S, lph;
 
   struct State { SlotMap<R> sm; A q[R][V]; A g[R][V]; A acc[R][V]; A lse[R]; A delta[R]; };
   struct Fetched { A k[R][V]; A v[R][V]; };
@@ -447,7 +453,7 @@ struct AttnBwdDstOp {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       st.delta[i] = dl[i];
-      if (st.sm.ok[i] && st.sm.efeat[i] == 0) delta[(long long)node * H + st.sm.head[i]] = dl[i];
+      if (st.sm.ok[i] && st.sm.efeat[i] == 0) stat[(long long)node * Hp + st.sm.head[i]] = StatPair<A>{st.lse[i], dl[i]};
     }
   }
   __device__ __forceinline__ void fetch(const State& st, Fetched& f, int c, int, int) const {
@@ -525,8 +531,8 @@ struct AttnBwdDstOp {
     for (int e = 0; e < V; ++e) z[e] = A(0);
     const long long n = (hi - lo) * S;
     for (long long kk = lane; kk < n; kk += 32) store_acc<T, V>(dq + lo * HD + kk * V, z);
-    const long long nl = (hi - lo) * H;
-    for (long long kk = lane; kk < nl; kk += 32) delta[lo * H + kk] = A(0);
+    const long long nl = (hi - lo) * Hp;
+    for (long long kk = lane; kk < nl; kk += 32) stat[lo * Hp + kk] = StatPair<A>{A(0), A(0)};
   }
 };
 
@@ -547,14 +553,13 @@ struct AttnBwdSrcOp {
   const T* __restrict__ k;
   const T* __restrict__ v;
   const T* __restrict__ dout;
-  const A* __restrict__ lse;
-  const A* __restrict__ delta;
+  const StatPair<A>* __restrict__ stat;  // (n_dst, Hp) from the destination pass
   T* __restrict__ dk;
   T* __restrict__ dv;
   A* __restrict__ carry;     // (2 * n_tiles, 2 * HD): dk partial then dv partial, written by this level
   const A* carry_in;         // partials of the level below (carry levels only)
   A scale;
-  int H, D, HD, S, lph;
+  int H, Hp, D, HD, S, lph;
 
   struct State { SlotMap<R> sm; A k[R][V]; A v[R][V]; A ak[R][V]; A av[R][V]; };
   struct Fetched { A q[R][V]; A g[R][V]; A lse[R]; A delta[R]; };
@@ -578,8 +583,9 @@ struct AttnBwdSrcOp {
       if (st.sm.ok[i]) {
         load_acc<T, V>(f.q[i], q + (long long)c * HD + st.sm.feat[i]);
         load_acc<T, V>(f.g[i], dout + (long long)c * HD + st.sm.feat[i]);
-        f.lse[i] = __ldg(lse + (long long)c * H + st.sm.head[i]);
-        f.delta[i] = __ldg(delta + (long long)c * H + st.sm.head[i]);
+        const StatPair<A> pr = stat[(long long)c * Hp + st.sm.head[i]];
+        f.lse[i] = pr.lse;
+        f.delta[i] = pr.delta;
       } else {
         f.lse[i] = A(0);
         f.delta[i] = A(0);

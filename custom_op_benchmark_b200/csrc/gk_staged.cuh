@@ -11,8 +11,9 @@
 //     positions belong to the same node;
 //   * up to kBatch consecutive edges of one node are folded together, which gives the
 //     scheduler kBatch independent dot-product / shuffle chains instead of one.
-// A lane only ever reads back the bytes it copied itself, so no barrier is needed between the
-// asynchronous copies and their use beyond cp.async.wait_group.
+// A lane reads back the bytes it copied itself, so no barrier is needed between the asynchronous
+// copies and their use beyond cp.async.wait_group (ops that share entry bytes between lanes say so
+// and get a warp barrier, see SharesEntries).
 #pragma once
 #include <type_traits>
 
@@ -24,6 +25,9 @@
 #endif
 #ifndef GK_TUNE_TILE
 #define GK_TUNE_TILE 256        // largest level-0 tile of the staged walker
+#endif
+#ifndef GK_TUNE_BATCH_MAX
+#define GK_TUNE_BATCH_MAX 8     // most edges of one node folded together
 #endif
 
 namespace gk {
@@ -86,6 +90,12 @@ __host__ __device__ constexpr size_t staged_warp_bytes(int tile) {
   return (((size_t)(tile + kMetaPad) * (Op::kUsesEid ? 13 : 9)) + 15) / 16 * 16 + (size_t)Op::kDepth * Op::kEdgeBytes;
 }
 
+// Ops whose lanes read ring bytes copied by other lanes declare `kSharedEntry = true`; the walker
+// then puts a warp barrier between the copies' completion and the reads, and between the reads and
+// the refill.  Every other op reads back only the bytes the same lane copied and needs neither.
+template <class Op, class = void> struct SharesEntries : std::false_type {};
+template <class Op> struct SharesEntries<Op, std::void_t<decltype(Op::kSharedEntry)>> : std::true_type {};
+
 template <class Op>
 __global__ void __launch_bounds__(Op::kWarps * 32, Op::kMinCtas)
 walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ erow,
@@ -95,6 +105,7 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
   constexpr int DEPTH = Op::kDepth;
   constexpr int EB = Op::kEdgeBytes;
   constexpr bool kOut = Op::kRowOut;
+  constexpr bool kShared = SharesEntries<Op>::value;
   static_assert((DEPTH & (DEPTH - 1)) == 0 && DEPTH >= U && U <= 32, "ring depth: a power of two >= batch");
   extern __shared__ uint4 gk_smem[];
   const int lane = threadIdx.x & 31;
@@ -214,14 +225,17 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
       cur = r;
     }
     cp_async_wait<DEPTH - U>();
+    if constexpr (kShared) __syncwarp();  // every lane's copies of these entries have landed
     if (rem >= U) {  // the common case: a full batch of one node's edges
       if (r >= 0) op.template consume_batch<true>(st, ring, i, U, Op::kUsesEid ? m_eid + i : nullptr, lane);
+      if constexpr (kShared) __syncwarp();  // all lanes have read the entries about to be refilled
 #pragma unroll
       for (int u = 0; u < U; ++u) issue(i + u + DEPTH);
       new_seg = rem == U;
       i += U;
     } else {
       if (r >= 0) op.template consume_batch<false>(st, ring, i, rem, Op::kUsesEid ? m_eid + i : nullptr, lane);
+      if constexpr (kShared) __syncwarp();
       for (int u = 0; u < rem; ++u) issue(i + u + DEPTH);
       new_seg = true;
       i += rem;
@@ -262,7 +276,8 @@ constexpr int pick_depth(int edge_bytes, int min_ctas, bool uses_eid) {
 }
 // Edges folded together; at most half the ring, so that the other half is in flight meanwhile.
 constexpr int pick_batch(int r, int depth) {
-  const int b = r == 1 ? 8 : (r == 2 ? 4 : 2);
+  const int b0 = r == 1 ? 8 : (r == 2 ? 4 : 2);
+  const int b = b0 < GK_TUNE_BATCH_MAX ? b0 : GK_TUNE_BATCH_MAX;
   const int half = depth / 2 > 1 ? depth / 2 : 1;
   return b < half ? b : half;
 }
@@ -589,7 +604,8 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         st.delta[i] = dl[i];
-        if (st.sm.ok[i] && st.sm.efeat[i] == 0) this->delta[(long long)node * this->H + st.sm.head[i]] = dl[i];
+        if (st.sm.ok[i] && st.sm.efeat[i] == 0)
+          this->stat[(long long)node * this->Hp + st.sm.head[i]] = StatPair<A>{st.lsen[i], dl[i]};
       }
       return;
     }
@@ -611,31 +627,30 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
                                                 int lane) const {
-    A s[kBatch][R], dp[kBatch][R];
+    // the k rows stay in registers between the dot product and the update: one shared-memory
+    // read per staged byte
+    A s[kBatch][R], dp[kBatch][R], kv[kBatch][R][V];
     GK_BATCH_LOOP(u) {
       const unsigned char* entry = GK_RING_ENTRY(i0 + u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        A kv[V], vv[V];
-        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
+        A vv[V];
+        lds_acc<T, V>(kv[u][i], entry + (lane + 32 * i) * 16);
         lds_acc<T, V>(vv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
         s[u][i] = A(0);
         dp[u][i] = A(0);
 #pragma unroll
-        for (int e = 0; e < V; ++e) { s[u][i] += st.q[i][e] * kv[e]; dp[u][i] += st.g[i][e] * vv[e]; }
+        for (int e = 0; e < V; ++e) { s[u][i] += st.q[i][e] * kv[u][i][e]; dp[u][i] += st.g[i][e] * vv[e]; }
       }
     }
     GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const A p = gk_exp2(s[u][i] - st.lse[i]);
         const A ds = p * (dp[u][i] - st.delta[i]) * this->scale;
-        A kv[V];
-        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
 #pragma unroll
-        for (int e = 0; e < V; ++e) st.acc[i][e] += ds * kv[e];
+        for (int e = 0; e < V; ++e) st.acc[i][e] += ds * kv[u][i][e];
       }
     }
   }
@@ -654,6 +669,7 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = false;
+  static constexpr bool kSharedEntry = true;  // lanes read pair bytes that other lanes copied
 
   __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
@@ -687,45 +703,45 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
       for (int e = 0; e < V; ++e) st.k[i][e] *= c;
   }
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
-    A* sc = reinterpret_cast<A*>(entry + 2 * Ring::kRowBytes);
+    // the node's (lse, delta) pairs: Hp pairs = `pieces` copies of 16 bytes, one per low lane
+    const unsigned char* pairs = reinterpret_cast<const unsigned char*>(this->stat + (long long)c * this->Hp);
+    const int pieces = this->Hp * (int)sizeof(StatPair<A>) / 16;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       cp_async16(entry + (lane + 32 * i) * 16, this->q + (long long)c * this->HD + st.sm.feat[i]);
       cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->dout + (long long)c * this->HD + st.sm.feat[i]);
-      cp_async_small<sizeof(A)>(sc + lane + 32 * i, this->lse + (long long)c * this->H + st.sm.head[i]);
-      cp_async_small<sizeof(A)>(sc + 32 * R + lane + 32 * i, this->delta + (long long)c * this->H + st.sm.head[i]);
+      const int piece = lane + 32 * i;
+      if (piece < pieces) cp_async16(entry + 2 * Ring::kRowBytes + piece * 16, pairs + piece * 16);
     }
   }
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
                                                 int lane) const {
-    A s[kBatch][R], dp[kBatch][R];
+    // the q and dout rows stay in registers between the dot products and the updates: one
+    // shared-memory read per staged byte
+    A s[kBatch][R], dp[kBatch][R], qv[kBatch][R][V], gv[kBatch][R][V];
     GK_BATCH_LOOP(u) {
       const unsigned char* entry = GK_RING_ENTRY(i0 + u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        A qv[V], gv[V];
-        lds_acc<T, V>(qv, entry + (lane + 32 * i) * 16);
-        lds_acc<T, V>(gv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+        lds_acc<T, V>(qv[u][i], entry + (lane + 32 * i) * 16);
+        lds_acc<T, V>(gv[u][i], entry + Ring::kRowBytes + (lane + 32 * i) * 16);
         s[u][i] = A(0);
         dp[u][i] = A(0);
 #pragma unroll
-        for (int e = 0; e < V; ++e) { s[u][i] += qv[e] * st.k[i][e]; dp[u][i] += gv[e] * st.v[i][e]; }
+        for (int e = 0; e < V; ++e) { s[u][i] += qv[u][i][e] * st.k[i][e]; dp[u][i] += gv[u][i][e] * st.v[i][e]; }
       }
     }
     GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
-      const A* sc = reinterpret_cast<const A*>(entry + 2 * Ring::kRowBytes);
+      const StatPair<A>* sc = reinterpret_cast<const StatPair<A>*>(GK_RING_ENTRY(i0 + u) + 2 * Ring::kRowBytes);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        const A p = gk_exp2(s[u][i] - sc[lane + 32 * i] * A(kLog2e));
-        const A ds = p * (dp[u][i] - sc[32 * R + lane + 32 * i]) * this->scale;
-        A qv[V], gv[V];
-        lds_acc<T, V>(qv, entry + (lane + 32 * i) * 16);
-        lds_acc<T, V>(gv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+        const StatPair<A> pr = sc[st.sm.head[i]];
+        const A p = gk_exp2(s[u][i] - pr.lse * A(kLog2e));
+        const A ds = p * (dp[u][i] - pr.delta) * this->scale;
 #pragma unroll
-        for (int e = 0; e < V; ++e) { st.av[i][e] += p * gv[e]; st.ak[i][e] += ds * qv[e]; }
+        for (int e = 0; e < V; ++e) { st.av[i][e] += p * gv[u][i][e]; st.ak[i][e] += ds * qv[u][i][e]; }
       }
     }
   }
