@@ -327,6 +327,7 @@ inline int run_aggregate(Arena& ar, const GraphView& g, const T* w, const T* x, 
         OpT op;
         op.w = w; op.x = x; op.y = y; op.carry = (A*)cout; op.carry_in = (const A*)cin;
         op.H = H; op.D = D; op.HD = HD; op.S = b.S; op.feat0 = feat0;
+        if constexpr (IsStaged<OpT>::value) op.wmode = OpT::pick_wmode(w, H, feat0, HD, block_elems);
         return op;
       });
     })));

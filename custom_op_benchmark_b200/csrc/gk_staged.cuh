@@ -21,8 +21,11 @@
 
 // Build-time tunables.
 #ifndef GK_TUNE_CTAS_NARROW
-#define GK_TUNE_CTAS_NARROW 3   // resident blocks per SM aimed at when a node row fits one slot per lane
+#define GK_TUNE_CTAS_NARROW 4   // resident blocks per SM aimed at when a node row fits one slot per lane
 #endif
+#ifndef GK_TUNE_CTAS_SRC
+#define GK_TUNE_CTAS_SRC 3      // the same for the attention backward over the transposed CSR: it keeps two
+#endif                          // accumulator rows and two resident rows, which 64 registers do not hold
 #ifndef GK_TUNE_TILE
 #define GK_TUNE_TILE 256        // largest level-0 tile of the staged walker
 #endif
@@ -282,13 +285,16 @@ constexpr int pick_batch(int r, int depth) {
   return b < half ? b : half;
 }
 
-template <typename T, int R, int kOperands, int kScalars, bool kEid>
+template <typename T, int R, int kOperands, int kScalars, bool kEid, int kCtasNarrow = GK_TUNE_CTAS_NARROW>
 struct RingShape {
   using A = typename AccOf<T>::type;
   static constexpr int kRowBytes = 32 * R * 16;
   static constexpr int kScalarBytes = 32 * R * (int)sizeof(A);
   static constexpr int kEdgeBytes = kOperands * kRowBytes + kScalars * kScalarBytes;
-  static constexpr int kMinCtas = R == 1 ? GK_TUNE_CTAS_NARROW : (R == 2 ? 2 : 1);
+  // 4-byte elements: 16 bytes of accumulator per slot, 64 registers are enough; 2-byte elements
+  // (8 accumulators per slot) and doubles need the 80 registers of 3 resident blocks
+  static constexpr int kMinCtas = R == 1 ? (sizeof(T) == 4 ? kCtasNarrow : (kCtasNarrow < 3 ? kCtasNarrow : 3))
+                                         : (R == 2 ? 2 : 1);
   static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, kEid);
   static constexpr int kBatch = pick_batch(R, kDepth);
 };
@@ -327,21 +333,50 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   static constexpr int kMinCtas = Ring::kMinCtas;
   static constexpr int kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = true;
+  static constexpr bool kSharedEntry = true;  // in the packed modes lanes read weights that other lanes copied
   static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, true);
   static constexpr int kBatch = pick_batch(R, kDepth);
+  // How an edge's H weights reach the ring entry (set by the host):
+  //   kWeightsPerLane  every lane copies the word of its own head (any H, any element size);
+  //   kWeightsWords    lane j < H copies weight j, lanes read the weight of their head (4- and 8-byte
+  //                    elements, H <= 32 * R);
+  //   kWeightsPieces   the H weights travel as 16-byte pieces copied by the first lanes (the weight
+  //                    row is a whole number of aligned 16-byte pieces).
+  // One scattered copy per edge instead of one per lane is what the packed modes buy.
+  enum { kWeightsPerLane = 0, kWeightsWords = 1, kWeightsPieces = 2 };
+  int wmode = kWeightsPerLane;
+
+  __host__ static int pick_wmode(const void* w, int H, int feat0, int HD, int block_elems) {
+    const bool whole = feat0 == 0 && HD <= block_elems && H <= 32 * R;  // one feature block sees every head
+    if (!whole) return kWeightsPerLane;
+    if ((H * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) return kWeightsPieces;
+    return sizeof(T) >= 4 ? kWeightsWords : kWeightsPerLane;
+  }
 
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
+    const unsigned char* wrow = reinterpret_cast<const unsigned char*>(this->w + (long long)e * this->H);
+    const int wbytes = this->H * (int)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const T* src = kEdgeFeat ? this->x + (long long)e * this->D + st.sm.efeat[i]
                                : this->x + (long long)c * this->HD + st.sm.feat[i];
       cp_async16(entry + (lane + 32 * i) * 16, src);
-      const T* wsrc = this->w + (long long)e * this->H + st.sm.head[i];
-      WWord* wdst = reinterpret_cast<WWord*>(entry + Ring::kRowBytes) + lane + 32 * i;
-      if constexpr (sizeof(T) == 2)
-        cp_async_small<4>(wdst, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(wsrc) & ~uintptr_t(3)));
-      else
-        cp_async_small<sizeof(T)>(wdst, wsrc);
+      const int j = lane + 32 * i;
+      if (wmode == kWeightsPieces) {
+        if (j * 16 < wbytes) cp_async16(entry + Ring::kRowBytes + j * 16, wrow + j * 16);
+      } else if (wmode == kWeightsWords) {
+        if constexpr (sizeof(T) >= 4) {
+          if (j < this->H)
+            cp_async_small<sizeof(T)>(entry + Ring::kRowBytes + j * sizeof(T), wrow + j * sizeof(T));
+        }
+      } else {
+        const T* wsrc = this->w + (long long)e * this->H + st.sm.head[i];
+        WWord* wdst = reinterpret_cast<WWord*>(entry + Ring::kRowBytes) + lane + 32 * i;
+        if constexpr (sizeof(T) == 2)
+          cp_async_small<4>(wdst, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(wsrc) & ~uintptr_t(3)));
+        else
+          cp_async_small<sizeof(T)>(wdst, wsrc);
+      }
     }
   }
   __device__ __forceinline__ void prefetch_node(State&, int, int) const {}
@@ -354,16 +389,18 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
       for (int i = 0; i < R; ++i) {
         A xv[V];
         lds_acc<T, V>(xv, entry + (lane + 32 * i) * 16);
-        const WWord word = reinterpret_cast<const WWord*>(entry + Ring::kRowBytes)[lane + 32 * i];
         A wv;
-        if constexpr (sizeof(T) == 2) {
+        if (wmode != kWeightsPerLane) {
+          wv = to_acc<T>(reinterpret_cast<const T*>(entry + Ring::kRowBytes)[st.sm.head[i]]);
+        } else if constexpr (sizeof(T) == 2) {
+          const WWord word = reinterpret_cast<const WWord*>(entry + Ring::kRowBytes)[lane + 32 * i];
           const bool hi = (((long long)eids[u] * this->H + st.sm.head[i]) & 1) != 0;
           union { uint16_t b; T t; } cvt;
           cvt.b = (uint16_t)(hi ? (word >> 16) : (word & 0xffffu));
           wv = to_acc<T>(cvt.t);
         } else {
           union { WWord wd; T t; } cvt;
-          cvt.wd = word;
+          cvt.wd = reinterpret_cast<const WWord*>(entry + Ring::kRowBytes)[lane + 32 * i];
           wv = to_acc<T>(cvt.t);
         }
 #pragma unroll
@@ -381,6 +418,9 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
   using Base = EdgeDotOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
   struct State : Base::State { A an[R][V]; int next_node; };
+  // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
+  // the registers for the node being processed
+  static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
   using Ring = RingShape<T, R, 1, 0, true>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
@@ -388,12 +428,13 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
 
   __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+    if constexpr (!kPrefetch) return;
 #pragma unroll
     for (int i = 0; i < R; ++i) load_acc<T, V>(st.an[i], this->a + (long long)node * this->HD + st.sm.feat[i]);
     st.next_node = node;
   }
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
-    if (st.next_node == node) {
+    if (kPrefetch && st.next_node == node) {
 #pragma unroll
       for (int i = 0; i < R; ++i)
 #pragma unroll
@@ -450,6 +491,9 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
   using Base = AttnFwdOp<T, V, R>;
   using A = typename Base::A;
   struct State : Base::State { A qn[R][V]; int next_node; };
+  // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
+  // the registers for the node being processed
+  static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
   using CarryIn = typename Base::CarryIn;
   using Ring = RingShape<T, R, 2, 0, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
@@ -458,13 +502,14 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
 
   __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+    if constexpr (!kPrefetch) return;
 #pragma unroll
     for (int i = 0; i < R; ++i) load_acc<T, V>(st.qn[i], this->q + (long long)node * this->HD + st.sm.feat[i]);
     st.next_node = node;
   }
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
     const A c = this->scale * A(kLog2e);
-    if (st.next_node == node) {
+    if (kPrefetch && st.next_node == node) {
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         st.m[i] = neg_inf<A>();
@@ -566,6 +611,9 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   using Base = AttnBwdDstOp<T, V, R>;
   using A = typename Base::A;
   struct State : Base::State { A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node; };
+  // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
+  // the registers for the node being processed
+  static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
   using Ring = RingShape<T, R, 2, 0, false>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
@@ -573,6 +621,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
 
   __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+    if constexpr (!kPrefetch) return;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const long long off = (long long)node * this->HD + st.sm.feat[i];
@@ -586,7 +635,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   // q scaled to base-2 score units, lse converted to base 2
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
     const A c = this->scale * A(kLog2e);
-    if (st.next_node == node) {
+    if (kPrefetch && st.next_node == node) {
       A dl[R];
 #pragma unroll
       for (int i = 0; i < R; ++i) {
@@ -627,30 +676,32 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
                                                 int lane) const {
-    // the k rows stay in registers between the dot product and the update: one shared-memory
-    // read per staged byte
-    A s[kBatch][R], dp[kBatch][R], kv[kBatch][R][V];
+    A s[kBatch][R], dp[kBatch][R];
     GK_BATCH_LOOP(u) {
       const unsigned char* entry = GK_RING_ENTRY(i0 + u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        A vv[V];
-        lds_acc<T, V>(kv[u][i], entry + (lane + 32 * i) * 16);
+        A kv[V], vv[V];
+        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
         lds_acc<T, V>(vv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
         s[u][i] = A(0);
         dp[u][i] = A(0);
 #pragma unroll
-        for (int e = 0; e < V; ++e) { s[u][i] += st.q[i][e] * kv[u][i][e]; dp[u][i] += st.g[i][e] * vv[e]; }
+        for (int e = 0; e < V; ++e) { s[u][i] += st.q[i][e] * kv[e]; dp[u][i] += st.g[i][e] * vv[e]; }
       }
     }
     GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
+    // the k row is read again rather than kept: registers matter more than the second read
     GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const A p = gk_exp2(s[u][i] - st.lse[i]);
         const A ds = p * (dp[u][i] - st.delta[i]) * this->scale;
+        A kv[V];
+        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
 #pragma unroll
-        for (int e = 0; e < V; ++e) st.acc[i][e] += ds * kv[u][i][e];
+        for (int e = 0; e < V; ++e) st.acc[i][e] += ds * kv[e];
       }
     }
   }
@@ -665,14 +716,24 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   using Base = AttnBwdSrcOp<T, V, R>;
   using A = typename Base::A;
   struct State : Base::State { A kn[R][V]; A vn[R][V]; int next_node; };
-  using Ring = RingShape<T, R, 2, 2, false>;
-  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
-                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
+  // the registers for the node being processed
+  static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
+  using Ring = RingShape<T, R, 2, 0, false, GK_TUNE_CTAS_SRC>;
+  // (lse, delta) pairs of the most heads this instantiation can see: 32 * R / LPH (every head when the
+  // lanes per head are only known at run time), at least one 16-byte piece
+  static constexpr int kMaxHeads = LPH ? (32 * R / LPH > 2 ? 32 * R / LPH : 2) : 32 * R;
+  static constexpr int kPairBytes = (kMaxHeads * (int)sizeof(StatPair<A>) + 15) / 16 * 16;
+  static constexpr int kEdgeBytes = 2 * Ring::kRowBytes + kPairBytes;
+  static constexpr int kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, false);
+  static constexpr int kBatch = pick_batch(R, kDepth);
   static constexpr bool kUsesEid = false;
   static constexpr bool kSharedEntry = true;  // lanes read pair bytes that other lanes copied
 
   __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
+    if constexpr (!kPrefetch) return;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const long long off = (long long)node * this->HD + st.sm.feat[i];
@@ -684,7 +745,7 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   // k scaled to base-2 score units
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
     const A c = this->scale * A(kLog2e);
-    if (st.next_node == node) {
+    if (kPrefetch && st.next_node == node) {
 #pragma unroll
       for (int i = 0; i < R; ++i)
 #pragma unroll
@@ -717,31 +778,35 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
                                                 int lane) const {
-    // the q and dout rows stay in registers between the dot products and the updates: one
-    // shared-memory read per staged byte
-    A s[kBatch][R], dp[kBatch][R], qv[kBatch][R][V], gv[kBatch][R][V];
+    A s[kBatch][R], dp[kBatch][R];
     GK_BATCH_LOOP(u) {
       const unsigned char* entry = GK_RING_ENTRY(i0 + u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        lds_acc<T, V>(qv[u][i], entry + (lane + 32 * i) * 16);
-        lds_acc<T, V>(gv[u][i], entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+        A qv[V], gv[V];
+        lds_acc<T, V>(qv, entry + (lane + 32 * i) * 16);
+        lds_acc<T, V>(gv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
         s[u][i] = A(0);
         dp[u][i] = A(0);
 #pragma unroll
-        for (int e = 0; e < V; ++e) { s[u][i] += qv[u][i][e] * st.k[i][e]; dp[u][i] += gv[u][i][e] * st.v[i][e]; }
+        for (int e = 0; e < V; ++e) { s[u][i] += qv[e] * st.k[i][e]; dp[u][i] += gv[e] * st.v[i][e]; }
       }
     }
     GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
+    // the q and dout rows are read again rather than kept: registers matter more than the second read
     GK_BATCH_LOOP(u) {
-      const StatPair<A>* sc = reinterpret_cast<const StatPair<A>*>(GK_RING_ENTRY(i0 + u) + 2 * Ring::kRowBytes);
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const StatPair<A>* sc = reinterpret_cast<const StatPair<A>*>(entry + 2 * Ring::kRowBytes);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const StatPair<A> pr = sc[st.sm.head[i]];
         const A p = gk_exp2(s[u][i] - pr.lse * A(kLog2e));
         const A ds = p * (dp[u][i] - pr.delta) * this->scale;
+        A qv[V], gv[V];
+        lds_acc<T, V>(qv, entry + (lane + 32 * i) * 16);
+        lds_acc<T, V>(gv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
 #pragma unroll
-        for (int e = 0; e < V; ++e) { st.av[i][e] += p * gv[u][i][e]; st.ak[i][e] += ds * qv[u][i][e]; }
+        for (int e = 0; e < V; ++e) { st.av[i][e] += p * gv[e]; st.ak[i][e] += ds * qv[e]; }
       }
     }
   }
