@@ -129,6 +129,38 @@ class Workload:
     def e2e_bytes(self):
         return _nbytes(self.host), _nbytes(self.outs)
 
+    def gather_streams(self):
+        """{kernel name: (int32 index stream, table, table or None)}: what each walker kernel gathers per edge."""
+        return {}
+
+    def gather_floor(self, lib, reps=5):
+        """Milliseconds of graphop_gather_probe_i32 (the gathers alone, nothing done with the rows) for every
+        kernel of gather_streams() whose rows are at most 512 bytes; {} when there is none."""
+        out = {}
+        sink = th.zeros(1, dtype=th.int32, device=self.dev)
+        stream = th.cuda.current_stream().cuda_stream
+        for name, (idx, t0, t1) in self.gather_streams().items():
+            row_bytes = t0[0].numel() * t0.element_size()
+            if idx.dtype != th.int32 or row_bytes > 512 or row_bytes % 16:
+                continue
+
+            def go():
+                rc = lib.graphop_gather_probe_i32(idx.data_ptr(), idx.numel(), t0.data_ptr(),
+                                                  t1.data_ptr() if t1 is not None else None, row_bytes,
+                                                  sink.data_ptr(), stream)
+                if rc:
+                    raise RuntimeError("graphop_gather_probe_i32 failed: %d" % rc)
+            for _ in range(3):
+                go()
+            a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                go()
+            b.record()
+            th.cuda.synchronize()
+            out[name] = a.elapsed_time(b) / reps
+        return out
+
 
 class AttentionWorkload(Workload):
     name = "fused attention forward + backward"
@@ -154,6 +186,10 @@ class AttentionWorkload(Workload):
         # every tensor once: forward 4F + I + 4NH, backward 8F + 2I + P + 4NH
         self.alg_step = (2 * z["F_dst"] + 2 * z["F_src"] + z["I"] + z["stat"]) + \
                         (4 * z["F_dst"] + 4 * z["F_src"] + z["I"] + z["I_t"] + z["P"] + z["stat"])
+
+    def gather_streams(self):
+        return {"attention_fwd": (self.R[3], self.K, self.V), "attention_bwd_dst": (self.R[3], self.K, self.V),
+                "attention_bwd_src": (self.C[3], self.Q, self.dO)}
 
     def forward(self):
         from custom_op_benchmark_b200 import graphop
@@ -505,6 +541,9 @@ def run_gpu(args):
     kernels = {k: {"launches_per_step": len(v) / prof_steps, "ms_per_step": sum(v) / prof_steps}
                for k, v in per_kernel.items()}
 
+    # -- the gathers alone, same index streams and tables (a floor for the walker kernels) ------
+    floors = wl.gather_floor(lib) if rank == 0 and hasattr(wl, "gather_floor") else {}
+
     # -- reduce over ranks ---------------------------------------------------------------------
     stats = th.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], dtype=th.float64, device=dev)
     work = th.tensor([wl.units()], dtype=th.float64, device=dev)
@@ -547,6 +586,13 @@ def run_gpu(args):
                          "step_frac": wl.alg_step / (ms_per_step * 1e-3) / 1e9 / peak},
             "kernels": kernels,
         }
+        if floors:
+            out["gather_floor"] = {
+                "what": "graphop_gather_probe_i32: one row per edge per operand read through the kernel's own index "
+                        "stream, nothing done with the rows",
+                "ms": floors,
+                "kernel_over_floor": {k: kernels[k]["ms_per_step"] / max(1.0, kernels[k]["launches_per_step"]) / v
+                                      for k, v in floors.items() if k in kernels}}
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(spec, args.cpu_sample_scale)
         print(json.dumps(out))

@@ -184,6 +184,9 @@ expand_rows_kernel(const I* __restrict__ row, const I* __restrict__ indptr, long
     if (cnt) a = below;
     if (cnt < 32) b = above;
   }
+  // 32 chunks at a time: lane l holds chunk a + l; every position of the part of the tile they cover
+  // finds its chunk by a 5-step search over the lanes' start positions, so that the stores are
+  // coalesced whatever the chunk lengths are
   for (long long c = a; c < C; c += 32) {
     const long long cc = c + lane;
     long long s = hi, e = hi;
@@ -193,24 +196,26 @@ expand_rows_kernel(const I* __restrict__ row, const I* __restrict__ indptr, long
       e = (long long)indptr[cc + 1];
       r = (int)row[cc];
     }
-    const long long raw_s = s;
-    s = s < lo ? lo : s;
-    e = e > hi ? hi : e;
-    const long long len = e > s ? e - s : 0;
-    // long pieces are written by the whole warp, short ones by their own lane
-    unsigned longmask = __ballot_sync(kFull, len >= 32);
-    if (len > 0 && len < 32)
-      for (long long p = s; p < e; ++p) erow[p] = r;
-    while (longmask) {
-      const int src = __ffs(longmask) - 1;
-      longmask &= longmask - 1;
-      const long long ss = __shfl_sync(kFull, s, src);
-      const long long ee = __shfl_sync(kFull, e, src);
-      const int rr = __shfl_sync(kFull, r, src);
-      for (long long p = ss + lane; p < ee; p += 32) erow[p] = rr;
+    const bool past = s >= hi;  // this chunk starts at or beyond the end of the tile
+    s = s < lo ? lo : (s > hi ? hi : s);
+    e = e < lo ? lo : (e > hi ? hi : e);
+    const int s_rel = (int)(s - lo);  // 0 .. kExpandTile, non-decreasing over the lanes
+    const long long from = __shfl_sync(kFull, s, 0);
+    const long long to = __shfl_sync(kFull, e, 31);
+    for (long long q = from; q < to; q += 32) {
+      const long long p = q + lane;
+      const int p_rel = (int)(p - lo);
+      int owner = 0;  // the last lane whose chunk starts at or before p
+#pragma unroll
+      for (int step = 16; step; step >>= 1) {
+        const int cand = owner + step;
+        const int start = __shfl_sync(kFull, s_rel, cand & 31);
+        if (cand < 32 && start <= p_rel) owner = cand;
+      }
+      const int rr = __shfl_sync(kFull, r, owner);
+      if (p < to) erow[p] = rr;
     }
-    // stop once some lane's chunk starts at or beyond the end of the tile
-    if (__any_sync(kFull, raw_s >= hi)) break;
+    if (__any_sync(kFull, past)) break;
   }
 }
 

@@ -50,6 +50,12 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// Address of a lane's 16 bytes of row `c`: the lane's own base pointer (row 0, its slot) plus c rows.
+// One 32 x 32 -> 64-bit multiply-add instead of a 64-bit index computation per copy.
+__device__ __forceinline__ const unsigned char* row_ptr(const unsigned char* lane_base, int c, unsigned row_bytes) {
+  return lane_base + (unsigned long long)(unsigned)c * row_bytes;
+}
+
 // 2^x.  float: the hardware approximation (relative error about 2^-22); double: exp2().
 __device__ __forceinline__ float gk_exp2(float x) {
   float y;
@@ -323,7 +329,7 @@ template <typename T, int V, int R, bool kEdgeFeat>
 struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   using Base = AggregateOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
-  using State = typename Base::State;
+  struct State : Base::State { const unsigned char* xb[R]; };
   using Ring = RingShape<T, R, 1, 0, true>;
   // weights: one 4- or 8-byte word per lane and register (2-byte elements travel as the aligned
   // 4-byte word that contains them; the word's last 2 bytes may lie past an odd-sized tensor's end,
@@ -353,14 +359,19 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
     return sizeof(T) >= 4 ? kWeightsWords : kWeightsPerLane;
   }
 
+  __device__ __forceinline__ void setup(State& st, int lane) const {
+    Base::setup(st, lane);
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      st.xb[i] = reinterpret_cast<const unsigned char*>(this->x + (kEdgeFeat ? st.sm.efeat[i] : st.sm.feat[i]));
+  }
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
-    const unsigned char* wrow = reinterpret_cast<const unsigned char*>(this->w + (long long)e * this->H);
     const int wbytes = this->H * (int)sizeof(T);
+    const unsigned char* wrow = row_ptr(reinterpret_cast<const unsigned char*>(this->w), e, (unsigned)wbytes);
+    const unsigned rowb = (unsigned)(kEdgeFeat ? this->D : this->HD) * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const T* src = kEdgeFeat ? this->x + (long long)e * this->D + st.sm.efeat[i]
-                               : this->x + (long long)c * this->HD + st.sm.feat[i];
-      cp_async16(entry + (lane + 32 * i) * 16, src);
+      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.xb[i], kEdgeFeat ? e : c, rowb));
       const int j = lane + 32 * i;
       if (wmode == kWeightsPieces) {
         if (j * 16 < wbytes) cp_async16(entry + Ring::kRowBytes + j * 16, wrow + j * 16);
@@ -417,7 +428,7 @@ template <typename T, int V, int R, bool kEdgeFeat, int LPH>
 struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
   using Base = EdgeDotOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
-  struct State : Base::State { A an[R][V]; int next_node; };
+  struct State : Base::State { A an[R][V]; int next_node; const unsigned char* bb[R]; };
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
@@ -426,7 +437,13 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = true;
 
-  __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
+  __device__ __forceinline__ void setup(State& st, int lane) const {
+    Base::setup(st, lane);
+    st.next_node = -1;
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      st.bb[i] = reinterpret_cast<const unsigned char*>(this->b + (kEdgeFeat ? st.sm.efeat[i] : st.sm.feat[i]));
+  }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
     if constexpr (!kPrefetch) return;
 #pragma unroll
@@ -444,11 +461,10 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
     }
   }
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
+    const unsigned rowb = (unsigned)(kEdgeFeat ? this->D : this->HD) * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const T* src = kEdgeFeat ? this->b + (long long)e * this->D + st.sm.efeat[i]
-                               : this->b + (long long)c * this->HD + st.sm.feat[i];
-      cp_async16(entry + (lane + 32 * i) * 16, src);
+      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.bb[i], kEdgeFeat ? e : c, rowb));
     }
   }
   template <bool kFullBatch>
@@ -490,7 +506,7 @@ template <typename T, int V, int R, int LPH>
 struct AttnFwdStaged : AttnFwdOp<T, V, R> {
   using Base = AttnFwdOp<T, V, R>;
   using A = typename Base::A;
-  struct State : Base::State { A qn[R][V]; int next_node; };
+  struct State : Base::State { A qn[R][V]; int next_node; const unsigned char* kb[R]; const unsigned char* vb[R]; };
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
@@ -500,7 +516,15 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = false;
 
-  __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
+  __device__ __forceinline__ void setup(State& st, int lane) const {
+    Base::setup(st, lane);
+    st.next_node = -1;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      st.kb[i] = reinterpret_cast<const unsigned char*>(this->k + st.sm.feat[i]);
+      st.vb[i] = reinterpret_cast<const unsigned char*>(this->v + st.sm.feat[i]);
+    }
+  }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
     if constexpr (!kPrefetch) return;
 #pragma unroll
@@ -526,10 +550,11 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
       for (int e = 0; e < V; ++e) st.q[i][e] *= c;
   }
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
+    const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      cp_async16(entry + (lane + 32 * i) * 16, this->k + (long long)c * this->HD + st.sm.feat[i]);
-      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->v + (long long)c * this->HD + st.sm.feat[i]);
+      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.kb[i], c, rowb));
+      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.vb[i], c, rowb));
     }
   }
   template <bool kFullBatch>
@@ -610,7 +635,10 @@ template <typename T, int V, int R, int LPH>
 struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   using Base = AttnBwdDstOp<T, V, R>;
   using A = typename Base::A;
-  struct State : Base::State { A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node; };
+  struct State : Base::State {
+    A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node;
+    const unsigned char* kb[R]; const unsigned char* vb[R];
+  };
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
@@ -619,7 +647,15 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = false;
 
-  __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
+  __device__ __forceinline__ void setup(State& st, int lane) const {
+    Base::setup(st, lane);
+    st.next_node = -1;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      st.kb[i] = reinterpret_cast<const unsigned char*>(this->k + st.sm.feat[i]);
+      st.vb[i] = reinterpret_cast<const unsigned char*>(this->v + st.sm.feat[i]);
+    }
+  }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
     if constexpr (!kPrefetch) return;
 #pragma unroll
@@ -667,10 +703,11 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
     }
   }
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
+    const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      cp_async16(entry + (lane + 32 * i) * 16, this->k + (long long)c * this->HD + st.sm.feat[i]);
-      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->v + (long long)c * this->HD + st.sm.feat[i]);
+      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.kb[i], c, rowb));
+      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.vb[i], c, rowb));
     }
   }
   template <bool kFullBatch>
@@ -765,10 +802,13 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   }
   __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
     // the node's (lse, delta) pairs: Hp pairs = `pieces` copies of 16 bytes, one per low lane
-    const unsigned char* pairs = reinterpret_cast<const unsigned char*>(this->stat + (long long)c * this->Hp);
-    const int pieces = this->Hp * (int)sizeof(StatPair<A>) / 16;
+    const unsigned pairb = (unsigned)this->Hp * (unsigned)sizeof(StatPair<A>);
+    const unsigned char* pairs = row_ptr(reinterpret_cast<const unsigned char*>(this->stat), c, pairb);
+    const int pieces = (int)(pairb / 16);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
+      // plain index arithmetic here: the per-lane base pointers of the other two kernels would cost this
+      // one, which is at its register limit, more than they save
       cp_async16(entry + (lane + 32 * i) * 16, this->q + (long long)c * this->HD + st.sm.feat[i]);
       cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->dout + (long long)c * this->HD + st.sm.feat[i]);
       const int piece = lane + 32 * i;

@@ -97,8 +97,10 @@ def shard_graph(g, rank, parts, chunk_size=32, index_dtype=th.int32):
 def all_gather_rows(local, bounds, group=None):
     """Concatenation over ranks of row blocks whose sizes are `bounds[p+1] - bounds[p]`.
 
-    Equal blocks go through one all_gather_into_tensor; unequal ones are padded to the largest
-    block for the collective and compacted afterwards (works on every backend)."""
+    Equal blocks go through one all_gather_into_tensor.  Unequal blocks: on NCCL every rank's block is
+    received straight into its slice of the result (all_gather over a list of views, which NCCL runs as
+    one group of broadcasts), so the gathered rows are written once; other backends pad to the largest
+    block for the collective and compact afterwards."""
     parts = bounds.numel() - 1
     counts = (bounds[1:] - bounds[:-1]).tolist()
     total = int(bounds[-1])
@@ -107,6 +109,10 @@ def all_gather_rows(local, bounds, group=None):
     out = th.empty((total,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     if len(set(counts)) == 1:
         dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+        return out
+    if local.is_cuda and min(counts) > 0 and dist.get_backend(group) == "nccl":
+        views = [out[int(bounds[p]):int(bounds[p + 1])] for p in range(parts)]
+        dist.all_gather(views, local.contiguous(), group=group)
         return out
     width = max(counts)
     padded = th.zeros((width,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)

@@ -81,6 +81,17 @@ long long graphop_launch_count(void);
 int graphop_profile_begin(graphop_stream_t stream);
 int graphop_profile_end(char* names, size_t names_bytes, float* ms, int max_entries);
 
+/* Gather ceiling, for benchmarks.  For every position k < n_edges a warp reads the row_bytes-byte
+ * row table0[indices[k]] (and table1[indices[k]] when table1 is not NULL) and nothing else: no
+ * arithmetic beyond a checksum that is never stored, no shared memory, every lane 16 bytes of each
+ * row, four edges of loads in flight per warp at 64 warps per SM.  The time of this launch is what
+ * gathering one row per edge from these tables through this index stream costs on the GPU at hand,
+ * whatever is then done with the rows; the benchmark reports each walker kernel against it.
+ * row_bytes: a multiple of 16, at most 512; tables 16-byte aligned; sink: 4 writable bytes (written
+ * only if a warp's checksum hits one particular value; the rows are summed as floats, any bit pattern will do).  The reference has no counterpart. */
+int graphop_gather_probe_i32(const int32_t* indices, int64_t n_edges, const void* table0, const void* table1,
+                             int row_bytes, void* sink, graphop_stream_t stream);
+
 /* Sufficient workspace for one call of `op`.  n_nodes: the largest node count among the
  * call's node tensors (for the softmax ops: an upper bound on node id + 1).  elem_bytes: 2, 4
  * or 8; index_bytes: 4 or 8. */

@@ -25,6 +25,8 @@ def _qkv(g, h, d, dtype, seed, mag=1.0):
     (4, 32, th.float32, th.int32, 1.0), (8, 64, th.float32, th.int64, 1.0), (4, 32, th.float64, th.int32, 3.0),
     (2, 64, th.float32, th.int32, 3.0), (1, 128, th.float32, th.int32, 1.0), (8, 64, th.bfloat16, th.int32, 1.0),
     (8, 64, th.float64, th.int64, 1.0), (1, 1024, th.float32, th.int32, 0.5), (16, 4, th.float32, th.int32, 1.0),
+    # odd head counts: the packed (lse, delta) rows are padded to an even number of heads for fp32
+    (3, 8, th.float32, th.int32, 1.0), (5, 16, th.float64, th.int32, 1.0), (3, 16, th.bfloat16, th.int32, 1.0),
 ])
 def test_fused_attention_matches_oracle_chain(name, g, cs, h, d, dtype, idt, mag):
     r, c = chunked(g, cs, dtype=idt), chunked(g, cs, transposed=True, dtype=idt)
