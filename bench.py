@@ -366,6 +366,28 @@ class ShardedSpmmWorkload:
     def e2e_bytes(self):
         return _nbytes(self.host), _nbytes(self.outs)
 
+    def collectives(self, reps=3):
+        """Milliseconds of the two all-gathers of one step, each timed alone on this rank (all ranks call
+        this together), and the bytes every rank receives from its peers per step."""
+        from custom_op_benchmark_b200 import sharding
+        if self.world == 1:
+            return None
+        xb = sharding.even_bounds(self.n_src, self.world)
+        out = {}
+        for name, local, bounds in (("x", self.x_shard, xb), ("dy", self.dy_local, self.sh.dst_bounds)):
+            sharding.all_gather_rows(local, bounds)
+            th.cuda.synchronize()
+            a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                sharding.all_gather_rows(local, bounds)
+            b.record()
+            th.cuda.synchronize()
+            out[name + "_ms"] = a.elapsed_time(b) / reps
+        row = self.d * 4
+        out["bytes_received_per_step"] = (self.n_src - self.x_shard.shape[0]) * row + (self.n_dst - self.sh.rows) * row
+        return out
+
 
 WORKLOAD_CLASSES = {"attention": AttentionWorkload, "gat": GatWorkload, "sddmm_softmax": SddmmSoftmaxWorkload,
                     "sharded_spmm": ShardedSpmmWorkload}
@@ -543,6 +565,8 @@ def run_gpu(args):
 
     # -- the gathers alone, same index streams and tables (a floor for the walker kernels) ------
     floors = wl.gather_floor(lib) if rank == 0 and hasattr(wl, "gather_floor") else {}
+    # -- the collectives of a sharded step, timed alone (per-kernel events count them with the kernel after them)
+    coll = wl.collectives() if hasattr(wl, "collectives") else None
 
     # -- reduce over ranks ---------------------------------------------------------------------
     stats = th.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], dtype=th.float64, device=dev)
@@ -586,6 +610,10 @@ def run_gpu(args):
                          "step_frac": wl.alg_step / (ms_per_step * 1e-3) / 1e9 / peak},
             "kernels": kernels,
         }
+        if coll:
+            out["all_gather"] = dict(coll, note="NCCL all-gathers of the sharded step timed alone on rank 0; inside the "
+                                                "step the per-kernel events charge them to the kernel that follows "
+                                                "(expand_rows), and the dy gather overlaps the dedata kernel")
         if floors:
             out["gather_floor"] = {
                 "what": "graphop_gather_probe_i32: one row per edge per operand read through the kernel's own index "

@@ -94,26 +94,31 @@ def shard_graph(g, rank, parts, chunk_size=32, index_dtype=th.int32):
                       cv(col), cv(ptr_t), cv(g.eid_t[tlo:thi]), cv(g.indices_t[tlo:thi]), lo)
 
 
-def all_gather_rows(local, bounds, group=None):
+def all_gather_rows(local, bounds, group=None, async_op=False):
     """Concatenation over ranks of row blocks whose sizes are `bounds[p+1] - bounds[p]`.
 
     Equal blocks go through one all_gather_into_tensor.  Unequal blocks: on NCCL every rank's block is
     received straight into its slice of the result (all_gather over a list of views, which NCCL runs as
     one group of broadcasts), so the gathered rows are written once; other backends pad to the largest
-    block for the collective and compact afterwards."""
+    block for the collective and compact afterwards.
+
+    async_op=True returns (result, work): the collective is only enqueued, and `work.wait()` (None when
+    nothing is pending) must be called before the result is read, so that independent kernels can run
+    on the compute stream meanwhile."""
     parts = bounds.numel() - 1
     counts = (bounds[1:] - bounds[:-1]).tolist()
     total = int(bounds[-1])
+    done = (lambda out, work=None: (out, work) if async_op else out)
     if parts == 1:
-        return local
+        return done(local)
     out = th.empty((total,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     if len(set(counts)) == 1:
-        dist.all_gather_into_tensor(out, local.contiguous(), group=group)
-        return out
+        work = dist.all_gather_into_tensor(out, local.contiguous(), group=group, async_op=async_op)
+        return done(out, work)
     if local.is_cuda and min(counts) > 0 and dist.get_backend(group) == "nccl":
         views = [out[int(bounds[p]):int(bounds[p + 1])] for p in range(parts)]
-        dist.all_gather(views, local.contiguous(), group=group)
-        return out
+        work = dist.all_gather(views, local.contiguous(), group=group, async_op=async_op)
+        return done(out, work)
     width = max(counts)
     padded = th.zeros((width,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     padded[: local.shape[0]] = local
@@ -121,7 +126,7 @@ def all_gather_rows(local, bounds, group=None):
     dist.all_gather_into_tensor(buf, padded, group=group)
     for p in range(parts):
         out[int(bounds[p]):int(bounds[p + 1])] = buf[p * width:p * width + counts[p]]
-    return out
+    return done(out)
 
 
 def _default_ops():
@@ -143,10 +148,13 @@ def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all, ops=None,
     rank owns in the transposed split.  `edata_all`: the weights of all edges by global edge id
     (gathered once per graph by the caller; the transposed CSR reads them through eid_t)."""
     ops = ops or _default_ops()
-    dy_all = all_gather_rows(dy_local, sh.dst_bounds, group)
+    # the gather of dy is only needed by dx: it is enqueued first and travels while dedata is computed
+    dy_all, pending = all_gather_rows(dy_local, sh.dst_bounds, group, async_op=True)
     # dedata: sampled dot products of the owned rows of dy against gathered x; no exchange.
     # The op reads dy by destination id and the local chunk table names local rows 0..rows-1.
     dedata = ops.maskedmm_csr_forward(sh.row, sh.indptr, sh.eid, sh.indices, dy_local, x_all)
+    if pending is not None:
+        pending.wait()
     # dx: row-owned aggregation over the transposed shard, dy gathered, weights by global edge id
     dx = ops.vector_spmm_forward(sh.col, sh.indptr_t, sh.eid_t, sh.indices_t, edata_all, dy_all, num_dst=sh.cols)
     return dedata, dx
