@@ -133,6 +133,18 @@ class Workload:
         """{kernel name: (int32 index stream, table, table or None)}: what each walker kernel gathers per edge."""
         return {}
 
+    def gather_bytes(self, kernel):
+        """B_gather of `kernel`: its compulsory bytes with every gathered node tensor counted once per edge
+        (the traffic of a machine without caches), or None when the kernel gathers nothing we track."""
+        streams = self.gather_streams()
+        if kernel not in streams or kernel not in self.alg:
+            return None
+        _, t0, t1 = streams[kernel]
+        tables = [t for t in (t0, t1) if t is not None]
+        once = sum(t.numel() * t.element_size() for t in tables)
+        per_edge = sum(t[0].numel() * t.element_size() for t in tables) * self.e
+        return self.alg[kernel] - once + per_edge
+
     def gather_floor(self, lib, reps=5):
         """Milliseconds of graphop_gather_probe_i32 (the gathers alone, nothing done with the rows) for every
         kernel of gather_streams() whose rows are at most 512 bytes; {} when there is none."""
@@ -445,6 +457,36 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # the GPU arm
 # --------------------------------------------------------------------------------------------
+def replay_from_graph(step, steps):
+    """Milliseconds per step of `step()` captured once into a CUDA graph and replayed `steps` times, or
+    {"error": ...} when the capture is refused."""
+    try:
+        side = th.cuda.Stream()
+        side.wait_stream(th.cuda.current_stream())
+        with th.cuda.stream(side):
+            for _ in range(3):
+                step()
+        th.cuda.current_stream().wait_stream(side)
+        th.cuda.synchronize()
+        graph = th.cuda.CUDAGraph()
+        with th.cuda.graph(graph):
+            keep = step()
+        for _ in range(3):
+            graph.replay()
+        th.cuda.synchronize()
+        a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            graph.replay()
+        b.record()
+        th.cuda.synchronize()
+        del keep
+        return a.elapsed_time(b) / steps
+    except Exception as exc:  # a capture that the runtime refuses is reported, not fatal
+        th.cuda.synchronize()
+        return {"error": "%s: %s" % (type(exc).__name__, str(exc)[:200])}
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -563,6 +605,11 @@ def run_gpu(args):
     kernels = {k: {"launches_per_step": len(v) / prof_steps, "ms_per_step": sum(v) / prof_steps}
                for k, v in per_kernel.items()}
 
+    # -- the same step replayed from a CUDA graph (what is left when launch latency is taken out) --
+    graph_ms = None
+    if args.cuda_graph and world == 1:
+        graph_ms = replay_from_graph(step_device, args.steps)
+
     # -- the gathers alone, same index streams and tables (a floor for the walker kernels) ------
     floors = wl.gather_floor(lib) if rank == 0 and hasattr(wl, "gather_floor") else {}
     # -- the collectives of a sharded step, timed alone (per-kernel events count them with the kernel after them)
@@ -605,11 +652,18 @@ def run_gpu(args):
             "phases": {"forward_ms": fwd_ms, "backward_ms": bwd_ms},
             "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": peak_kind, "algorithmic_bytes": alg[top],
+                         "frac_of_spec_8000": achieved / 8000.0,
                          "ms": top_ms, "traffic": traffic_for(top, args.workload),
+                         "gather_bytes": wl.gather_bytes(top) if hasattr(wl, "gather_bytes") else None,
                          "step_algorithmic_bytes": wl.alg_step,
                          "step_frac": wl.alg_step / (ms_per_step * 1e-3) / 1e9 / peak},
             "kernels": kernels,
         }
+        if graph_ms is not None:
+            out["cuda_graph"] = graph_ms if isinstance(graph_ms, dict) else {
+                "ms_per_step": graph_ms, "value": units / (graph_ms * 1e-3), "unit": UNIT,
+                "note": "one forward + backward captured with torch.cuda.graph and replayed; same kernels, no host "
+                        "launch latency"}
         if coll:
             out["all_gather"] = dict(coll, note="NCCL all-gathers of the sharded step timed alone on rank 0; inside the "
                                                 "step the per-kernel events charge them to the kernel that follows "
@@ -696,6 +750,8 @@ def main():
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (smaller runs)")
     ap.add_argument("--cpu-sample-scale", type=int, default=18)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="also replay the step from a CUDA graph and report it (1 GPU)")
     ap.add_argument("--lean", action="store_true",
                     help="warm-up and timed steps only (for ncu captures); prints a reduced line")
     args = ap.parse_args()
