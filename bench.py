@@ -332,6 +332,8 @@ class ShardedSpmmWorkload:
         g = make_graph(spec, seed=0, device=dev)          # the same graph on every rank
         self.e, self.n_dst, self.n_src = g.n_edges, g.n_dst, g.n_src
         self.sh = sh = sharding.shard_graph(g, rank, world, chunk_size=32)
+        # world > 1: fetch only the node rows this shard's edges reference (built once per graph)
+        self.ex = sharding.plan_shard_exchange(sh) if (world > 1 and spec.get("exchange", "needed") == "needed") else None
         del g
         th.cuda.empty_cache()
         gen = th.Generator(device=dev).manual_seed(7)     # edge weights by global edge id, same on every rank
@@ -360,18 +362,19 @@ class ShardedSpmmWorkload:
 
     def forward(self):
         from custom_op_benchmark_b200 import sharding
-        self.y, self.x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, self.x_shard)
+        self.y, self.x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, self.x_shard, exchange=self.ex)
 
     def backward(self):
         from custom_op_benchmark_b200 import sharding
-        return sharding.sharded_spmm_backward(self.sh, self.w_local, self.dy_local, self.x_all, self.w_all)
+        return sharding.sharded_spmm_backward(self.sh, self.w_local, self.dy_local, self.x_all, self.w_all,
+                                              exchange=self.ex)
 
     def e2e_step(self):
         from custom_op_benchmark_b200 import sharding
         x = self.stage[0].copy_(self.host[0], non_blocking=True)
         dy = self.stage[1].copy_(self.host[1], non_blocking=True)
-        y, x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, x)
-        _, dx = sharding.sharded_spmm_backward(self.sh, self.w_local, dy, x_all, self.w_all)
+        y, x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, x, exchange=self.ex)
+        _, dx = sharding.sharded_spmm_backward(self.sh, self.w_local, dy, x_all, self.w_all, exchange=self.ex)
         self.outs[0].copy_(y, non_blocking=True)
         self.outs[1].copy_(dx, non_blocking=True)
 
@@ -379,25 +382,38 @@ class ShardedSpmmWorkload:
         return _nbytes(self.host), _nbytes(self.outs)
 
     def collectives(self, reps=3):
-        """Milliseconds of the two all-gathers of one step, each timed alone on this rank (all ranks call
-        this together), and the bytes every rank receives from its peers per step."""
+        """Milliseconds of the two exchanges of one step, each timed alone on this rank (all ranks call this
+        together), and the bytes every rank receives from its peers per step."""
         from custom_op_benchmark_b200 import sharding
         if self.world == 1:
             return None
         xb = sharding.even_bounds(self.n_src, self.world)
-        out = {}
-        for name, local, bounds in (("x", self.x_shard, xb), ("dy", self.dy_local, self.sh.dst_bounds)):
-            sharding.all_gather_rows(local, bounds)
+        if self.ex is not None:
+            from custom_op_benchmark_b200 import graphop
+            legs = (("x", lambda: sharding.exchange_rows(self.x_shard, self.ex.x, gather=graphop.gather_rows)),
+                    ("dy", lambda: sharding.exchange_rows(self.dy_local, self.ex.dy, gather=graphop.gather_rows)))
+        else:
+            legs = (("x", lambda: sharding.all_gather_rows(self.x_shard, xb)),
+                    ("dy", lambda: sharding.all_gather_rows(self.dy_local, self.sh.dst_bounds)))
+        out = {"kind": "all-to-all of the referenced rows" if self.ex is not None else "all-gather of every row"}
+        for name, leg in legs:
+            leg()
             th.cuda.synchronize()
             a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
             a.record()
             for _ in range(reps):
-                sharding.all_gather_rows(local, bounds)
+                leg()
             b.record()
             th.cuda.synchronize()
             out[name + "_ms"] = a.elapsed_time(b) / reps
         row = self.d * 4
-        out["bytes_received_per_step"] = (self.n_src - self.x_shard.shape[0]) * row + (self.n_dst - self.sh.rows) * row
+        if self.ex is not None:
+            rows = sum(self.ex.x.recv_counts) + sum(self.ex.dy.recv_counts)
+            out["rows_referenced"] = {"x": self.ex.x.needed.numel(), "of": self.n_src,
+                                      "dy": self.ex.dy.needed.numel(), "of_dst": self.n_dst}
+        else:
+            rows = (self.n_src - self.x_shard.shape[0]) + (self.n_dst - self.sh.rows)
+        out["bytes_received_per_step"] = rows * row
         return out
 
 
@@ -518,6 +534,7 @@ def run_gpu(args):
     if args.scale and spec["kind"] == "rmat":
         spec["scale"] = args.scale
     if spec["ops"] == "sharded_spmm":
+        spec["exchange"] = args.exchange
         wl = ShardedSpmmWorkload(spec, rank, dev, world)
     else:
         wl = WORKLOAD_CLASSES[spec["ops"]](spec, rank, dev)
@@ -665,9 +682,9 @@ def run_gpu(args):
                 "note": "one forward + backward captured with torch.cuda.graph and replayed; same kernels, no host "
                         "launch latency"}
         if coll:
-            out["all_gather"] = dict(coll, note="NCCL all-gathers of the sharded step timed alone on rank 0; inside the "
-                                                "step the per-kernel events charge them to the kernel that follows "
-                                                "(expand_rows), and the dy gather overlaps the dedata kernel")
+            out["exchange"] = dict(coll, note="the NCCL exchanges of the sharded step timed alone on rank 0; inside the "
+                                              "step the per-kernel events charge them to the kernel that follows "
+                                              "(expand_rows), and the dy exchange overlaps the dedata kernel")
         if floors:
             out["gather_floor"] = {
                 "what": "graphop_gather_probe_i32: one row per edge per operand read through the kernel's own index "
@@ -750,6 +767,8 @@ def main():
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (smaller runs)")
     ap.add_argument("--cpu-sample-scale", type=int, default=18)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="needed", choices=["needed", "all"],
+                    help="sharded workload: fetch only the node rows a shard references, or all-gather every row")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="also replay the step from a CUDA graph and report it (1 GPU)")
     ap.add_argument("--lean", action="store_true",

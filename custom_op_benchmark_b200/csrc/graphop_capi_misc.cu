@@ -187,6 +187,50 @@ extern "C" int graphop_gather_probe_i32(const int32_t* indices, int64_t n_edges,
   return GRAPHOP_OK;
 }
 
+namespace gk {
+// out[r] = table[idx[r]]: one warp per group of 4 rows, lanes copy 16-byte pieces; the 4 rows' loads are all
+// issued before the first store.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const int32_t* __restrict__ idx, long long n_rows,
+                                                         const uint4* __restrict__ table, int row_vec,
+                                                         uint4* __restrict__ out) {
+  constexpr int kRows = 4;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * 8;
+  for (long long g = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); g * kRows < n_rows; g += warps) {
+    const long long r0 = g * kRows;
+    long long src[kRows];
+#pragma unroll
+    for (int u = 0; u < kRows; ++u) src[u] = r0 + u < n_rows ? (long long)__ldg(idx + r0 + u) : -1;
+    for (int j = lane; j < row_vec; j += 32) {
+      uint4 v[kRows];
+#pragma unroll
+      for (int u = 0; u < kRows; ++u)
+        if (src[u] >= 0) v[u] = __ldg(table + src[u] * row_vec + j);
+#pragma unroll
+      for (int u = 0; u < kRows; ++u)
+        if (src[u] >= 0) out[(r0 + u) * row_vec + j] = v[u];
+    }
+  }
+}
+}  // namespace gk
+
+extern "C" int graphop_gather_rows_i32(const int32_t* idx, int64_t n_rows, const void* table, int64_t row_bytes,
+                                       void* out, graphop_stream_t stream) {
+  using namespace gk;
+  if (n_rows < 0 || row_bytes <= 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (n_rows == 0) return GRAPHOP_OK;
+  if (!idx || !table || !out) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (row_bytes % 16 || row_bytes / 16 > 0x7fffffff || (((uintptr_t)table | (uintptr_t)out) & 15))
+    return GRAPHOP_ERR_UNSUPPORTED;
+  const long long groups = (n_rows + 3) / 4;
+  const long long blocks = (groups + 7) / 8;
+  const unsigned grid = (unsigned)(blocks < 148 * 64 ? blocks : 148 * 64);
+  cudaStream_t st = (cudaStream_t)stream;
+  gather_rows_kernel<<<grid, 256, 0, st>>>(idx, n_rows, (const uint4*)table, (int)(row_bytes / 16), (uint4*)out);
+  GK_LAUNCHED("gather_rows");
+  return GRAPHOP_OK;
+}
+
 extern "C" size_t graphop_workspace_bytes(int op, int64_t n_edges, int64_t n_nodes, int H, int D, int elem_bytes,
                                           int index_bytes) {
   using namespace gk;

@@ -20,7 +20,7 @@ from . import _capi
 __all__ = [
     "maskedmm_csr_forward", "maskedmm_csr_backward", "node_mul_edge_forward", "node_mul_edge_backward",
     "sparse_softmax_forward", "sparse_softmax_backward", "vector_spmm_forward", "vector_spmm_backward",
-    "attention_forward", "attention_backward", "attention_supported", "check_graph",
+    "attention_forward", "attention_backward", "attention_supported", "check_graph", "gather_rows",
 ]
 
 _ELEM = {th.float32: ("f32", 4), th.float64: ("f64", 8), th.bfloat16: ("bf16", 2)}
@@ -279,6 +279,27 @@ def attention_backward(row, indptr, indices, col, indptr_t, indices_t, q, k, v, 
                          _p(k), _p(v), _p(o), _p(lse), _p(d_o), float(scale), _p(dq), _p(dk), _p(dv), e, q.size(0),
                          k.size(0), h, d])
     return [dq, dk, dv]
+
+
+def gather_rows(table, idx, out=None):
+    """out[r] = table[idx[r]] (rows of a contiguous CUDA tensor, int32 or int64 row ids; 16-byte multiples go
+    through the library's copy kernel, anything else through torch)."""
+    _check_all(table=table, idx=idx)
+    row_bytes = (table[0].numel() if table.size(0) else 0) * table.element_size()
+    if out is None:
+        out = th.empty((idx.numel(),) + tuple(table.shape[1:]), dtype=table.dtype, device=table.device)
+    if idx.numel() == 0:
+        return out
+    if row_bytes == 0 or row_bytes % 16 or table.data_ptr() % 16 or out.data_ptr() % 16 or not out.is_contiguous() \
+            or table.size(0) >= 2 ** 31:
+        return th.index_select(table, 0, idx.long(), out=out)
+    idx32 = idx if idx.dtype == th.int32 else idx.to(th.int32)
+    with th.cuda.device(table.device):
+        rc = _capi.lib().graphop_gather_rows_i32(_p(idx32), idx32.numel(), _p(table), row_bytes, _p(out),
+                                                 th.cuda.current_stream(table.device).cuda_stream)
+    if rc != _capi.OK:
+        raise RuntimeError("graphop_gather_rows: %s" % _capi.error_message(rc))
+    return out
 
 
 def check_graph(row, indptr, eid, indices, n_nodes, n_other):

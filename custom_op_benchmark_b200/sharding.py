@@ -14,6 +14,11 @@ module adds the split the large configurations need:
   all-gathered, so every gradient row is owned by exactly one rank: no reduce-scatter and no
   atomics, results stay bit-reproducible.  dedata needs no exchange at all.
 
+All-gathering a node tensor delivers (P-1)/P of it to every rank whatever P is.  The alternative,
+built once per graph by ``plan_shard_exchange``, fetches from their owners only the rows a shard's
+edges reference (one all-to-all by index lists) and renumbers the shard's indices into that compact
+set; ``sharded_spmm_forward/backward(..., exchange=plan)`` use it.
+
 The compute is whatever ``ops`` namespace is passed (default: the CUDA ops of this package); the
 CPU tests pass the oracle and run the same bookkeeping over gloo.
 """
@@ -25,6 +30,7 @@ import torch.distributed as dist
 from .part_csr import partition_csr
 
 __all__ = ["balanced_bounds", "even_bounds", "GraphShard", "shard_graph", "all_gather_rows",
+           "RowExchange", "ShardExchange", "plan_row_exchange", "plan_shard_exchange", "exchange_rows",
            "sharded_spmm_forward", "sharded_spmm_backward"]
 
 
@@ -129,32 +135,126 @@ def all_gather_rows(local, bounds, group=None, async_op=False):
     return done(out)
 
 
+@dataclass
+class RowExchange:
+    """How one rank obtains the rows of a row-sharded tensor that its shard references.  The received
+    buffer holds the rows of the other ranks in rank order, then the rows of this rank's own block
+    (which never pass through the collective)."""
+    needed: th.Tensor     # (M,) global row ids in buffer order
+    send_idx: th.Tensor   # rows of this rank's own block to send, concatenated by receiving rank
+    send_counts: list     # rows sent to each rank (0 for this rank)
+    recv_counts: list     # rows received from each rank, in rank order (0 for this rank)
+    own_idx: th.Tensor    # rows of this rank's own block that it references itself
+
+
+@dataclass
+class ShardExchange:
+    """Both exchanges of a sharded SpMM step and the shard's indices renumbered into the received rows."""
+    x: RowExchange            # source features, owners by even_bounds(n_src)
+    dy: RowExchange           # upstream gradient rows, owners by the shard's dst_bounds
+    indices: th.Tensor        # sh.indices as positions in x.needed
+    indices_t: th.Tensor      # sh.indices_t as positions in dy.needed
+
+
+def plan_row_exchange(indices, owner_bounds, rank, group=None):
+    """(RowExchange, compact indices) for the rows named by `indices` of a tensor whose row block p lives on
+    rank p (`owner_bounds`, P + 1 entries).  Collective: every rank of the group calls it once per graph."""
+    parts = owner_bounds.numel() - 1
+    dev = indices.device
+    idx = indices.to(th.int64)
+    uniq = th.unique(idx)                                     # sorted
+    ob = owner_bounds.to(device=dev, dtype=th.int64)
+    cuts = th.searchsorted(uniq, ob)                          # rows of owner p: uniq[cuts[p]:cuts[p+1]]
+    counts = cuts[1:] - cuts[:-1]
+    local_id = uniq - th.repeat_interleave(ob[:-1], counts)   # row ids local to their owner
+    c0, c1 = int(cuts[rank]), int(cuts[rank + 1])
+    own_n, m = c1 - c0, uniq.numel()
+    # buffer order: the other ranks' rows (sorted), then the own rows
+    pos = th.searchsorted(uniq, idx)
+    compact = th.where(pos < c0, pos, th.where(pos < c1, pos - c0 + (m - own_n), pos - own_n)).to(indices.dtype)
+    needed = th.cat([uniq[:c0], uniq[c1:], uniq[c0:c1]])
+    request = th.cat([local_id[:c0], local_id[c1:]])
+    recv_counts = counts.tolist()
+    recv_counts[rank] = 0
+    own_idx = local_id[c0:c1].contiguous()
+    if parts == 1:
+        return RowExchange(needed, request, [0], [0], own_idx), compact
+    send_counts_t = th.empty(parts, dtype=th.int64, device=dev)
+    dist.all_to_all_single(send_counts_t, th.tensor(recv_counts, dtype=th.int64, device=dev), group=group)
+    send_counts = send_counts_t.tolist()
+    send_idx = th.empty(sum(send_counts), dtype=th.int64, device=dev)
+    dist.all_to_all_single(send_idx, request.contiguous(), output_split_sizes=send_counts,
+                           input_split_sizes=recv_counts, group=group)
+    if int(ob[-1]) < 2 ** 31:   # row ids of one block: the copy kernel takes them as int32
+        send_idx, own_idx = send_idx.to(th.int32), own_idx.to(th.int32)
+    return RowExchange(needed, send_idx, send_counts, recv_counts, own_idx), compact
+
+
+def plan_shard_exchange(sh, group=None):
+    """The two exchanges of `sh` (collective; once per graph)."""
+    x_plan, ic = plan_row_exchange(sh.indices, even_bounds(sh.n_src, sh.parts), sh.rank, group)
+    dy_plan, itc = plan_row_exchange(sh.indices_t, sh.dst_bounds, sh.rank, group)
+    return ShardExchange(x_plan, dy_plan, ic.contiguous(), itc.contiguous())
+
+
+def _torch_gather_rows(table, idx, out=None):
+    return th.index_select(table, 0, idx, out=out)
+
+
+def exchange_rows(local, plan, group=None, async_op=False, gather=None):
+    """The rows `plan.needed` of the row-sharded tensor whose block on this rank is `local`, in that order.
+    async_op=True returns (rows, work) like all_gather_rows.  `gather(table, idx, out=None)` packs rows
+    (default: torch.index_select; the CUDA ops bring their own copy kernel)."""
+    gather = gather or _torch_gather_rows
+    peers, own = sum(plan.recv_counts), plan.own_idx.numel()
+    out = th.empty((peers + own,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    work = None
+    if len(plan.recv_counts) > 1:
+        send = gather(local, plan.send_idx)
+        work = dist.all_to_all_single(out[:peers], send, output_split_sizes=plan.recv_counts,
+                                      input_split_sizes=plan.send_counts, group=group, async_op=async_op)
+    gather(local, plan.own_idx, out=out[peers:])   # own rows: a local copy, meanwhile
+    return (out, work if async_op else None) if async_op else out
+
+
 def _default_ops():
     from . import graphop
     return graphop
 
 
-def sharded_spmm_forward(sh, edata_local, x_shard, ops=None, group=None):
+def sharded_spmm_forward(sh, edata_local, x_shard, ops=None, group=None, exchange=None):
     """y rows of the owned destinations.  `edata_local`: weights of the owned edges (local edge
-    order), `x_shard`: this rank's even share of the source features.  Returns (y_local, x_all)."""
+    order), `x_shard`: this rank's even share of the source features.  Returns (y_local, x_rows):
+    x_rows is the gathered node tensor, or with `exchange` only the rows the shard references."""
     ops = ops or _default_ops()
+    if exchange is not None:
+        x_rows = exchange_rows(x_shard, exchange.x, group, gather=getattr(ops, "gather_rows", None))
+        y = ops.vector_spmm_forward(sh.row, sh.indptr, sh.eid, exchange.indices, edata_local, x_rows, num_dst=sh.rows)
+        return y, x_rows
     x_all = all_gather_rows(x_shard, even_bounds(sh.n_src, sh.parts), group)
     y = ops.vector_spmm_forward(sh.row, sh.indptr, sh.eid, sh.indices, edata_local, x_all, num_dst=sh.rows)
     return y, x_all
 
 
-def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all, ops=None, group=None):
+def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all, ops=None, group=None, exchange=None):
     """(dedata_local, dx_owned): gradients of the owned edges' weights, and of the source rows this
     rank owns in the transposed split.  `edata_all`: the weights of all edges by global edge id
-    (gathered once per graph by the caller; the transposed CSR reads them through eid_t)."""
+    (gathered once per graph by the caller; the transposed CSR reads them through eid_t).  `x_all`: what
+    the forward returned (with `exchange`: the referenced rows)."""
     ops = ops or _default_ops()
-    # the gather of dy is only needed by dx: it is enqueued first and travels while dedata is computed
-    dy_all, pending = all_gather_rows(dy_local, sh.dst_bounds, group, async_op=True)
-    # dedata: sampled dot products of the owned rows of dy against gathered x; no exchange.
+    # the rows of dy are only needed by dx: their transfer is enqueued first and travels while dedata is computed
+    if exchange is not None:
+        dy_rows, pending = exchange_rows(dy_local, exchange.dy, group, async_op=True,
+                                         gather=getattr(ops, "gather_rows", None))
+        src_ids, dst_ids = exchange.indices, exchange.indices_t
+    else:
+        dy_rows, pending = all_gather_rows(dy_local, sh.dst_bounds, group, async_op=True)
+        src_ids, dst_ids = sh.indices, sh.indices_t
+    # dedata: sampled dot products of the owned rows of dy against the source rows; no exchange.
     # The op reads dy by destination id and the local chunk table names local rows 0..rows-1.
-    dedata = ops.maskedmm_csr_forward(sh.row, sh.indptr, sh.eid, sh.indices, dy_local, x_all)
+    dedata = ops.maskedmm_csr_forward(sh.row, sh.indptr, sh.eid, src_ids, dy_local, x_all)
     if pending is not None:
         pending.wait()
-    # dx: row-owned aggregation over the transposed shard, dy gathered, weights by global edge id
-    dx = ops.vector_spmm_forward(sh.col, sh.indptr_t, sh.eid_t, sh.indices_t, edata_all, dy_all, num_dst=sh.cols)
+    # dx: row-owned aggregation over the transposed shard, weights by global edge id
+    dx = ops.vector_spmm_forward(sh.col, sh.indptr_t, sh.eid_t, dst_ids, edata_all, dy_rows, num_dst=sh.cols)
     return dedata, dx

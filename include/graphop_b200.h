@@ -92,6 +92,12 @@ int graphop_profile_end(char* names, size_t names_bytes, float* ms, int max_entr
 int graphop_gather_probe_i32(const int32_t* indices, int64_t n_edges, const void* table0, const void* table1,
                              int row_bytes, void* sink, graphop_stream_t stream);
 
+/* out[r, :] = table[idx[r], :] for r < n_rows, rows of row_bytes bytes (a multiple of 16; both tensors
+ * 16-byte aligned).  Packs the rows a peer asked for before they are sent, and the rows a shard references
+ * from its own block (sharded SpMM).  The reference runs on one device and has no counterpart. */
+int graphop_gather_rows_i32(const int32_t* idx, int64_t n_rows, const void* table, int64_t row_bytes, void* out,
+                            graphop_stream_t stream);
+
 /* Sufficient workspace for one call of `op`.  n_nodes: the largest node count among the
  * call's node tensors (for the softmax ops: an upper bound on node id + 1).  elem_bytes: 2, 4
  * or 8; index_bytes: 4 or 8. */

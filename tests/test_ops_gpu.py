@@ -353,3 +353,24 @@ def test_empty_graph_and_empty_edges():
     row, ptr = th.arange(5, device=DEV), z(6)
     y = graphop.vector_spmm_forward(row, ptr, eid, idx, th.empty(0, 2, device=DEV), x)
     assert bool((y == 0).all())
+
+
+# ------------------------------------------------------------------------------------------
+# gather_rows (packs rows for the sharded exchange)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,dtype,idt", [
+    ((1000, 128), th.float32, th.int32), ((777, 4, 32), th.float32, th.int64), ((513, 8), th.bfloat16, th.int32),
+    ((300, 2, 1024), th.float64, th.int64), ((64, 3), th.float32, th.int32), ((50, 4), th.float32, th.int64),
+])
+def test_gather_rows_is_an_exact_copy(shape, dtype, idt):
+    gen = _gen(31)
+    table = th.randn(*shape, generator=gen, dtype=th.float64).to(dtype).to(DEV)
+    for count in (0, 1, 5, 4099):
+        idx = th.randint(0, shape[0], (count,), generator=gen).to(idt).to(DEV)
+        got = graphop.gather_rows(table, idx)
+        assert got.shape == (count,) + tuple(shape[1:]) and th.equal(got, table[idx.long()])
+    # into a slice of a larger buffer, as the exchange does
+    idx = th.randint(0, shape[0], (37,), generator=gen).to(idt).to(DEV)
+    buf = th.zeros((50,) + tuple(shape[1:]), dtype=dtype, device=DEV)
+    graphop.gather_rows(table, idx, out=buf[13:])
+    assert th.equal(buf[13:], table[idx.long()]) and not bool(buf[:13].any())

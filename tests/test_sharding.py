@@ -58,6 +58,18 @@ def test_shards_cover_the_graph_exactly():
     assert th.equal(th.cat(seen_t), g.eid_t.long())  # every edge id exactly once on the transposed side
 
 
+def _test_graph(world):
+    """R-MAT 256 nodes for 2 ranks; for 3 ranks a graph whose node count 3 divides, with empty rows and one
+    row longer than a shard."""
+    if world == 2:
+        return graphs.rmat_graph(8, 8, seed=5, index_dtype=th.int64)
+    gen = th.Generator().manual_seed(11)
+    degs = th.randint(0, 12, (150,), generator=gen)
+    degs[th.rand(150, generator=gen) < 0.3] = 0
+    degs[17] = 900
+    return random_graph(150, 150, degs, 12)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -69,7 +81,7 @@ def _free_port():
 def _worker(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    g = graphs.rmat_graph(8, 8, seed=5, index_dtype=th.int64)
+    g = _test_graph(world)
     h, d = 2, 4
     gen = th.Generator().manual_seed(6)
     x = th.randn(g.n_src, h, d, generator=gen, dtype=th.float64)
@@ -82,16 +94,27 @@ def _worker(rank, world, port, out_dir):
     y, x_all = sharding.sharded_spmm_forward(sh, w[lo:hi].contiguous(), x[int(xb[rank]):int(xb[rank + 1])].contiguous(),
                                              ops=orc)
     dw, dx = sharding.sharded_spmm_backward(sh, w[lo:hi].contiguous(), dy[r0:r1].contiguous(), x_all, w, ops=orc)
-    th.save({"y": y, "dw": dw, "dx": dx, "rows": (r0, r1), "edges": (lo, hi),
+    # the same step fetching only the referenced rows
+    ex = sharding.plan_shard_exchange(sh)
+    assert th.equal(ex.x.needed[ex.indices.long()], sh.indices.long())
+    assert th.equal(ex.dy.needed[ex.indices_t.long()], sh.indices_t.long())
+    assert sum(ex.x.recv_counts) + ex.x.own_idx.numel() == ex.x.needed.numel() <= g.n_src
+    assert ex.x.recv_counts[rank] == 0 and ex.x.send_counts[rank] == 0   # own rows stay out of the collective
+    y2, x_rows = sharding.sharded_spmm_forward(sh, w[lo:hi].contiguous(),
+                                               x[int(xb[rank]):int(xb[rank + 1])].contiguous(), ops=orc, exchange=ex)
+    assert th.equal(x_rows, x[ex.x.needed])
+    dw2, dx2 = sharding.sharded_spmm_backward(sh, w[lo:hi].contiguous(), dy[r0:r1].contiguous(), x_rows, w, ops=orc,
+                                              exchange=ex)
+    th.save({"y": y, "dw": dw, "dx": dx, "y2": y2, "dw2": dw2, "dx2": dx2, "rows": (r0, r1), "edges": (lo, hi),
              "cols": (int(sh.src_bounds[rank]), int(sh.src_bounds[rank + 1]))}, os.path.join(out_dir, "r%d.pt" % rank))
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_two_rank_sharded_spmm_matches_unsharded(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_spmm_matches_unsharded(tmp_path, world):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    g = graphs.rmat_graph(8, 8, seed=5, index_dtype=th.int64)
+    g = _test_graph(world)
     h, d = 2, 4
     gen = th.Generator().manual_seed(6)
     x = th.randn(g.n_src, h, d, generator=gen, dtype=th.float64)
@@ -100,12 +123,13 @@ def test_two_rank_sharded_spmm_matches_unsharded(tmp_path):
     r, c = chunked(g, 8), chunked(g, 8, transposed=True)
     want_y = orc.vector_spmm_forward(*r, w, x)
     want_dw, want_dx = orc.vector_spmm_backward(*r, *c, w, dy, x)
-    y, dw, dx = th.zeros_like(want_y), th.zeros_like(want_dw), th.zeros_like(want_dx)
-    for rank in range(world):
-        o = th.load(os.path.join(str(tmp_path), "r%d.pt" % rank))
-        y[o["rows"][0]:o["rows"][1]] = o["y"]
-        dw[o["edges"][0]:o["edges"][1]] = o["dw"]
-        dx[o["cols"][0]:o["cols"][1]] = o["dx"]
-    assert_close(y, want_y, 1e-12, 1e-13, "y")
-    assert_close(dw, want_dw, 1e-12, 1e-13, "dedata")
-    assert_close(dx, want_dx, 1e-12, 1e-13, "dx")
+    for suffix in ("", "2"):   # all-gathered rows, then only the referenced rows
+        y, dw, dx = th.zeros_like(want_y), th.zeros_like(want_dw), th.zeros_like(want_dx)
+        for rank in range(world):
+            o = th.load(os.path.join(str(tmp_path), "r%d.pt" % rank))
+            y[o["rows"][0]:o["rows"][1]] = o["y" + suffix]
+            dw[o["edges"][0]:o["edges"][1]] = o["dw" + suffix]
+            dx[o["cols"][0]:o["cols"][1]] = o["dx" + suffix]
+        assert_close(y, want_y, 1e-12, 1e-13, "y" + suffix)
+        assert_close(dw, want_dw, 1e-12, 1e-13, "dedata" + suffix)
+        assert_close(dx, want_dx, 1e-12, 1e-13, "dx" + suffix)
