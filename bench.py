@@ -212,7 +212,7 @@ class AttentionWorkload(Workload):
         from custom_op_benchmark_b200 import graphop
         R, C = self.R, self.C
         return graphop.attention_backward(R[0], R[1], R[3], C[0], C[1], C[3], self.Q, self.K, self.V, self.o, self.lse,
-                                          self.dO, self.scale)
+                                          self.dO, self.scale, eid_t=C[2])
 
     def e2e_step(self):
         from custom_op_benchmark_b200 import wrapper
@@ -220,7 +220,7 @@ class AttentionWorkload(Workload):
         q, k, v = (b.copy_(hst, non_blocking=True).requires_grad_(True)
                    for b, hst in zip(self.stage[:3], self.host[:3]))
         go = self.stage[3].copy_(self.host[3], non_blocking=True)
-        out = wrapper.GraphAttention.apply(R[0], R[1], R[3], C[0], C[1], C[3], q, k, v, self.scale)
+        out = wrapper.GraphAttention.apply(R[0], R[1], R[3], C[0], C[1], C[3], q, k, v, self.scale, C[2])
         out.backward(go)
         for dst, src in zip(self.outs, (out.detach(), q.grad, k.grad, v.grad)):
             dst.copy_(src, non_blocking=True)

@@ -33,7 +33,7 @@ SIGNATURES = {
     "vector_spmm_forward": [_P] * 7 + [_I64] * 4 + [_INT] * 2 + _TAIL,
     "vector_spmm_backward": [_P] * 4 + [_I64] + [_P] * 4 + [_I64] + [_P] * 5 + [_I64] * 3 + [_INT] * 2 + _TAIL,
     "attention_forward": [_P] * 3 + [_I64] + [_P] * 3 + [_DBL] + [_P] * 2 + [_I64] * 3 + [_INT] * 2 + _TAIL,
-    "attention_backward": [_P] * 3 + [_I64] + [_P] * 3 + [_I64] + [_P] * 6 + [_DBL] + [_P] * 3 + [_I64] * 3
+    "attention_backward": [_P] * 3 + [_I64] + [_P] * 4 + [_I64] + [_P] * 6 + [_DBL] + [_P] * 3 + [_I64] * 3
                           + [_INT] * 2 + _TAIL,
 }
 

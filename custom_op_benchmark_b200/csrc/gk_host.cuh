@@ -652,7 +652,8 @@ inline int attention_forward(const I* row, const I* indptr, const I* indices, lo
 
 template <typename T, typename I>
 inline int attention_backward(const I* row, const I* indptr, const I* indices, long long C, const I* col,
-                              const I* indptr_t, const I* indices_t, long long Ct, const T* q, const T* k, const T* v,
+                              const I* indptr_t, const I* eid_t, const I* indices_t, long long Ct, const T* q,
+                              const T* k, const T* v,
                               const T* o, const void* lse, const T* dout, double scale, T* dq, T* dk, T* dv,
                               long long E, long long n_dst, long long n_src, int H, int D, void* ws, size_t wsb,
                               cudaStream_t st) {
@@ -673,6 +674,8 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
   const int tile0 = pick_tile(E);
   const int Hp = stat_heads(H, (int)sizeof(A));
   StatPair<A>* stat = (StatPair<A>*)ar.take((size_t)n_dst * Hp * sizeof(StatPair<A>));  // survives both passes
+  // with the transposed CSR's edge ids the destination pass leaves (p, ds) of every edge for the source pass
+  EdgePair<A>* pd = eid_t ? (EdgePair<A>*)ar.take((size_t)E * Hp * sizeof(EdgePair<A>)) : nullptr;
   const size_t mark = ar.used;
   {
     GraphView g;
@@ -685,7 +688,7 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
         auto generic = [&](void* cout, void* cin) {
           AttnBwdDstStaged<T, V, R, LPH> op;
           op.q = q; op.k = k; op.v = v; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.stat = stat;
-          op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+          op.pd = pd; op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
           op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
           return op;
         };
@@ -695,12 +698,22 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
   }
   ar.used = mark;
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, col, indptr_t, (const I*)nullptr, indices_t, Ct, E, st, &g));
+  GK_TRY(prepare_graph<I>(ar, col, indptr_t, eid_t, indices_t, Ct, E, st, &g));
   return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
     if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
     else return dispatch_lph(D / V, [&](auto Lc) -> int {
       constexpr int LPH = decltype(Lc)::value;
+      if (pd) {
+        auto weighted = [&](void* cout, void* cin) {
+          AttnBwdSrcPairsStaged<T, V, R, LPH> op;
+          op.q = q; op.k = k; op.v = v; op.dout = dout; op.stat = stat; op.pd = pd; op.dk = dk;
+          op.dv = dv; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+          op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+          return op;
+        };
+        return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, weighted);
+      }
       auto generic = [&](void* cout, void* cin) {
         AttnBwdSrcStaged<T, V, R, LPH> op;
         op.q = q; op.k = k; op.v = v; op.dout = dout; op.stat = stat; op.dk = dk;

@@ -403,6 +403,9 @@ struct AttnFwdOp {
 // source pass fetches both with one load.  Rows hold `stat_heads(H)` pairs: H rounded up so that a row is
 // a whole number of 16-byte pieces.
 template <typename A> struct alignas(2 * sizeof(A)) StatPair { A lse, delta; };
+// (p, ds) of one (edge, head): the probability and the score gradient the destination pass computed, kept
+// for the source pass when the caller gives the transposed CSR's edge ids.  Rows hold stat_heads(H) pairs.
+template <typename A> struct alignas(2 * sizeof(A)) EdgePair { A p, ds; };
 __host__ __device__ constexpr int stat_heads(int H, int acc_bytes) { return acc_bytes >= 8 ? H : ((H + 1) & ~1); }
 
 // ---------------------------------------------------------------------------------------

@@ -105,6 +105,11 @@ __host__ __device__ constexpr size_t staged_warp_bytes(int tile) {
 template <class Op, class = void> struct SharesEntries : std::false_type {};
 template <class Op> struct SharesEntries<Op, std::void_t<decltype(Op::kSharedEntry)>> : std::true_type {};
 
+// Ops that need the global position of the edges they fold declare `kTileBase = true` and get the tile's
+// first position in `State::tile_base` (positions stay below 2^31).
+template <class Op, class = void> struct WantsTileBase : std::false_type {};
+template <class Op> struct WantsTileBase<Op, std::void_t<decltype(Op::kTileBase)>> : std::true_type {};
+
 template <class Op>
 __global__ void __launch_bounds__(Op::kWarps * 32, Op::kMinCtas)
 walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ erow,
@@ -189,6 +194,7 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
 
   typename Op::State st;
   op.setup(st, lane);
+  if constexpr (WantsTileBase<Op>::value) st.tile_base = (int)j0;
   const int first = m_row[0];
   const bool head_open = before >= 0 && before == first;
   bool first_seg = true;
@@ -636,9 +642,12 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   using Base = AttnBwdDstOp<T, V, R>;
   using A = typename Base::A;
   struct State : Base::State {
-    A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node;
+    A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node; int tile_base;
     const unsigned char* kb[R]; const unsigned char* vb[R];
+    unsigned char* pdw[R];  // where this lane writes its head's (p, ds) of edge 0, or null: not the head's writer
   };
+  static constexpr bool kTileBase = true;
+  EdgePair<A>* __restrict__ pd = nullptr;  // (n_edges, Hp) out when not null: (p, ds) of every edge, by position
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
@@ -654,6 +663,8 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
     for (int i = 0; i < R; ++i) {
       st.kb[i] = reinterpret_cast<const unsigned char*>(this->k + st.sm.feat[i]);
       st.vb[i] = reinterpret_cast<const unsigned char*>(this->v + st.sm.feat[i]);
+      st.pdw[i] = (pd && st.sm.ok[i] && st.sm.efeat[i] == 0) ? reinterpret_cast<unsigned char*>(pd + st.sm.head[i])
+                                                              : nullptr;
     }
   }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
@@ -713,6 +724,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
                                                 int lane) const {
+    const unsigned pairb = (unsigned)this->Hp * (unsigned)sizeof(EdgePair<A>);
     A s[kBatch][R], dp[kBatch][R];
     GK_BATCH_LOOP(u) {
       const unsigned char* entry = GK_RING_ENTRY(i0 + u);
@@ -735,6 +747,9 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
       for (int i = 0; i < R; ++i) {
         const A p = gk_exp2(s[u][i] - st.lse[i]);
         const A ds = p * (dp[u][i] - st.delta[i]) * this->scale;
+        if (st.pdw[i])
+          *reinterpret_cast<EdgePair<A>*>(st.pdw[i] + (unsigned long long)(unsigned)(st.tile_base + i0 + u) * pairb) =
+              EdgePair<A>{p, ds};
         A kv[V];
         lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
 #pragma unroll
@@ -852,6 +867,76 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   }
   // dk accumulated against k in base-2 units would be wrong: ak sums ds * q, which does not involve k,
   // so nothing to undo at store time.
+};
+
+// ---------------------------------------------------------------------------------------
+// Source side of the attention backward when the destination pass left (p, ds) of every edge:
+//     dv[c] = sum_k p_k * dO[dst_k],     dk[c] = sum_k ds_k * q[dst_k]
+// Two weighted aggregations: no dot products, no k / v rows.  Ring entry = [q row][dO row][(p, ds) pairs of the
+// edge], the pairs fetched by edge id (the transposed CSR's eid).  Row output, carries and gap fill are the
+// base op's.
+// ---------------------------------------------------------------------------------------
+template <typename T, int V, int R, int LPH>
+struct AttnBwdSrcPairsStaged : AttnBwdSrcOp<T, V, R> {
+  using Base = AttnBwdSrcOp<T, V, R>;
+  using A = typename Base::A;
+  struct State : Base::State { const unsigned char* qb[R]; const unsigned char* gb[R]; };
+  using Ring = RingShape<T, R, 2, 0, true, GK_TUNE_CTAS_SRC>;
+  static constexpr int kMaxHeads = LPH ? (32 * R / LPH > 2 ? 32 * R / LPH : 2) : 32 * R;
+  static constexpr int kPairBytes = (kMaxHeads * (int)sizeof(EdgePair<A>) + 15) / 16 * 16;
+  static constexpr int kEdgeBytes = 2 * Ring::kRowBytes + kPairBytes;
+  static constexpr int kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, true);
+  static constexpr int kBatch = pick_batch(R, kDepth);
+  static constexpr bool kUsesEid = true;
+  static constexpr bool kSharedEntry = true;  // lanes read pair bytes that other lanes copied
+  const EdgePair<A>* __restrict__ pd;          // (n_edges, Hp) by edge id, from the destination pass
+
+  __device__ __forceinline__ void setup(State& st, int lane) const {
+    Base::setup(st, lane);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      st.qb[i] = reinterpret_cast<const unsigned char*>(this->q + st.sm.feat[i]);
+      st.gb[i] = reinterpret_cast<const unsigned char*>(this->dout + st.sm.feat[i]);
+    }
+  }
+  __device__ __forceinline__ void prefetch_node(State&, int, int) const {}
+  __device__ __forceinline__ void begin(State& st, int, int) const {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+      for (int e = 0; e < V; ++e) { st.ak[i][e] = A(0); st.av[i][e] = A(0); }
+  }
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int e, int lane) const {
+    const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
+    const unsigned pairb = (unsigned)this->Hp * (unsigned)sizeof(EdgePair<A>);
+    const unsigned char* pairs = row_ptr(reinterpret_cast<const unsigned char*>(pd), e, pairb);
+    const int pieces = (int)(pairb / 16);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.qb[i], c, rowb));
+      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.gb[i], c, rowb));
+      const int piece = lane + 32 * i;
+      if (piece < pieces) cp_async16(entry + 2 * Ring::kRowBytes + piece * 16, pairs + piece * 16);
+    }
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+                                                int lane) const {
+    GK_BATCH_LOOP(u) {
+      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const EdgePair<A>* pr = reinterpret_cast<const EdgePair<A>*>(entry + 2 * Ring::kRowBytes);
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const EdgePair<A> w = pr[st.sm.head[i]];
+        A qv[V], gv[V];
+        lds_acc<T, V>(qv, entry + (lane + 32 * i) * 16);
+        lds_acc<T, V>(gv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+#pragma unroll
+        for (int e = 0; e < V; ++e) { st.av[i][e] += w.p * gv[e]; st.ak[i][e] += w.ds * qv[e]; }
+      }
+    }
+  }
 };
 
 }  // namespace gk

@@ -73,10 +73,10 @@
   }                                                                                                                  \
   extern "C" int graphop_attention_backward_##SUF(                                                                   \
       const I* row, const I* indptr, const I* indices, int64_t n_chunks, const I* col, const I* indptr_t,            \
-      const I* indices_t, int64_t n_chunks_t, const CT* q, const CT* k, const CT* v, const CT* o, const void* lse,   \
-      const CT* d_o, double scale, CT* dq, CT* dk, CT* dv, int64_t n_edges, int64_t n_dst, int64_t n_src, int H,     \
-      int D, void* ws, size_t wsb, graphop_stream_t stream) {                                                        \
-    return gk::attention_backward<T, I>(row, indptr, indices, n_chunks, col, indptr_t, indices_t, n_chunks_t,        \
+      const I* eid_t, const I* indices_t, int64_t n_chunks_t, const CT* q, const CT* k, const CT* v, const CT* o,    \
+      const void* lse, const CT* d_o, double scale, CT* dq, CT* dk, CT* dv, int64_t n_edges, int64_t n_dst,          \
+      int64_t n_src, int H, int D, void* ws, size_t wsb, graphop_stream_t stream) {                                  \
+    return gk::attention_backward<T, I>(row, indptr, indices, n_chunks, col, indptr_t, eid_t, indices_t, n_chunks_t, \
                                         (const T*)q, (const T*)k, (const T*)v, (const T*)o, lse, (const T*)d_o,      \
                                         scale, (T*)dq, (T*)dk, (T*)dv, n_edges, n_dst, n_src, H, D, ws, wsb,         \
                                         (cudaStream_t)stream);                                                       \

@@ -261,13 +261,22 @@ def attention_forward(row, indptr, indices, q, k, v, scale):
     return o, lse
 
 
-def attention_backward(row, indptr, indices, col, indptr_t, indices_t, q, k, v, o, lse, d_o, scale):
-    """[dq, dk, dv] of attention_forward; probabilities are recomputed from q, k and lse."""
+def attention_backward(row, indptr, indices, col, indptr_t, indices_t, q, k, v, o, lse, d_o, scale, eid_t=None):
+    """[dq, dk, dv] of attention_forward; probabilities are recomputed from q, k and lse.
+
+    ``eid_t`` (optional): for every position of the transposed CSR the position of the same edge in the row
+    CSR, i.e. the transposed CSR's edge ids when the row CSR's are 0..e-1.  With it the destination pass
+    keeps (p, ds) per edge (2 * e * h accumulator-sized values of workspace) and the source pass does not
+    recompute them."""
     d_o = d_o.contiguous()
     _check_all(row=row, indptr=indptr, indices=indices, col=col, indptr_t=indptr_t, indices_t=indices_t, q=q, k=k,
                v=v, o=o, lse=lse, d_o=d_o)
     elem = _elem(q, k, v, o, d_o)
-    index = _index(row, indptr, indices, col, indptr_t, indices_t)
+    if eid_t is not None:
+        _check_all(eid_t=eid_t)
+        index = _index(row, indptr, indices, col, indptr_t, indices_t, eid_t)
+    else:
+        index = _index(row, indptr, indices, col, indptr_t, indices_t)
     h, d = _heads(q, True)
     e, c, ct = indices.size(0), _chunks(row, indptr), _chunks(col, indptr_t)
     dq, dk, dv = th.empty_like(q), th.empty_like(k), th.empty_like(v)
@@ -275,7 +284,7 @@ def attention_backward(row, indptr, indices, col, indptr_t, indices_t, q, k, v, 
         return [dq.zero_(), dk.zero_(), dv.zero_()]
     with th.cuda.device(q.device):
         _call("attention_backward", elem, index, _capi.OP_ATTENTION_BWD, e, max(q.size(0), k.size(0)), h, d,
-              q.device, [_p(row), _p(indptr), _p(indices), c, _p(col), _p(indptr_t), _p(indices_t), ct, _p(q),
+              q.device, [_p(row), _p(indptr), _p(indices), c, _p(col), _p(indptr_t), _p(eid_t), _p(indices_t), ct, _p(q),
                          _p(k), _p(v), _p(o), _p(lse), _p(d_o), float(scale), _p(dq), _p(dk), _p(dv), e, q.size(0),
                          k.size(0), h, d])
     return [dq, dk, dv]

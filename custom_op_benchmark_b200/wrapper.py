@@ -80,22 +80,25 @@ class VectorSPMM(Function):
 class GraphAttention(Function):
     """O = VectorSPMM(SparseSoftmax(scale * MaskedMMCSR(Q, K)), V) in one kernel per direction.
 
-    ``apply(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale)``; no edge ids are
-    needed because no edge tensor is materialised.  Only the (n, h) log-sum-exp is saved."""
+    ``apply(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale, eid_t=None)``; no edge tensor is
+    materialised and only the (n, h) log-sum-exp is saved.  ``eid_t`` (the transposed CSR's edge ids, valid
+    when the row CSR's edge ids are its positions) lets the backward pass each edge's probability from its
+    destination-side kernel to its source-side kernel instead of recomputing it."""
 
     @staticmethod
-    def forward(ctx, row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale):
+    def forward(ctx, row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale, eid_t=None):
         o, lse = _g.attention_forward(row, indptr, indices, Q, K, V, scale)
         ctx.save_for_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse)
         ctx.scale = scale
+        ctx.eid_t = eid_t
         return o
 
     @staticmethod
     def backward(ctx, d_o):
         row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse = ctx.saved_tensors
         dq, dk, dv = _g.attention_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse, d_o,
-                                           ctx.scale)
-        return None, None, None, None, None, None, dq, dk, dv, None
+                                           ctx.scale, eid_t=ctx.eid_t)
+        return None, None, None, None, None, None, dq, dk, dv, None, None
 
 
 def graph_attention(row, indptr, eid, indices, col, indptr_t, eid_t, indices_t, Q, K, V, scale):

@@ -181,9 +181,14 @@ int graphop_check_graph_i64(const int64_t* row, const int64_t* indptr, const int
                                       int64_t n_dst, int64_t n_src, int H, int D, void* workspace,                  \
                                       size_t workspace_bytes, graphop_stream_t stream);                             \
   /* Gradients of the fused chain: dq over the row CSR, dk and dv over the transposed CSR, probabilities            \
-   * recomputed from q, k and lse.  Composes graphop_kernel.cu:544-600, 465-507 and 355-409. */                     \
+   * recomputed from q, k and lse.  Composes graphop_kernel.cu:544-600, 465-507 and 355-409.  eid_t (may be NULL):  \
+   * for every position of the transposed CSR the position of the same edge in the row CSR (the eid_t the           \
+   * reference's callers build, wrapper.py:129-141, when the row CSR's edge ids are its positions).  With it the    \
+   * row pass leaves (p, ds) of every edge in the workspace and the transposed pass only aggregates; without it     \
+   * the transposed pass recomputes both from q, k, lse and delta. */                                               \
   int graphop_attention_backward_##SUF(const I* row, const I* indptr, const I* indices, int64_t n_chunks,           \
-                                       const I* col, const I* indptr_t, const I* indices_t, int64_t n_chunks_t,     \
+                                       const I* col, const I* indptr_t, const I* eid_t, const I* indices_t,         \
+                                       int64_t n_chunks_t,                                                          \
                                        const T* q, const T* k, const T* v, const T* o, const void* lse,             \
                                        const T* d_o, double scale, T* dq, T* dk, T* dv, int64_t n_edges,            \
                                        int64_t n_dst, int64_t n_src, int H, int D, void* workspace,                 \

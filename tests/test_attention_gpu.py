@@ -62,6 +62,14 @@ def test_fused_attention_matches_oracle_chain(name, g, cs, h, d, dtype, idt, mag
     at = at * max(1.0, (deg_max / 256.0) ** 0.5)
     for got, want, what in ((dq, want_dq, "dq"), (dk, want_dk, "dk"), (dv, want_dv, "dv")):
         assert_close(got, want, rt * 5, at * max(1.0, float(want.abs().max())), what)
+    # the same backward with the transposed CSR's edge ids: (p, ds) handed from the destination pass to the
+    # source pass instead of recomputed (valid when the row CSR's edge ids are its positions)
+    assert th.equal(r[2].long(), th.arange(g.n_edges))
+    dq2, dk2, dv2 = graphop.attention_backward(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], Q.to(DEV), K.to(DEV),
+                                               V.to(DEV), o, lse, dO.to(DEV), scale, eid_t=cc[2])
+    assert th.equal(dq2, dq)
+    for got, want, what in ((dk2, want_dk, "dk (pairs)"), (dv2, want_dv, "dv (pairs)")):
+        assert_close(got, want, rt * 5, at * max(1.0, float(want.abs().max())), what)
 
 
 def test_fused_attention_matches_dense_masked_config1():
@@ -91,6 +99,11 @@ def test_fused_attention_is_bit_reproducible_and_matches_unfused_ops():
     b2 = graphop.attention_backward(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], Q, K, V, o1, l1, dO, scale)
     for a, b in zip(b1, b2):
         assert th.equal(a, b)
+    b3 = graphop.attention_backward(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], Q, K, V, o1, l1, dO, scale, eid_t=cc[2])
+    b4 = graphop.attention_backward(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], Q, K, V, o1, l1, dO, scale, eid_t=cc[2])
+    for a, b, c_ in zip(b3, b4, b1):
+        assert th.equal(a, b)
+        assert_close(a, c_.cpu().double(), 1e-5, 1e-5, "pairs vs recomputed")
     s = graphop.maskedmm_csr_forward(*rc, Q, K) * scale
     p = graphop.sparse_softmax_forward(*rc[:3], s)
     o3 = graphop.vector_spmm_forward(*rc, p, V, num_dst=g.n_dst)

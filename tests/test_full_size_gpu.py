@@ -68,7 +68,8 @@ def test_rmat21_fused_chain_equals_unfused_ops(rmat21):
     Q, K, V, dO = (th.randn(n, h, d, generator=gen, device=DEV) for _ in range(4))
     scale = d ** -0.5
     o, lse = graphop.attention_forward(R[0], R[1], R[3], Q, K, V, scale)
-    dq, dk, dv = graphop.attention_backward(R[0], R[1], R[3], C[0], C[1], C[3], Q, K, V, o, lse, dO, scale)
+    dq, dk, dv = graphop.attention_backward(R[0], R[1], R[3], C[0], C[1], C[3], Q, K, V, o, lse, dO, scale,
+                                            eid_t=C[2])
     s = graphop.maskedmm_csr_forward(*R, Q, K) * scale
     p = graphop.sparse_softmax_forward(*R[:3], s)
     o2 = graphop.vector_spmm_forward(*R, p, V)
