@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("GRAPHOP_B200_LIBRARY") or os.path.join(HERE, "libgrap
 OK, ERR_INVALID_ARGUMENT, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_CUDA = range(5)
 
 OP_MASKEDMM_FWD, OP_MASKEDMM_BWD, OP_NODE_MUL_EDGE_FWD, OP_NODE_MUL_EDGE_BWD, OP_SOFTMAX_FWD, \
-    OP_SOFTMAX_BWD, OP_SPMM_FWD, OP_SPMM_BWD, OP_ATTENTION_FWD, OP_ATTENTION_BWD = range(10)
+    OP_SOFTMAX_BWD, OP_SPMM_FWD, OP_SPMM_BWD, OP_ATTENTION_FWD, OP_ATTENTION_BWD, OP_ATTENTION_BWD_PAIRS = range(11)
 
 ELEM_SUFFIXES = ("f32", "f64", "bf16")
 INDEX_SUFFIXES = ("i32", "i64")

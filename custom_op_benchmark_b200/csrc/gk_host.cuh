@@ -380,8 +380,19 @@ inline int run_edge_mix(const GraphView& g, const T* dy, const T* a, T* db, int 
   const bool vec = aligned16(a) && aligned16(db) && D % VM == 0;
   const long long total = g.E * (vec ? D / VM : D);
   const unsigned grid = (unsigned)((total + 255) / 256 < (1 << 20) ? (total + 255) / 256 : (1 << 20));
-  if (vec) edge_mix_heads_kernel<T, VM><<<grid ? grid : 1, 256, 0, st>>>(g.erow, g.eid, dy, a, db, g.E, H, D);
-  else edge_mix_heads_kernel<T, 1><<<grid ? grid : 1, 256, 0, st>>>(g.erow, g.eid, dy, a, db, g.E, H, D);
+  const int ds = vec ? D / VM : D;
+  int shift = -1;
+  if (is_pow2(ds)) for (shift = 0; (1 << shift) < ds; ++shift) {}
+  const unsigned blocks = grid ? grid : 1;
+#define GK_MIX(VV, HH) \
+  edge_mix_heads_kernel<T, VV, HH><<<blocks, 256, 0, st>>>(g.erow, g.eid, dy, a, db, g.E, H, D, shift)
+  if (vec) {
+    if (H == 1) GK_MIX(VM, 1); else if (H == 2) GK_MIX(VM, 2); else if (H == 4) GK_MIX(VM, 4);
+    else if (H == 8) GK_MIX(VM, 8); else GK_MIX(VM, 0);
+  } else {
+    GK_MIX(1, 0);
+  }
+#undef GK_MIX
   GK_LAUNCHED("edge_mix_heads");
   return GRAPHOP_OK;
 }

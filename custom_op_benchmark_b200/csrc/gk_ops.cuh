@@ -208,29 +208,47 @@ struct EdgeDotAnyOp {
 // node_mul_edge backward, edge half:  dB[eid[k], :] = sum_h dy[eid[k], h] * A[node(k), h, :]
 // (graphop_kernel.cu:84-92).  One thread per (position, D-slot); no reduction across edges.
 // ---------------------------------------------------------------------------------------
-template <typename T, int V>
+// kH: the head count when it is 1, 2, 4 or 8 (all of an edge's loads are then issued before the first use),
+// 0: read it from H.  ds_shift >= 0: D / V is that power of two (no 64-bit division per element).
+template <typename T, int V, int kH>
 __global__ void __launch_bounds__(256)
 edge_mix_heads_kernel(const int32_t* __restrict__ erow, const int32_t* __restrict__ eid, const T* __restrict__ dy,
-                      const T* __restrict__ a, T* __restrict__ db, long long E, int H, int D) {
+                      const T* __restrict__ a, T* __restrict__ db, long long E, int H, int D, int ds_shift) {
   using A = typename AccOf<T>::type;
   const int ds = D / V;
+  const int nh = kH ? kH : H;
   const long long total = E * ds;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-    const long long j = idx / ds;
+    const long long j = ds_shift >= 0 ? (idx >> ds_shift) : idx / ds;
     const int s = (int)(idx - j * ds);
     const int node = __ldg(erow + j);
     if (node < 0) continue;
     const long long e = eid ? (long long)__ldg(eid + j) : j;
+    const T* arow = a + (long long)node * nh * D + s * V;
+    const T* grow = dy + e * nh;
     A acc[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) acc[v] = A(0);
-    for (int h = 0; h < H; ++h) {
-      const A g = to_acc<T>(__ldg(dy + e * H + h));
-      A av[V];
-      load_acc<T, V>(av, a + ((long long)node * H + h) * D + s * V);
+    if constexpr (kH != 0) {
+      A g[kH], av[kH][V];
 #pragma unroll
-      for (int v = 0; v < V; ++v) acc[v] += g * av[v];
+      for (int h = 0; h < kH; ++h) {
+        g[h] = to_acc<T>(__ldg(grow + h));
+        load_acc<T, V>(av[h], arow + (long long)h * D);
+      }
+#pragma unroll
+      for (int h = 0; h < kH; ++h)
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] += g[h] * av[h][v];
+    } else {
+      for (int h = 0; h < nh; ++h) {
+        const A g = to_acc<T>(__ldg(grow + h));
+        A av[V];
+        load_acc<T, V>(av, arow + (long long)h * D);
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] += g * av[v];
+      }
     }
     store_acc<T, V>(db + e * D + s * V, acc);
   }

@@ -266,8 +266,9 @@ extern "C" size_t graphop_workspace_bytes(int op, int64_t n_edges, int64_t n_nod
       need += levels_bytes(E, tile0, 3 * HD * acc);
       break;
     case GRAPHOP_OP_ATTENTION_BWD:
-      need += align_up((size_t)n_nodes * stat_heads(H, (int)acc) * 2 * acc) +
-              align_up((size_t)E * stat_heads(H, (int)acc) * 2 * acc) + levels_bytes(E, tile0, 2 * HD * acc);
+    case GRAPHOP_OP_ATTENTION_BWD_PAIRS:
+      need += align_up((size_t)n_nodes * stat_heads(H, (int)acc) * 2 * acc) + levels_bytes(E, tile0, 2 * HD * acc);
+      if (op == GRAPHOP_OP_ATTENTION_BWD_PAIRS) need += align_up((size_t)E * stat_heads(H, (int)acc) * 2 * acc);
       break;
     default:
       return 0;

@@ -283,7 +283,8 @@ def attention_backward(row, indptr, indices, col, indptr_t, indices_t, q, k, v, 
     if e == 0:
         return [dq.zero_(), dk.zero_(), dv.zero_()]
     with th.cuda.device(q.device):
-        _call("attention_backward", elem, index, _capi.OP_ATTENTION_BWD, e, max(q.size(0), k.size(0)), h, d,
+        op_id = _capi.OP_ATTENTION_BWD if eid_t is None else _capi.OP_ATTENTION_BWD_PAIRS
+        _call("attention_backward", elem, index, op_id, e, max(q.size(0), k.size(0)), h, d,
               q.device, [_p(row), _p(indptr), _p(indices), c, _p(col), _p(indptr_t), _p(eid_t), _p(indices_t), ct, _p(q),
                          _p(k), _p(v), _p(o), _p(lse), _p(d_o), float(scale), _p(dq), _p(dk), _p(dv), e, q.size(0),
                          k.size(0), h, d])

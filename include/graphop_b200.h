@@ -61,7 +61,8 @@ enum {
   GRAPHOP_OP_SPMM_FWD = 6,
   GRAPHOP_OP_SPMM_BWD = 7,
   GRAPHOP_OP_ATTENTION_FWD = 8,
-  GRAPHOP_OP_ATTENTION_BWD = 9
+  GRAPHOP_OP_ATTENTION_BWD = 9,          /* graphop_attention_backward with eid_t == NULL */
+  GRAPHOP_OP_ATTENTION_BWD_PAIRS = 10     /* ... with eid_t: room for (p, ds) of every edge and head */
 };
 
 int graphop_version(void);
