@@ -256,6 +256,7 @@ inline int launch_staged(const Op& op, const GraphView& g, int tile, long long n
   return GRAPHOP_OK;
 }
 
+template <class X> struct TypeTag { using type = X; };
 template <class Op, class = void> struct IsStaged : std::false_type {};
 template <class Op> struct IsStaged<Op, std::void_t<decltype(Op::kEdgeBytes)>> : std::true_type {};
 
@@ -324,13 +325,24 @@ inline int run_aggregate(Arena& ar, const GraphView& g, const T* w, const T* x, 
       constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
       using OpT = typename std::conditional<(V > 1 || sizeof(T) == 16), AggregateStaged<T, V, R, kEdgeFeat>,
                                             AggregateOp<T, V, R, kEdgeFeat>>::type;
-      return run_row_levels(ar, g, tile0, n_rows, sizeof(A), HD, st, [&](void* cout, void* cin) {
-        OpT op;
-        op.w = w; op.x = x; op.y = y; op.carry = (A*)cout; op.carry_in = (const A*)cin;
-        op.H = H; op.D = D; op.HD = HD; op.S = b.S; op.feat0 = feat0;
-        if constexpr (IsStaged<OpT>::value) op.wmode = OpT::pick_wmode(w, H, feat0, HD, block_elems);
-        return op;
-      });
+      int wm = 0;
+      if constexpr (IsStaged<OpT>::value) wm = OpT::pick_wmode(w, H, feat0, HD, block_elems);
+      auto run = [&](auto op_type) -> int {
+        using OpM = typename decltype(op_type)::type;
+        return run_row_levels(ar, g, tile0, n_rows, sizeof(A), HD, st, [&](void* cout, void* cin) {
+          OpM op;
+          op.w = w; op.x = x; op.y = y; op.carry = (A*)cout; op.carry_in = (const A*)cin;
+          op.H = H; op.D = D; op.HD = HD; op.S = b.S; op.feat0 = feat0;
+          if constexpr (IsStaged<OpM>::value) op.wmode = wm;
+          return op;
+        });
+      };
+      if constexpr (IsStaged<OpT>::value) {
+        // the packed-pieces mode (the common one: H * sizeof(T) a multiple of 16) gets its own instantiation
+        using Pieces = AggregateStaged<T, V, R, kEdgeFeat, OpT::kWeightsPieces>;
+        if (wm == OpT::kWeightsPieces) return run(TypeTag<Pieces>{});
+      }
+      return run(TypeTag<OpT>{});
     })));
     if (feat0 + block_elems < HD) ar.used = mark;  // blocks run back to back on one stream: reuse the scratch
   }

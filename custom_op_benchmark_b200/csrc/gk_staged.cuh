@@ -331,7 +331,9 @@ __device__ __forceinline__ void reduce_heads_ct(A (&p)[R], int lph) {
 // ---------------------------------------------------------------------------------------
 // AggregateOp, staged: ring entry = [feature row][weights]
 // ---------------------------------------------------------------------------------------
-template <typename T, int V, int R, bool kEdgeFeat>
+// kMode >= 0: the weight staging mode is known at compile time (the host instantiates the packed-pieces mode
+// that way: no mode tests per edge); -1: read it from `wmode`.
+template <typename T, int V, int R, bool kEdgeFeat, int kMode = -1>
 struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   using Base = AggregateOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
@@ -357,6 +359,7 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   // One scattered copy per edge instead of one per lane is what the packed modes buy.
   enum { kWeightsPerLane = 0, kWeightsWords = 1, kWeightsPieces = 2 };
   int wmode = kWeightsPerLane;
+  __device__ __forceinline__ int mode() const { return kMode >= 0 ? kMode : wmode; }
 
   __host__ static int pick_wmode(const void* w, int H, int feat0, int HD, int block_elems) {
     const bool whole = feat0 == 0 && HD <= block_elems && H <= 32 * R;  // one feature block sees every head
@@ -379,9 +382,9 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
     for (int i = 0; i < R; ++i) {
       cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.xb[i], kEdgeFeat ? e : c, rowb));
       const int j = lane + 32 * i;
-      if (wmode == kWeightsPieces) {
+      if (mode() == kWeightsPieces) {
         if (j * 16 < wbytes) cp_async16(entry + Ring::kRowBytes + j * 16, wrow + j * 16);
-      } else if (wmode == kWeightsWords) {
+      } else if (mode() == kWeightsWords) {
         if constexpr (sizeof(T) >= 4) {
           if (j < this->H)
             cp_async_small<sizeof(T)>(entry + Ring::kRowBytes + j * sizeof(T), wrow + j * sizeof(T));
@@ -407,7 +410,7 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
         A xv[V];
         lds_acc<T, V>(xv, entry + (lane + 32 * i) * 16);
         A wv;
-        if (wmode != kWeightsPerLane) {
+        if (mode() != kWeightsPerLane) {
           wv = to_acc<T>(reinterpret_cast<const T*>(entry + Ring::kRowBytes)[st.sm.head[i]]);
         } else if constexpr (sizeof(T) == 2) {
           const WWord word = reinterpret_cast<const WWord*>(entry + Ring::kRowBytes)[lane + 32 * i];
