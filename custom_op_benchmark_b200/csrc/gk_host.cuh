@@ -338,9 +338,11 @@ inline int run_aggregate(Arena& ar, const GraphView& g, const T* w, const T* x, 
         });
       };
       if constexpr (IsStaged<OpT>::value) {
-        // the packed-pieces mode (the common one: H * sizeof(T) a multiple of 16) gets its own instantiation
+        // the two packed modes get their own instantiations; the per-lane mode keeps the run-time test
         using Pieces = AggregateStaged<T, V, R, kEdgeFeat, OpT::kWeightsPieces>;
+        using Words = AggregateStaged<T, V, R, kEdgeFeat, OpT::kWeightsWords>;
         if (wm == OpT::kWeightsPieces) return run(TypeTag<Pieces>{});
+        if (wm == OpT::kWeightsWords) return run(TypeTag<Words>{});
       }
       return run(TypeTag<OpT>{});
     })));
