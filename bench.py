@@ -57,6 +57,71 @@ WORKLOADS = {
 DTYPES = {"f32": th.float32, "bf16": th.bfloat16, "f64": th.float64}
 
 
+class Twin:
+    """libgraphop_b200_bench.so: the library's sources compiled a second time with launch accounting and a CUDA
+    event behind every kernel (custom_op_benchmark_b200/csrc/bench/graphop_bench.h).  The timed region of the
+    benchmark runs through the product library; the same step is replayed through this twin to split its time
+    over the kernels, to count the launches and to time the gather probe."""
+
+    def __init__(self, path=None):
+        import ctypes
+        from custom_op_benchmark_b200 import _capi
+        path = path or os.path.join(ROOT, "custom_op_benchmark_b200", "libgraphop_b200_bench.so")
+        if not os.path.exists(path):
+            raise ImportError("%s is missing; build it with `python -m custom_op_benchmark_b200.build`" % path)
+        self._capi, self._ct = _capi, ctypes
+        h = _capi.bind(ctypes.CDLL(path), strict=False)
+        P, I64, INT, SZ = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+        h.graphop_bench_launch_count.argtypes, h.graphop_bench_launch_count.restype = [], ctypes.c_longlong
+        h.graphop_bench_profile_begin.argtypes, h.graphop_bench_profile_begin.restype = [P], INT
+        h.graphop_bench_profile_end.argtypes, h.graphop_bench_profile_end.restype = [P, SZ, P, INT], INT
+        h.graphop_bench_gather_probe_i32.argtypes = [P, I64, P, P, INT, P, P]
+        h.graphop_bench_gather_probe_i32.restype = INT
+        self.h = h
+
+    class _Routed:
+        def __init__(self, capi, handle):
+            self.capi, self.handle = capi, handle
+
+        def __enter__(self):
+            self.capi.lib()                      # make sure the product library is what gets restored
+            self.saved, self.capi._lib = self.capi._lib, self.handle
+
+        def __exit__(self, *exc):
+            self.capi._lib = self.saved
+
+    def routed(self):
+        """Context in which the package's ops call the twin instead of the product library."""
+        return Twin._Routed(self._capi, self.h)
+
+    def launch_count(self):
+        return int(self.h.graphop_bench_launch_count())
+
+    def profile(self, fn, stream, max_entries=8192):
+        """Runs fn() through the twin with per-kernel timing on; returns [(kernel name, milliseconds), ...]."""
+        ct = self._ct
+        with self.routed():
+            if self.h.graphop_bench_profile_begin(stream) != 0:
+                raise RuntimeError("graphop_bench_profile_begin failed")
+            try:
+                fn()
+            finally:
+                names = ct.create_string_buffer(64 * max_entries)
+                ms = (ct.c_float * max_entries)()
+                n = self.h.graphop_bench_profile_end(ct.cast(names, ct.c_void_p), len(names),
+                                                     ct.cast(ms, ct.c_void_p), max_entries)
+        if n < 0:
+            raise RuntimeError("graphop_bench_profile_end failed")
+        return list(zip(names.value.decode().split("\n")[:n], [float(v) for v in ms[:n]]))
+
+    def gather_probe(self, idx, t0, t1, row_bytes, sink, stream):
+        rc = self.h.graphop_bench_gather_probe_i32(idx.data_ptr(), idx.numel(), t0.data_ptr(),
+                                                   t1.data_ptr() if t1 is not None else None, row_bytes,
+                                                   sink.data_ptr(), stream)
+        if rc:
+            raise RuntimeError("graphop_bench_gather_probe_i32 failed: %d" % rc)
+
+
 def make_graph(spec, seed, device):
     from custom_op_benchmark_b200 import graphs
     if spec["kind"] == "rmat":
@@ -145,9 +210,9 @@ class Workload:
         per_edge = sum(t[0].numel() * t.element_size() for t in tables) * self.e
         return self.alg[kernel] - once + per_edge
 
-    def gather_floor(self, lib, reps=5):
-        """Milliseconds of graphop_gather_probe_i32 (the gathers alone, nothing done with the rows) for every
-        kernel of gather_streams() whose rows are at most 512 bytes; {} when there is none."""
+    def gather_floor(self, twin, reps=5):
+        """Milliseconds of graphop_bench_gather_probe_i32 (the gathers alone, nothing done with the rows) for
+        every kernel of gather_streams() whose rows are at most 512 bytes; {} when there is none."""
         out = {}
         sink = th.zeros(1, dtype=th.int32, device=self.dev)
         stream = th.cuda.current_stream().cuda_stream
@@ -157,11 +222,7 @@ class Workload:
                 continue
 
             def go():
-                rc = lib.graphop_gather_probe_i32(idx.data_ptr(), idx.numel(), t0.data_ptr(),
-                                                  t1.data_ptr() if t1 is not None else None, row_bytes,
-                                                  sink.data_ptr(), stream)
-                if rc:
-                    raise RuntimeError("graphop_gather_probe_i32 failed: %d" % rc)
+                twin.gather_probe(idx, t0, t1, row_bytes, sink, stream)
             for _ in range(3):
                 go()
             a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
@@ -185,7 +246,6 @@ class AttentionWorkload(Workload):
         self.Q, self.K, self.V, self.dO = (t.to(dev) for t in self.host)
         self.scale = d ** -0.5
         self.outs = [th.empty_like(t).pin_memory() for t in (self.host[0], self.host[0], self.host[1], self.host[2])]
-        self.stage = [th.empty_like(t) for t in (self.Q, self.K, self.V, self.dO)]
         z = self.sizes()
         self.alg = {
             # q, k, v read, o written, indices, lse written
@@ -214,17 +274,26 @@ class AttentionWorkload(Workload):
         return graphop.attention_backward(R[0], R[1], R[3], C[0], C[1], C[3], self.Q, self.K, self.V, self.o, self.lse,
                                           self.dO, self.scale, eid_t=C[2])
 
-    def e2e_step(self):
+    def max_err(self):
+        from oracle import edge_list_f64 as ref
+        self.forward()
+        got = [self.o, self.lse] + list(self.backward())
+        want = ref.attention_f64(self.g.indptr, self.g.indices, self.Q, self.K, self.V, self.scale, self.dO)
+        out = {}
+        for name, a, b in zip(("o", "lse", "dq", "dk", "dv"), got, want):
+            keep = th.isfinite(b)
+            out[name] = ref.max_err(a[keep], b[keep])[0]
+        return dict(out, max_err=max(out.values()),
+                    what="every element of O, lse, dQ, dK, dV of one step against the float64 edge-list reference "
+                         "on the same inputs, |x - ref| / (1 + |ref|)")
+
+    def e2e_compute(self, stage):
         from custom_op_benchmark_b200 import wrapper
         R, C = self.R, self.C
-        q, k, v = (b.copy_(hst, non_blocking=True).requires_grad_(True)
-                   for b, hst in zip(self.stage[:3], self.host[:3]))
-        go = self.stage[3].copy_(self.host[3], non_blocking=True)
+        q, k, v = (t.detach().requires_grad_(True) for t in stage[:3])
         out = wrapper.GraphAttention.apply(R[0], R[1], R[3], C[0], C[1], C[3], q, k, v, self.scale, C[2])
-        out.backward(go)
-        for dst, src in zip(self.outs, (out.detach(), q.grad, k.grad, v.grad)):
-            dst.copy_(src, non_blocking=True)
-        self._release(self.stage[:3])
+        out.backward(stage[3])
+        return [out.detach(), q.grad, k.grad, v.grad]
 
 
 class GatWorkload(Workload):
@@ -240,7 +309,6 @@ class GatWorkload(Workload):
         w = graphop.sparse_softmax_forward(*self.R[:3], raw)          # sparse_softmax-normalised weights
         self.host = [self._host(n, h, d), self._host(e, d), w.cpu().pin_memory(), self._host(e, h), self._host(n, h, d)]
         self.X, self.Be, self.w, self.dY1, self.dY2 = (t.to(dev) for t in self.host)
-        self.stage = [th.empty_like(t) for t in (self.X, self.Be, self.w, self.dY1, self.dY2)]
         self.outs = [th.empty(s, dtype=self.dtype).pin_memory() for s in ((e, h), (n, h, d), (e, d), (n, h, d), (e, h))]
         z = self.sizes()
         gather = 2 * z["F_dst"] + z["S"] + z["I"]
@@ -262,18 +330,24 @@ class GatWorkload(Workload):
         b = graphop.vector_spmm_backward(*self.R, *self.C, self.w, self.dY2, self.X)
         return a + b
 
-    def e2e_step(self):
+    def max_err(self):
+        from oracle import edge_list_f64 as ref
+        self.forward()
+        da, dbe, dw, dx = self.backward()
+        want = ref.gat_f64(self.g.indptr, self.g.indices, self.X, self.Be, self.w, self.dY1, self.dY2)
+        got = (self.y1, self.y2, da + dx, dbe, dw)     # X feeds both ops: its gradient is the sum of the two
+        out = {name: ref.max_err(a, b)[0] for name, a, b in zip(("y1", "y2", "dX", "dBe", "dw"), got, want)}
+        return dict(out, max_err=max(out.values()),
+                    what="every element of both outputs and the three gradients against the float64 edge-list "
+                         "reference, |x - ref| / (1 + |ref|)")
+
+    def e2e_compute(self, stage):
         from custom_op_benchmark_b200 import wrapper
-        x, be, w = (b.copy_(hst, non_blocking=True).requires_grad_(True)
-                    for b, hst in zip(self.stage[:3], self.host[:3]))
-        g1 = self.stage[3].copy_(self.host[3], non_blocking=True)
-        g2 = self.stage[4].copy_(self.host[4], non_blocking=True)
+        x, be, w = (t.detach().requires_grad_(True) for t in stage[:3])
         y1 = wrapper.NodeMulEdge.apply(*self.R[:3], x, be)
         y2 = wrapper.VectorSPMM.apply(*self.R, *self.C, w, x)
-        th.autograd.backward([y1, y2], [g1, g2])
-        for dst, src in zip(self.outs, (y1.detach(), y2.detach(), be.grad, x.grad, w.grad)):
-            dst.copy_(src, non_blocking=True)
-        self._release(self.stage[:3])
+        th.autograd.backward([y1, y2], [stage[3], stage[4]])
+        return [y1.detach(), y2.detach(), be.grad, x.grad, w.grad]
 
 
 class SddmmSoftmaxWorkload(Workload):
@@ -285,7 +359,6 @@ class SddmmSoftmaxWorkload(Workload):
         n, m, h, d, e = self.n_dst, self.n_src, self.h, self.d, self.e
         self.host = [self._host(n, h, d, mag=3.0), self._host(m, h, d, mag=3.0), self._host(e, h)]
         self.Q, self.K, self.dP = (t.to(dev) for t in self.host)
-        self.stage = [th.empty_like(t) for t in (self.Q, self.K, self.dP)]
         self.outs = [th.empty(s, dtype=self.dtype).pin_memory() for s in ((e, h), (n, h, d), (m, h, d))]
         z = self.sizes()
         gather = z["F_dst"] + z["F_src"] + z["S"] + z["I"]
@@ -306,23 +379,62 @@ class SddmmSoftmaxWorkload(Workload):
         ds = graphop.sparse_softmax_backward(*self.R[:3], self.p, self.dP)
         return graphop.maskedmm_csr_backward(*self.R, *self.C, self.Q, self.K, ds)
 
-    def e2e_step(self):
+    def max_err(self):
+        from oracle import edge_list_f64 as ref
+        self.forward()
+        dq, dk = self.backward()
+        want = ref.sddmm_softmax_f64(self.g.indptr, self.g.indices, self.Q, self.K, self.dP)
+        out = {name: ref.max_err(a, b)[0] for name, a, b in zip(("s", "p", "dq", "dk"), (self.s, self.p, dq, dk), want)}
+        return dict(out, max_err=max(out.values()),
+                    what="every score, probability and gradient element against the float64 edge-list reference, "
+                         "|x - ref| / (1 + |ref|)")
+
+    def e2e_compute(self, stage):
         from custom_op_benchmark_b200 import wrapper
-        q, k = (b.copy_(hst, non_blocking=True).requires_grad_(True) for b, hst in zip(self.stage[:2], self.host[:2]))
-        gp = self.stage[2].copy_(self.host[2], non_blocking=True)
+        q, k = (t.detach().requires_grad_(True) for t in stage[:2])
         s = wrapper.MaskedMMCSR.apply(*self.R, *self.C, q, k)
         p = wrapper.SparseSoftmax.apply(*self.R[:3], s)
-        p.backward(gp)
-        for dst, src in zip(self.outs, (p.detach(), q.grad, k.grad)):
-            dst.copy_(src, non_blocking=True)
-        self._release(self.stage[:2])
+        p.backward(stage[2])
+        return [p.detach(), q.grad, k.grad]
+
+
+def sharding_local_indptr(row, indptr_, n_rows):
+    """Plain CSR indptr (n_rows + 1, int64) of a shard from its chunk table (row, indptr_)."""
+    cnt = th.zeros(n_rows, dtype=th.int64, device=row.device)
+    ip = indptr_.to(th.int64)
+    cnt.index_add_(0, row.to(th.int64), ip[1:] - ip[:-1])
+    out = th.zeros(n_rows + 1, dtype=th.int64, device=row.device)
+    th.cumsum(cnt, 0, out=out[1:])
+    return out + int(ip[0]) if ip.numel() else out
+
+
+def hashed_uniform(ids, cols, seed):
+    """(len(ids), cols) float32 in (0, 1), a pure function of (id, column, seed): any rank can reproduce any
+    row of a sharded tensor without holding it (a 32-bit integer mixer over int64 torch ops)."""
+    c = th.arange(cols, device=ids.device, dtype=th.int64).view(1, -1)
+    x = (ids.to(th.int64).view(-1, 1) * 2654435761 + c * 40503 + (seed * 7919 + 12345)) & 0xFFFFFFFF
+    for _ in range(2):
+        x = ((x ^ (x >> 16)) * 0x45D9F3B) & 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    return (x.to(th.float32) + 0.5) * (1.0 / 4294967296.0)
+
+
+def hashed_normal(ids, cols, seed, chunk=1 << 20):
+    """(len(ids), cols) float32 ~ N(0, 1) by Box-Muller over two hashed uniforms; rows computed in chunks."""
+    out = th.empty(ids.numel(), cols, dtype=th.float32, device=ids.device)
+    for lo in range(0, ids.numel(), chunk):
+        part = ids[lo:lo + chunk]
+        u1, u2 = hashed_uniform(part, cols, 2 * seed), hashed_uniform(part, cols, 2 * seed + 1)
+        out[lo:lo + chunk] = th.sqrt(-2.0 * th.log(u1)) * th.cos(6.283185307179586 * u2)
+    return out
 
 
 class ShardedSpmmWorkload:
     """vector_spmm forward + backward over a graph row-partitioned across the ranks (sharding.py).
     Every rank generates the same seeded graph and keeps its own shard."""
     name = "vector_spmm forward + backward, destination rows sharded over the ranks"
-    resident = "graph shard and edge weights; e2e copies this rank's x shard and dy rows in, y rows and dx rows out"
+    resident = "graph shard and this rank's edge weights; e2e copies this rank's x shard and dy rows in, y rows " \
+               "and dx rows out; the weights of the transposed shard's edges are exchanged every step"
     scaling = "strong"
 
     def __init__(self, spec, rank, dev, world):
@@ -336,16 +448,15 @@ class ShardedSpmmWorkload:
         self.ex = sharding.plan_shard_exchange(sh) if (world > 1 and spec.get("exchange", "needed") == "needed") else None
         del g
         th.cuda.empty_cache()
-        gen = th.Generator(device=dev).manual_seed(7)     # edge weights by global edge id, same on every rank
-        self.w_all = th.rand(self.e, generator=gen, device=dev)
-        lo = sh.edge_lo
-        self.w_local = self.w_all[lo:lo + sh.indices.numel()].contiguous()
+        # every input is a pure function of its global id (edge id, source node, destination node), so that any
+        # rank can rebuild the rows it needs for checking; a rank holds only its own rows and its own edges' weights
+        ar = lambda lo, n: th.arange(lo, lo + n, device=dev, dtype=th.int64)
+        self.w_local = hashed_uniform(ar(sh.edge_lo, sh.indices.numel()), 1, 7).view(-1)
         xb = sharding.even_bounds(self.n_src, world)
         rows_x = int(xb[rank + 1] - xb[rank])
-        hgen = th.Generator().manual_seed(1000 + rank)
-        self.host = [_pinned(th.randn(rows_x, self.d, generator=hgen)), _pinned(th.randn(sh.rows, self.d, generator=hgen))]
-        self.x_shard, self.dy_local = (t.to(dev) for t in self.host)
-        self.stage = [th.empty_like(self.x_shard), th.empty_like(self.dy_local)]
+        self.x_shard = hashed_normal(ar(int(xb[rank]), rows_x), self.d, 11)
+        self.dy_local = hashed_normal(ar(int(sh.dst_bounds[rank]), sh.rows), self.d, 13)
+        self.host = [_pinned(self.x_shard.cpu()), _pinned(self.dy_local.cpu())]
         self.outs = [_pinned(th.empty(sh.rows, self.d)), _pinned(th.empty(sh.cols, self.d))]
         s, i = 4, 4
         e_loc, e_t = sh.indices.numel(), sh.eid_t.numel()
@@ -366,20 +477,62 @@ class ShardedSpmmWorkload:
 
     def backward(self):
         from custom_op_benchmark_b200 import sharding
-        return sharding.sharded_spmm_backward(self.sh, self.w_local, self.dy_local, self.x_all, self.w_all,
-                                              exchange=self.ex)
+        return sharding.sharded_spmm_backward(self.sh, self.w_local, self.dy_local, self.x_all, exchange=self.ex)
 
-    def e2e_step(self):
+    def e2e_compute(self, stage):
         from custom_op_benchmark_b200 import sharding
-        x = self.stage[0].copy_(self.host[0], non_blocking=True)
-        dy = self.stage[1].copy_(self.host[1], non_blocking=True)
-        y, x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, x, exchange=self.ex)
-        _, dx = sharding.sharded_spmm_backward(self.sh, self.w_local, dy, x_all, self.w_all, exchange=self.ex)
-        self.outs[0].copy_(y, non_blocking=True)
-        self.outs[1].copy_(dx, non_blocking=True)
+        y, x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, stage[0], exchange=self.ex)
+        _, dx = sharding.sharded_spmm_backward(self.sh, self.w_local, stage[1], x_all, exchange=self.ex)
+        return [y, dx]
 
     def e2e_bytes(self):
         return _nbytes(self.host), _nbytes(self.outs)
+
+    def max_err(self, count=4000):
+        """Sampled rows of this rank's y, dedata and dx against a float64 reference built from the hashed inputs
+        (any row of x, dy or w is recomputed from its global id, so the exchanges are checked too)."""
+        from oracle import edge_list_f64 as ref
+        from custom_op_benchmark_b200 import sharding
+        sh, dev, d = self.sh, self.dev, self.d
+        self.forward()
+        dedata, dx = self.backward()
+        errs = {}
+        # y and dedata: sampled local destination rows, their edges' global sources
+        ip = sharding_local_indptr(sh.row, sh.indptr, sh.rows)
+        rows = ref.pick_rows(ip, count=count)
+        pos, local = ref.edges_of_rows(ip, rows)
+        src = sh.indices.index_select(0, pos).to(th.int64)
+        uniq, inv = th.unique(src, return_inverse=True)
+        x_rows = hashed_normal(uniq, d, 11).to(th.float64)
+        w = hashed_uniform(pos + sh.edge_lo, 1, 7).view(-1).to(th.float64)
+        want_y = th.zeros(rows.numel(), d, dtype=th.float64, device=dev)
+        for lo in range(0, pos.numel(), 1 << 20):
+            sl = slice(lo, lo + (1 << 20))
+            want_y.index_add_(0, local[sl], w[sl].view(-1, 1) * x_rows.index_select(0, inv[sl]))
+        errs["y"] = ref.max_err(self.y.index_select(0, rows), want_y)[0]
+        dy_rows = hashed_normal(rows + int(sh.dst_bounds[sh.rank]), d, 13).to(th.float64)
+        want_dw = th.empty(pos.numel(), dtype=th.float64, device=dev)
+        for lo in range(0, pos.numel(), 1 << 20):
+            sl = slice(lo, lo + (1 << 20))
+            want_dw[sl] = (dy_rows.index_select(0, local[sl]) * x_rows.index_select(0, inv[sl])).sum(-1)
+        errs["dedata"] = ref.max_err(dedata.view(-1).index_select(0, pos), want_dw)[0]
+        # dx: sampled owned source rows of the transposed shard, weights by global edge id, dy by global node id
+        ipt = sharding_local_indptr(sh.col, sh.indptr_t, sh.cols)
+        cols = ref.pick_rows(ipt, count=count, seed=1)
+        pos, local = ref.edges_of_rows(ipt, cols)
+        dst = sh.indices_t.index_select(0, pos).to(th.int64)
+        uniq, inv = th.unique(dst, return_inverse=True)
+        g_rows = hashed_normal(uniq, d, 13).to(th.float64)
+        w = hashed_uniform(sh.eid_t.index_select(0, pos).to(th.int64), 1, 7).view(-1).to(th.float64)
+        want_dx = th.zeros(cols.numel(), d, dtype=th.float64, device=dev)
+        for lo in range(0, pos.numel(), 1 << 20):
+            sl = slice(lo, lo + (1 << 20))
+            want_dx.index_add_(0, local[sl], w[sl].view(-1, 1) * g_rows.index_select(0, inv[sl]))
+        errs["dx"] = ref.max_err(dx.index_select(0, cols), want_dx)[0]
+        return dict(errs, max_err=max(errs.values()),
+                    what="%d sampled rows of y (and their edges' dedata) and of dx per rank, incl. the 32 longest rows, "
+                         "empty rows and the last row, float64 reference rebuilt from the inputs' generating function, "
+                         "|x - ref| / (1 + |ref|)" % count)
 
     def collectives(self, reps=3):
         """Milliseconds of the two exchanges of one step, each timed alone on this rank (all ranks call this
@@ -518,9 +671,154 @@ def traffic_for(kernel, workload):
     return None
 
 
-def run_gpu(args):
-    from custom_op_benchmark_b200 import _capi
+def build_workload(args, spec, rank, dev, world):
+    if args.scale and spec["kind"] == "rmat":
+        spec["scale"] = args.scale
+    if spec["ops"] == "sharded_spmm":
+        spec["exchange"] = args.exchange
+        return ShardedSpmmWorkload(spec, rank, dev, world)
+    return WORKLOAD_CLASSES[spec["ops"]](spec, rank, dev)
 
+
+def time_steps(wl, steps, world):
+    """K steps with inputs resident, CUDA events on the launching stream, a barrier and a device
+    synchronisation on both sides.  Returns (total ms, mean forward ms, mean backward ms, wall t0, wall t1)."""
+    if world > 1:
+        dist.barrier()
+    th.cuda.synchronize()
+    ev = [th.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1)]
+    t0 = time.time()
+    ev[0].record()
+    for i in range(steps):
+        wl.forward()
+        ev[2 * i + 1].record()
+        wl.backward()
+        ev[2 * i + 2].record()
+    th.cuda.synchronize()
+    t1 = time.time()
+    if world > 1:
+        dist.barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    fwd_ms = statistics.mean(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(steps))
+    bwd_ms = statistics.mean(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(steps))
+    return total_ms, fwd_ms, bwd_ms, t0, t1
+
+
+class EndToEnd:
+    """The step through the public API with host buffers: every step copies all of its inputs from pinned host
+    memory to the device and all of its results back.  Three streams: the copies in, the compute (the stream the
+    autograd Functions are called on) and the copies out, with two sets of device staging buffers, so that step
+    i + 1's inputs travel while step i computes and step i - 1's results travel back (PCIe is full duplex).
+    Nothing is skipped and nothing is reused between steps."""
+
+    def __init__(self, wl, dev):
+        self.wl = wl
+        self.stage = [[th.empty(h.shape, dtype=h.dtype, device=dev) for h in wl.host] for _ in range(2)]
+        self.s_in, self.s_out = th.cuda.Stream(dev), th.cuda.Stream(dev)
+        self.free = [None, None]
+
+    def run(self, steps):
+        wl, cur = self.wl, th.cuda.current_stream()
+        self.s_in.wait_stream(cur)
+        for i in range(steps):
+            b = i & 1
+            with th.cuda.stream(self.s_in):
+                if self.free[b] is not None:
+                    self.s_in.wait_event(self.free[b])      # the step that last used these buffers is done
+                for dst, src in zip(self.stage[b], wl.host):
+                    dst.copy_(src, non_blocking=True)
+                arrived = th.cuda.Event()
+                arrived.record(self.s_in)
+            cur.wait_event(arrived)
+            outs = wl.e2e_compute(self.stage[b])
+            done = th.cuda.Event()
+            done.record(cur)
+            self.free[b] = done
+            for t in outs:
+                t.record_stream(self.s_out)
+            with th.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                for dst, src in zip(wl.outs, outs):
+                    dst.copy_(src, non_blocking=True)
+            del outs
+        cur.wait_stream(self.s_out)
+
+    def time(self, steps, world):
+        self.run(2)
+        th.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+        a.record()
+        self.run(steps)
+        b.record()
+        th.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+
+def kernel_breakdown(wl, twin, prof_steps):
+    """Per-kernel device time of the step replayed through the instrumented twin, and its launches per step."""
+    def step_device():
+        wl.forward()
+        return wl.backward()
+    with twin.routed():
+        step_device()            # settle the allocator before timing
+    th.cuda.synchronize()
+    n0 = twin.launch_count()
+
+    def profiled():
+        for _ in range(prof_steps):   # results dropped at once: kept alive they would force fresh cudaMallocs
+            step_device()
+    recs = twin.profile(profiled, th.cuda.current_stream().cuda_stream)
+    launches = (twin.launch_count() - n0) / prof_steps
+    per_kernel = {}
+    for name, ms in recs:
+        per_kernel.setdefault(name, []).append(ms)
+    return {k: {"launches_per_step": len(v) / prof_steps, "ms_per_step": sum(v) / prof_steps}
+            for k, v in per_kernel.items()}, launches
+
+
+def sharded_extra(args, rank, dev, world):
+    """The one configuration that is cut over the GPUs (R-MAT scale 24 vector SpMM, rows sharded by destination,
+    strong scaling), run beside the headline workload at every N so that a scaling run carries a curve with
+    communication in its data path.  Returns a dict on rank 0, None elsewhere."""
+    spec = dict(WORKLOADS["rmat24_spmm"])
+    if args.sharded_scale:
+        spec["scale"] = args.sharded_scale
+    spec["exchange"] = args.exchange
+    free_b, _ = th.cuda.mem_get_info(dev)
+    need = (1 << spec["scale"]) * (spec["edge_factor"] * 40 + 128 * 4 * 5)      # graph build + node tensors, generous
+    if free_b < need:
+        return {"skipped": "needs about %.0f GB of device memory, %.0f GB free" % (need / 1e9, free_b / 1e9)} \
+            if rank == 0 else None
+    wl = ShardedSpmmWorkload(spec, rank, dev, world)
+    steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        wl.forward()
+        wl.backward()
+    total_ms, fwd_ms, bwd_ms, _, _ = time_steps(wl, steps, world)
+    coll = wl.collectives()
+    err = wl.max_err()
+    stats = th.tensor([total_ms, fwd_ms, bwd_ms, err["max_err"]], dtype=th.float64, device=dev)
+    work = th.tensor([wl.units()], dtype=th.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    total_ms, fwd_ms, bwd_ms, worst = stats.tolist()
+    out = None
+    if rank == 0:
+        ms = total_ms / steps
+        out = {"workload": "rmat24_spmm" if spec["scale"] == 24 else "rmat%d_spmm" % spec["scale"],
+               "ops": wl.name, "scaling": "strong", "n_gpus": world, "nodes": wl.n_dst, "edges": wl.e, "dim": wl.d,
+               "steps": steps, "ms_per_step": ms, "forward_ms": fwd_ms, "backward_ms": bwd_ms,
+               "value": work.item() / (ms * 1e-3), "unit": UNIT, "max_err": worst, "max_err_what": err["what"],
+               "exchange": coll}
+    del wl
+    th.cuda.empty_cache()
+    return out
+
+
+def run_gpu(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -531,14 +829,7 @@ def run_gpu(args):
     dev = th.device("cuda", local)
     th.cuda.set_device(dev)
     spec = dict(WORKLOADS[args.workload])
-    if args.scale and spec["kind"] == "rmat":
-        spec["scale"] = args.scale
-    if spec["ops"] == "sharded_spmm":
-        spec["exchange"] = args.exchange
-        wl = ShardedSpmmWorkload(spec, rank, dev, world)
-    else:
-        wl = WORKLOAD_CLASSES[spec["ops"]](spec, rank, dev)
-    lib = _capi.lib()
+    wl = build_workload(args, spec, rank, dev, world)
 
     def step_device():
         wl.forward()
@@ -559,31 +850,13 @@ def run_gpu(args):
         print(json.dumps({"lean": True, "workload": args.workload, "edges": wl.e, "nodes": wl.n_dst, "heads": wl.h,
                           "dim": wl.d, "ms_per_step": a.elapsed_time(b) / args.steps}))
         return
+    twin = Twin()
 
-    # -- timed region: K steps, inputs resident, CUDA events on the launching stream ----------
+    # -- timed region: K steps through the product library, inputs resident ---------------------
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.3)
-    if world > 1:
-        dist.barrier()
-    th.cuda.synchronize()
-    ev = [th.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
-    launches0 = lib.graphop_launch_count()
-    t_wall0 = time.time()
-    ev[0].record()
-    for i in range(args.steps):
-        wl.forward()
-        ev[2 * i + 1].record()
-        wl.backward()
-        ev[2 * i + 2].record()
-    th.cuda.synchronize()
-    t_wall1 = time.time()
-    launches = lib.graphop_launch_count() - launches0
-    if world > 1:
-        dist.barrier()
-    total_ms = ev[0].elapsed_time(ev[-1])
-    fwd_ms = statistics.mean(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps))
-    bwd_ms = statistics.mean(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps))
+    total_ms, fwd_ms, bwd_ms, t_wall0, t_wall1 = time_steps(wl, args.steps, world)
     if t_wall1 - t_wall0 < 0.6:   # a short timed region: keep the same load up until the sampler has a few rows
         t_end = time.time() + 0.7
         while time.time() < t_end:
@@ -594,33 +867,11 @@ def run_gpu(args):
     clocks = sampler.summary(t_wall0, t_wall1)
 
     # -- end to end: the autograd Functions a user calls, host buffers copied in and out every step
-    e2e_steps = max(2, min(args.steps, 5))
-    wl.e2e_step()
-    th.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(e2e_steps):
-        wl.e2e_step()
-    b.record()
-    th.cuda.synchronize()
-    e2e_ms = a.elapsed_time(b) / e2e_steps
+    e2e_ms = EndToEnd(wl, dev).time(max(3, min(args.steps, 6)), world)
+    th.cuda.empty_cache()
 
-    # -- per-kernel times of the same step, CUDA events behind every kernel ---------------------
-    per_kernel = {}
-    prof_steps = max(2, min(args.steps, 5))
-    step_device()            # the e2e loop left the allocator in another state: settle it before timing
-    th.cuda.synchronize()
-    def profiled():
-        for _ in range(prof_steps):   # results dropped at once: kept alive they would force fresh cudaMallocs
-            step_device()
-
-    recs = _capi.profile(profiled, th.cuda.current_stream().cuda_stream)
-    for name, ms in recs:
-        per_kernel.setdefault(name, []).append(ms)
-    kernels = {k: {"launches_per_step": len(v) / prof_steps, "ms_per_step": sum(v) / prof_steps}
-               for k, v in per_kernel.items()}
+    # -- per-kernel times and launch count of the same step, through the instrumented twin -------
+    kernels, launches_per_step = kernel_breakdown(wl, twin, max(2, min(args.steps, 5)))
 
     # -- the same step replayed from a CUDA graph (what is left when launch latency is taken out) --
     graph_ms = None
@@ -628,7 +879,7 @@ def run_gpu(args):
         graph_ms = replay_from_graph(step_device, args.steps)
 
     # -- the gathers alone, same index streams and tables (a floor for the walker kernels) ------
-    floors = wl.gather_floor(lib) if rank == 0 and hasattr(wl, "gather_floor") else {}
+    floors = wl.gather_floor(twin) if rank == 0 and hasattr(wl, "gather_floor") else {}
     # -- the collectives of a sharded step, timed alone (per-kernel events count them with the kernel after them)
     coll = wl.collectives() if hasattr(wl, "collectives") else None
 
@@ -641,6 +892,7 @@ def run_gpu(args):
     total_ms, e2e_ms, fwd_ms, bwd_ms = stats.tolist()
     units = work.item()  # edges*heads of all ranks, per step
 
+    out = None
     if rank == 0:
         alg = wl.alg
         top = max((k for k in kernels if k in alg), key=lambda k: kernels[k]["ms_per_step"])
@@ -663,8 +915,10 @@ def run_gpu(args):
                            in_bytes / 1e9, "larger than" if in_bytes > 2 * 126e6 else "NOT larger than"),
                        "resident": wl.resident},
             "e2e": {"value": units / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(launches),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "how": "pinned host buffers, copies in / compute / copies out on three streams, two staging sets"},
+            "gpu_launches": int(round(launches_per_step * args.steps)),
+            "gpu_launches_per_step": launches_per_step,
             "clocks": clocks,
             "phases": {"forward_ms": fwd_ms, "backward_ms": bwd_ms},
             "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -676,24 +930,38 @@ def run_gpu(args):
                          "step_frac": wl.alg_step / (ms_per_step * 1e-3) / 1e9 / peak},
             "kernels": kernels,
         }
+        traffic_step = sum(traffic_for(k, args.workload) or 0 for k in kernels)
+        if traffic_step:
+            out["roofline"]["step_dram_traffic"] = traffic_step
+            out["roofline"]["step_dram_frac"] = traffic_step / (ms_per_step * 1e-3) / 1e9 / peak
         if graph_ms is not None:
             out["cuda_graph"] = graph_ms if isinstance(graph_ms, dict) else {
                 "ms_per_step": graph_ms, "value": units / (graph_ms * 1e-3), "unit": UNIT,
                 "note": "one forward + backward captured with torch.cuda.graph and replayed; same kernels, no host "
                         "launch latency"}
         if coll:
-            out["exchange"] = dict(coll, note="the NCCL exchanges of the sharded step timed alone on rank 0; inside the "
-                                              "step the per-kernel events charge them to the kernel that follows "
-                                              "(expand_rows), and the dy exchange overlaps the dedata kernel")
+            out["exchange"] = dict(coll, note="the exchanges of the sharded step timed alone on rank 0; inside the "
+                                              "step the per-kernel events charge them to the kernel that follows, "
+                                              "and the dy exchange overlaps the dedata kernel")
         if floors:
             out["gather_floor"] = {
-                "what": "graphop_gather_probe_i32: one row per edge per operand read through the kernel's own index "
-                        "stream, nothing done with the rows",
+                "what": "graphop_bench_gather_probe_i32: one row per edge per operand read through the kernel's own "
+                        "index stream, nothing done with the rows",
                 "ms": floors,
                 "kernel_over_floor": {k: kernels[k]["ms_per_step"] / max(1.0, kernels[k]["launches_per_step"]) / v
                                       for k, v in floors.items() if k in kernels}}
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(spec, args.cpu_sample_scale)
+            # the checker's other job: the same step's results against the float64 edge-list reference
+            out["max_err"] = wl.max_err()
+    # -- the sharded configuration beside the headline one (strong scaling, communication in the data path)
+    if args.sharded != "off" and spec["ops"] != "sharded_spmm":
+        del wl
+        th.cuda.empty_cache()
+        extra = sharded_extra(args, rank, dev, world)
+        if rank == 0:
+            out["sharded"] = extra
+    if rank == 0:
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
@@ -720,40 +988,147 @@ def cpu_baseline(spec, sample_scale):
     else:
         g = graphs.zipf_graph(spec["n"] // 25, spec["total"] // 25, cap=spec["total"] // 25, seed=0)
         sample = "the same degree law at 1/25 of the nodes and edges"
-    sec = cb.time_workload(spec["ops"], g, h, d)
+    ops = "gat" if spec["ops"] == "gat" else ("sddmm_softmax" if spec["ops"] == "sddmm_softmax" else "attention")
+    sec = cb.time_workload(ops, g, h, d)
     return {"value": g.n_edges * h / sec, "unit": UNIT, "cores": th.get_num_threads(), "host_cpus": os.cpu_count(),
             "kind": "port", "seconds": sec,
             "sample": sample + "; torch CPU fp32, forward + backward through autograd"}
 
 
+def reference_cuda(spec, graph, steps=3):
+    """The reference's own CUDA extension (oracle/_ref, built unmodified from graphop/graphop.cpp and
+    graphop/graphop_kernel.cu) timed on this box's GPU: the same ops on the same graph, int64 chunk tables of
+    partition_csr(32) as its contract wants, CUDA events, one untimed step first.  Sizes are limited to what its
+    32-bit index arithmetic allows (graphop_kernel.cu:49, 144: (h * d) * n must stay below 2^31)."""
+    if not th.cuda.is_available():
+        return {"unavailable": "no CUDA device"}
+    try:
+        from oracle.build_reference import load_reference
+        ref = load_reference()
+    except Exception as exc:  # a build made for another torch
+        return {"unavailable": "oracle/_ref does not load: %s" % str(exc)[:120]}
+    if ref is None:
+        return {"unavailable": "oracle/_ref holds no build of the reference"}
+    from custom_op_benchmark_b200.part_csr import partition_csr
+    h, d, ops = spec["heads"], spec["dim"], spec["ops"]
+    if ops not in ("attention", "gat", "sddmm_softmax"):
+        return {"unavailable": "not run on this workload"}
+    if spec["dtype"] != "f32":
+        return {"unavailable": "the reference has no %s kernels (AT_DISPATCH_FLOATING_TYPES)" % spec["dtype"]}
+    dev = th.device("cuda", 0)
+    g = graph.to(device=dev, dtype=th.int64)
+    n, m, e = g.n_dst, g.n_src, g.n_edges
+    if h * d * max(n, m) >= 2 ** 31 or n != m:
+        return {"unavailable": "(h * d) * n overflows the reference's int arithmetic at this size"}
+    row, ptr = partition_csr(g.indptr, 32)
+    col, ptr_t = partition_csr(g.indptr_t, 32)
+    R, C = [row, ptr, g.eid, g.indices], [col, ptr_t, g.eid_t, g.indices_t]
+    gen = th.Generator(device=dev).manual_seed(1)
+    rn = lambda *s: th.randn(*s, generator=gen, device=dev)
+    times = {}
+
+    def timed(name, fn):
+        a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn()
+        b.record()
+        times.setdefault(name, []).append((a, b))
+        return out
+
+    if ops == "attention":
+        Q, K, V, dO, scale = rn(n, h, d), rn(m, h, d), rn(m, h, d), rn(n, h, d), d ** -0.5
+
+        def step():
+            s = timed("maskedmm_fwd", lambda: ref.maskedmm_csr_forward(*R, Q, K))
+            p = timed("softmax_fwd", lambda: ref.sparse_softmax_forward(*R[:3], s * scale))
+            timed("spmm_fwd", lambda: ref.vector_spmm_forward(*R, p, V))
+            dp, _ = timed("spmm_bwd", lambda: ref.vector_spmm_backward(*R, *C, p, dO, V))
+            ds = timed("softmax_bwd", lambda: ref.sparse_softmax_backward(*R[:3], p, dp))
+            timed("maskedmm_bwd", lambda: ref.maskedmm_csr_backward(*R, *C, Q, K, ds * scale))
+    elif ops == "gat":
+        X, Be, w, dY1, dY2 = rn(n, h, d), rn(e, d), th.rand(e, h, generator=gen, device=dev), rn(e, h), rn(n, h, d)
+
+        def step():
+            timed("node_mul_edge_fwd", lambda: ref.node_mul_edge_forward(*R[:3], X, Be))
+            timed("spmm_fwd", lambda: ref.vector_spmm_forward(*R, w, X))
+            timed("node_mul_edge_bwd", lambda: ref.node_mul_edge_backward(*R[:3], X, Be, dY1))
+            timed("spmm_bwd", lambda: ref.vector_spmm_backward(*R, *C, w, dY2, X))
+    else:
+        Q, K, dP = rn(n, h, d) * 3, rn(m, h, d) * 3, rn(e, h)
+
+        def step():
+            s = timed("maskedmm_fwd", lambda: ref.maskedmm_csr_forward(*R, Q, K))
+            p = timed("softmax_fwd", lambda: ref.sparse_softmax_forward(*R[:3], s))
+            ds = timed("softmax_bwd", lambda: ref.sparse_softmax_backward(*R[:3], p, dP))
+            timed("maskedmm_bwd", lambda: ref.maskedmm_csr_backward(*R, *C, Q, K, ds))
+    step()
+    th.cuda.synchronize()
+    times.clear()
+    a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    th.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    per_op = {k: sum(x.elapsed_time(y) for x, y in v) / len(v) for k, v in times.items()}
+    return {"ms_per_step": ms, "value": e * h / (ms * 1e-3), "unit": UNIT, "steps": steps, "per_op_ms": per_op,
+            "what": "the reference's CUDA ops, compiled unmodified for sm_100a, on the same graph (int64 chunk "
+                    "tables, chunk_size 32), forward + backward, CUDA events",
+            "note": "its dx kernel is launched with the row CSR's chunk count (graphop_kernel.cu:566, 588): on a graph "
+                    "whose transposed CSR has more chunks it leaves the last ones out, so its time is a lower bound"}
+
+
 def run_reference(args):
-    """Reference arm.  The reference is a CUDA-only extension with no CPU implementation of its
-    own, so this arm times the torch CPU restatement of its chain on the host cores, every step a
-    bounded sample of the workload."""
+    """Reference arm.  The reference is a CUDA-only extension with no CPU implementation of its own, so `value`
+    times the torch CPU restatement of its chain on all host cores, on the workload's own graph (the same
+    generator and seed as rank 0 of the GPU arm).  Beside it, under `reference_cuda`, the reference's own CUDA ops
+    are timed on this box's GPU."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cores = os.cpu_count() or 1
+    th.set_num_threads(cores)     # torch.distributed.run exports OMP_NUM_THREADS=1: use every host core anyway
+    from oracle import cpu_baseline as cb
     spec = dict(WORKLOADS[args.workload])
-    h = spec["heads"]
-    base = None
-    secs = []
-    for _ in range(max(1, min(args.warmup, 1)) + max(1, min(args.steps, 3))):
-        base = cpu_baseline(spec, args.cpu_sample_scale)
-        secs.append(base["seconds"])
-    secs = secs[1:] or secs
-    sec = statistics.mean(secs)
-    edges_heads = base["value"] * base["seconds"]
-    value = edges_heads / sec
-    base["value"] = value
+    if args.scale and spec["kind"] == "rmat":
+        spec["scale"] = args.scale
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    h, d = spec["heads"], spec["dim"]
+    note = "the reference has no CPU code path; this is the torch CPU restatement of its chain, all host cores"
+    if spec["ops"] == "sharded_spmm":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference runs on one device and its index "
+                          "arithmetic overflows at R-MAT scale 24 (graphop_kernel.cu:49, 144)"}))
+        return
+    t0 = time.time()
+    g = make_graph(spec, seed=0, device="cuda" if th.cuda.is_available() else "cpu").to(device="cpu")
+    ops = spec["ops"]
+    secs = []
+    budget_s = 150.0
+    planned = max(1, args.steps)
+    for k in range(1 + planned):               # one untimed step first
+        t = cb.time_workload(ops, g, h, d)
+        if k:
+            secs.append(t)
+        if time.time() - t0 + t > budget_s and secs:
+            break
+    sec = statistics.mean(secs)
+    value = g.n_edges * h / sec
+    base = {"value": value, "unit": UNIT, "cores": th.get_num_threads(), "host_cpus": cores, "kind": "port",
+            "seconds": sec, "sample": "the whole workload graph, %d steps of the %d asked for (bounded to ~%d s of "
+                                      "CPU work); torch CPU fp32, forward + backward through autograd" % (
+                                          len(secs), planned, int(budget_s))}
     out = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
            "steps": len(secs), "warmup": 1, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
-           "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": args.workload, "graph": describe(spec), "heads": h, "dim": spec["dim"],
-                      "note": "the reference has no CPU code path; this is the torch CPU restatement of its chain"},
+           "vs_baseline": None, "dtype": spec["dtype"], "data": "synthetic",
+           "config": {"workload": args.workload, "ops": WORKLOAD_CLASSES[ops].name, "graph": describe(spec),
+                      "nodes": g.n_dst, "edges": g.n_edges, "heads": h, "dim": d,
+                      "index": "int32 CSR, chunk tables of partition_csr(32)", "note": note},
            "cpu_baseline": base,
            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
+    if world == 1 or rank == 0:
+        out["reference_cuda"] = reference_cuda(spec, g)
     print(json.dumps(out))
 
 
@@ -765,10 +1140,13 @@ def main():
     ap.add_argument("--impl", default="graphop_b200", choices=["graphop_b200", "reference"])
     ap.add_argument("--workload", default="rmat21_attention", choices=sorted(WORKLOADS))
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (smaller runs)")
-    ap.add_argument("--cpu-sample-scale", type=int, default=18)
+    ap.add_argument("--cpu-sample-scale", type=int, default=19)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="needed", choices=["needed", "all"],
                     help="sharded workload: fetch only the node rows a shard references, or all-gather every row")
+    ap.add_argument("--sharded", default="auto", choices=["auto", "off"],
+                    help="also run the row-sharded R-MAT scale-24 SpMM at this GPU count and attach it as `sharded`")
+    ap.add_argument("--sharded-scale", type=int, default=0, help="override the R-MAT scale of the sharded extra")
     ap.add_argument("--cuda-graph", action="store_true",
                     help="also replay the step from a CUDA graph and report it (1 GPU)")
     ap.add_argument("--lean", action="store_true",

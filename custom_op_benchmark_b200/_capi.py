@@ -8,8 +8,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# GRAPHOP_B200_LIBRARY points at another build of the same library (kernel tuning experiments)
-LIB_PATH = os.environ.get("GRAPHOP_B200_LIBRARY") or os.path.join(HERE, "libgraphop_b200.so")
+LIB_PATH = os.path.join(HERE, "libgraphop_b200.so")
 
 OK, ERR_INVALID_ARGUMENT, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_CUDA = range(5)
 
@@ -42,13 +41,9 @@ UNTYPED = {
     "graphop_error_string": ([_INT], ctypes.c_char_p),
     "graphop_last_cuda_error": ([], _INT),
     "graphop_workspace_bytes": ([_INT, _I64, _I64, _INT, _INT, _INT, _INT], _SZ),
-    "graphop_launch_count": ([], ctypes.c_longlong),
-    "graphop_profile_begin": ([_P], _INT),
-    "graphop_profile_end": ([_P, _SZ, _P, _INT], _INT),
     "graphop_static_scratch_bytes": ([], _SZ),
     "graphop_vector_spmm_forward_f32_i32_static": ([_P] * 7 + [_I64] * 4 + [_INT] * 2 + [_P], _INT),
     "graphop_gather_rows_i32": ([_P, _I64, _P, _I64, _P, _P], _INT),
-    "graphop_gather_probe_i32": ([_P, _I64, _P, _P, _INT, _P, _P], _INT),
     "graphop_check_graph_i32": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
     "graphop_check_graph_i64": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
 }
@@ -67,6 +62,23 @@ def exported_symbols():
 _lib = None
 
 
+def bind(handle, strict=True):
+    """Sets argtypes / restype of every entry point of include/graphop_b200.h on a loaded library.
+    strict=False skips symbols the library does not export (a build with fewer element types)."""
+    for name, (args, res) in UNTYPED.items():
+        fn = getattr(handle, name, None) if not strict else getattr(handle, name)
+        if fn is not None:
+            fn.argtypes, fn.restype = args, res
+    for op, args in SIGNATURES.items():
+        for e in ELEM_SUFFIXES:
+            for i in INDEX_SUFFIXES:
+                name = "graphop_%s_%s_%s" % (op, e, i)
+                fn = getattr(handle, name, None) if not strict else getattr(handle, name)
+                if fn is not None:
+                    fn.argtypes, fn.restype = args, _INT
+    return handle
+
+
 def lib():
     """The loaded library with argtypes set; raises if it has not been built."""
     global _lib
@@ -76,17 +88,8 @@ def lib():
         raise ImportError(
             "graphop_b200: %s is missing; build it with `python -m custom_op_benchmark_b200.build` "
             "(nvcc, sm_100a). There is no CPU or PyTorch fallback." % LIB_PATH)
-    handle = ctypes.CDLL(LIB_PATH)
-    for name, (args, res) in UNTYPED.items():
-        fn = getattr(handle, name)
-        fn.argtypes, fn.restype = args, res
-    for op, args in SIGNATURES.items():
-        for e in ELEM_SUFFIXES:
-            for i in INDEX_SUFFIXES:
-                fn = getattr(handle, "graphop_%s_%s_%s" % (op, e, i))
-                fn.argtypes, fn.restype = args, _INT
-    _lib = handle
-    return handle
+    _lib = bind(ctypes.CDLL(LIB_PATH))
+    return _lib
 
 
 def error_message(code):
@@ -95,21 +98,3 @@ def error_message(code):
     if code == ERR_CUDA:
         msg += " (cudaError %d)" % handle.graphop_last_cuda_error()
     return msg
-
-
-def profile(fn, stream, max_entries=4096):
-    """Runs fn() with per-kernel timing on; returns [(kernel name, milliseconds), ...]."""
-    handle = lib()
-    rc = handle.graphop_profile_begin(stream)
-    if rc != OK:
-        raise RuntimeError("graphop_profile_begin: " + error_message(rc))
-    try:
-        fn()
-    finally:
-        names = ctypes.create_string_buffer(64 * max_entries)
-        ms = (ctypes.c_float * max_entries)()
-        n = handle.graphop_profile_end(ctypes.cast(names, ctypes.c_void_p), len(names),
-                                       ctypes.cast(ms, ctypes.c_void_p), max_entries)
-    if n < 0:
-        raise RuntimeError("graphop_profile_end failed")
-    return list(zip(names.value.decode().split("\n")[:n], [float(v) for v in ms[:n]]))

@@ -91,9 +91,20 @@ __device__ __forceinline__ void store_raw(A* p, const A (&src)[V]) {
   for (int i = 0; i < V; ++i) p[i] = src[i];
 }
 
+// Every cross-lane sum in these kernels is a butterfly over lane distances 1, 2, 4, ... in that order, whichever
+// routine forms it: two kernels that reduce the same per-lane partials (delta in the destination pass, dO . v in
+// the source pass) then agree bit for bit.
 template <typename A> __device__ __forceinline__ A warp_sum(A v) {
 #pragma unroll
-  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+  for (int o = 1; o < 32; o <<= 1) v += __shfl_xor_sync(kFull, v, o);
+  return v;
+}
+
+// One value per lane summed over the LPH lanes of a head, lane distances 1, 2, 4, ... in that order.
+template <int LPH, typename A>
+__device__ __forceinline__ A reduce_ascending(A v) {
+#pragma unroll
+  for (int o = 1; o < LPH; o <<= 1) v += __shfl_xor_sync(kFull, v, o);
   return v;
 }
 
@@ -136,7 +147,7 @@ __device__ __forceinline__ void reduce_heads(A (&p)[R], int lph) {
 #pragma unroll
     for (int i = 0; i < R; ++i) p[i] = warp_sum(p[i]);
   } else {
-    for (int o = lph >> 1; o; o >>= 1) {
+    for (int o = 1; o < lph; o <<= 1) {
 #pragma unroll
       for (int i = 0; i < R; ++i) p[i] += __shfl_xor_sync(kFull, p[i], o);
     }

@@ -1,7 +1,9 @@
 // Host side of the C ABI: argument checks, workspace carving, kernel selection and the
 // launch sequences.  Everything here enqueues on the caller's stream and never synchronises.
 #pragma once
+#include <atomic>
 #include <cstdio>
+#include <mutex>
 #include <type_traits>
 #include <utility>
 #include <vector>
@@ -26,11 +28,13 @@ inline thread_local int g_last_cuda_error = 0;
   } while (0)
 #define GK_LAUNCH_CHECK() GK_CUDA(cudaGetLastError())
 
-// Launch accounting and optional per-kernel timing.  Every kernel launch of the library goes
-// through GK_LAUNCHED(name): it checks the launch, counts it and, while a profile is open
-// (graphop_profile_begin), records a CUDA event behind the kernel on the caller's stream, so
-// the time between two consecutive events is the device time of the later kernel.
+// Every kernel launch of the library goes through GK_LAUNCHED(name), which checks the launch.  The benchmark's
+// instrumented twin of the library (compiled with -DGK_BENCH_HOOKS, see csrc/bench/) also counts the launch and,
+// while a profile is open, records a CUDA event behind the kernel on the caller's stream, so that the time
+// between two consecutive events is the device time of the later kernel.  The product library has none of it.
+#ifdef GK_BENCH_HOOKS
 struct Profiler {
+  std::mutex lock;   // autograd runs the backward ops on another host thread
   bool enabled = false;
   long long launches = 0;
   std::vector<std::pair<const char*, cudaEvent_t>> marks;
@@ -41,6 +45,7 @@ inline Profiler& profiler() {
 }
 inline void mark(const char* name, cudaStream_t st) {
   Profiler& p = profiler();
+  std::lock_guard<std::mutex> hold(p.lock);
   ++p.launches;
   if (p.enabled) {
     cudaEvent_t e;
@@ -55,6 +60,9 @@ inline void mark(const char* name, cudaStream_t st) {
     GK_LAUNCH_CHECK();     \
     gk::mark(name, st);    \
   } while (0)
+#else
+#define GK_LAUNCHED(name) GK_LAUNCH_CHECK()
+#endif
 #define GK_TRY(expr)                    \
   do {                                  \
     int rc__ = (expr);                  \
@@ -90,7 +98,7 @@ constexpr int kMaxLevels = 12;
 // large graphs get 256 so that carries stay a fraction of a percent of the traffic.
 inline int pick_tile(long long n_edges) {
   long long t = 32;
-  while (t < GK_TUNE_TILE && n_edges / t > 16384) t <<= 1;
+  while (t < GK_TILE && n_edges / t > 16384) t <<= 1;
   return (int)t;
 }
 
@@ -233,24 +241,26 @@ inline int dispatch_lph(int lph, F&& f) {
 // level-0 + carry-level launch sequence of a row-producing op
 // ---------------------------------------------------------------------------------------
 template <class Op>
-inline size_t staged_smem_bytes(int tile) {
-  return (size_t)Op::kWarps * staged_warp_bytes<Op>(tile);
+inline size_t staged_smem_bytes() {
+  return (size_t)Op::kWarps * staged_warp_bytes<Op>();
 }
 
 // Launches the staged level-0 walker; raises the kernel's dynamic shared memory limit once per device.
 template <class Op>
 inline int launch_staged(const Op& op, const GraphView& g, int tile, long long n_rows, int32_t* rows_next,
                          cudaStream_t st) {
-  static bool configured[64] = {};
+  // one flag per device and kernel; several host threads may get here at once (autograd's backward thread):
+  // setting the attribute twice is harmless, the flag only saves the call
+  static std::atomic<bool> configured[64];
   int dev = 0;
   GK_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
     GK_CUDA(cudaFuncSetAttribute(walk_staged_kernel<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)staged_smem_bytes<Op>(GK_TUNE_TILE)));
-    configured[dev] = true;
+                                 (int)staged_smem_bytes<Op>()));
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   const long long nt = (g.E + tile - 1) / tile;
-  walk_staged_kernel<Op><<<grid_for_warps(nt, Op::kWarps), Op::kWarps * 32, staged_smem_bytes<Op>(tile), st>>>(
+  walk_staged_kernel<Op><<<grid_for_warps(nt, Op::kWarps), Op::kWarps * 32, staged_smem_bytes<Op>(), st>>>(
       op, g.hdr, g.erow, g.other, g.eid, g.E, tile, n_rows, rows_next);
   GK_LAUNCHED(Op::kName);
   return GRAPHOP_OK;
@@ -333,7 +343,7 @@ inline int run_aggregate(Arena& ar, const GraphView& g, const T* w, const T* x, 
           OpM op;
           op.w = w; op.x = x; op.y = y; op.carry = (A*)cout; op.carry_in = (const A*)cin;
           op.H = H; op.D = D; op.HD = HD; op.S = b.S; op.feat0 = feat0;
-          if constexpr (IsStaged<OpM>::value) op.wmode = wm;
+          if constexpr (IsStaged<OpM>::value) { op.wmode = wm; op.set_weight_bounds((long long)g.E * H); }
           return op;
         });
       };
@@ -631,6 +641,15 @@ inline int spmm_backward(const I* row, const I* indptr, const I* eid, const I* i
   return run_aggregate<T, false>(ar, g, edata, dy, dx, n_src, H, D, st);
 }
 
+template <typename A>
+__global__ void fill_kernel(A* __restrict__ out, A value, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = value;
+}
+template <typename A> inline A neg_inf_host();
+template <> inline float neg_inf_host<float>() { return -INFINITY; }
+template <> inline double neg_inf_host<double>() { return -(double)INFINITY; }
+
 template <typename T>
 inline bool attention_shape_ok(int H, int D, bool al, VecShape* s) {
   *s = pick_shape<T>(H * D, D, al);
@@ -653,8 +672,13 @@ inline int attention_forward(const I* row, const I* indptr, const I* indices, lo
   GraphView g;
   const int HD = H * D;
   if (E == 0) {
-    // no edge anywhere: o = 0 and lse = -inf for every node, written by the gap filler of an empty walk
-    return GRAPHOP_ERR_UNSUPPORTED;
+    // no edge anywhere: o = 0 and lse = -inf for every node
+    GK_CUDA(cudaMemsetAsync(o, 0, (size_t)n_dst * HD * sizeof(T), st));
+    const long long cells = n_dst * H;
+    const unsigned grid = (unsigned)((cells + 255) / 256 < 4096 ? (cells + 255) / 256 : 4096);
+    fill_kernel<A><<<grid ? grid : 1, 256, 0, st>>>((A*)lse, neg_inf_host<A>(), cells);
+    GK_LAUNCHED("fill");
+    return GRAPHOP_OK;
   }
   if (!row || !indptr || !indices) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(prepare_graph<I>(ar, row, indptr, (const I*)nullptr, indices, C, E, st, &g));
@@ -690,7 +714,14 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
   const bool al = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(dout) && aligned16(dq) &&
                   aligned16(dk) && aligned16(dv);
   if (!attention_shape_ok<T>(H, D, al, &s)) return GRAPHOP_ERR_UNSUPPORTED;
-  if (E == 0) return GRAPHOP_ERR_UNSUPPORTED;
+  if (E == 0) {  // no edge: every gradient is zero
+    if ((n_dst && !dq) || (n_src && (!dk || !dv))) return GRAPHOP_ERR_INVALID_ARGUMENT;
+    const size_t rowb = (size_t)H * D * sizeof(T);
+    if (n_dst) GK_CUDA(cudaMemsetAsync(dq, 0, (size_t)n_dst * rowb, st));
+    if (n_src) GK_CUDA(cudaMemsetAsync(dk, 0, (size_t)n_src * rowb, st));
+    if (n_src) GK_CUDA(cudaMemsetAsync(dv, 0, (size_t)n_src * rowb, st));
+    return GRAPHOP_OK;
+  }
   if (!row || !indptr || !indices || !col || !indptr_t || !indices_t || !q || !k || !v || !o || !lse || !dout || !dq ||
       !dk || !dv)
     return GRAPHOP_ERR_INVALID_ARGUMENT;

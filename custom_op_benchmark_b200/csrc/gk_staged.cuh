@@ -19,19 +19,14 @@
 
 #include "gk_ops.cuh"
 
-// Build-time tunables.
-#ifndef GK_TUNE_CTAS_NARROW
-#define GK_TUNE_CTAS_NARROW 4   // resident blocks per SM aimed at when a node row fits one slot per lane
-#endif
-#ifndef GK_TUNE_CTAS_SRC
-#define GK_TUNE_CTAS_SRC 3      // the same for the attention backward over the transposed CSR: it keeps two
-#endif                          // accumulator rows and two resident rows, which 64 registers do not hold
-#ifndef GK_TUNE_TILE
-#define GK_TUNE_TILE 256        // largest level-0 tile of the staged walker
-#endif
-#ifndef GK_TUNE_BATCH_MAX
-#define GK_TUNE_BATCH_MAX 8     // most edges of one node folded together
-#endif
+// Launch shape of the staged kernels, chosen by measurement on a B200 (R-MAT scale 21, 4 heads x 32, fp32).
+// All of them are bound by how many gathered rows the shared-memory rings keep in flight per SM, so the numbers
+// below trade resident warps against ring depth.
+#define GK_CTAS_NARROW 4     // resident blocks per SM aimed at when a node row fits one 16-byte slot per lane
+#define GK_CTAS_DST 3        // attention backward, destination side: its state needs the 80 registers of 3 blocks
+#define GK_CTAS_SRC 4        // attention backward, source side
+#define GK_TILE 256          // largest level-0 tile (positions per warp)
+#define GK_FAST_BATCH 2      // batch of the transposed-reduction paths (2 or 4)
 
 namespace gk {
 
@@ -84,19 +79,33 @@ __device__ __forceinline__ void lds_acc(typename AccOf<T>::type (&dst)[V], const
 //   void stage(const State&, unsigned char* entry, int other, int edge, int lane)   cp.async the edge's operands
 //   void prefetch_node(State&, int node, int lane)   start loading what begin(node) will need (may be a no-op)
 //   template <bool kFullBatch>
-//   void consume_batch(State&, const unsigned char* ring, int i, int cnt, const int* eids, int lane)
-//        fold ring entries i .. i+cnt-1 (entry of position p at ring + (p & (kDepth-1)) * kEdgeBytes);
+//   void consume_batch(State&, const unsigned char* first, int cnt, const int* eids, int lane)
+//        fold cnt positions whose ring entries are first, first + kEdgeBytes, ...;
 //        kFullBatch: cnt == kBatch, known at compile time
 // Lanes whose slot does not exist (slot >= S) are not masked in stage / consume_batch: their slot map
 // points at slot 0, so their copies and arithmetic are harmless duplicates, their node-resident
 // operand is zero, and only stores test `ok`.
-constexpr int kMetaPad = 32;  // metadata entries past the tile that the prefetcher may read
 
-// Shared memory of one warp: metadata of tile + kMetaPad positions (node, other endpoint, edge id if
-// the op uses it, one run-length byte), rounded to 16 bytes, then kDepth ring entries.
+// Ops that hand a batch's per-edge scalars from their owner lanes to all lanes of a head through shared memory
+// declare `kScratchBytes` (a multiple of 16): that many bytes per warp follow the ring.
+template <class Op, class = void> struct ScratchBytes { static constexpr int value = 0; };
+template <class Op> struct ScratchBytes<Op, std::void_t<decltype(Op::kScratchBytes)>> {
+  static constexpr int value = Op::kScratchBytes;
+};
+
+// Tile metadata lives in a window of two blocks of 32 positions per warp (node, other endpoint, edge id if the
+// op uses it, one run-length byte), refilled block by block while the tile is walked: a few hundred bytes per
+// warp instead of the whole tile's, which leaves the shared memory to the rings.
+constexpr int kWinBlock = 32, kWin = 2 * kWinBlock;
+
+// Shared memory of one warp: the metadata window rounded to 16 bytes, kDepth ring entries, the op's scratch.
 template <class Op>
-__host__ __device__ constexpr size_t staged_warp_bytes(int tile) {
-  return (((size_t)(tile + kMetaPad) * (Op::kUsesEid ? 13 : 9)) + 15) / 16 * 16 + (size_t)Op::kDepth * Op::kEdgeBytes;
+__host__ __device__ constexpr size_t staged_meta_bytes() {
+  return ((size_t)kWin * (Op::kUsesEid ? 13 : 9) + 15) / 16 * 16;
+}
+template <class Op>
+__host__ __device__ constexpr size_t staged_warp_bytes() {
+  return staged_meta_bytes<Op>() + (size_t)Op::kDepth * Op::kEdgeBytes + (size_t)ScratchBytes<Op>::value;
 }
 
 // Ops whose lanes read ring bytes copied by other lanes declare `kSharedEntry = true`; the walker
@@ -106,9 +115,38 @@ template <class Op, class = void> struct SharesEntries : std::false_type {};
 template <class Op> struct SharesEntries<Op, std::void_t<decltype(Op::kSharedEntry)>> : std::true_type {};
 
 // Ops that need the global position of the edges they fold declare `kTileBase = true` and get the tile's
-// first position in `State::tile_base` (positions stay below 2^31).
+// first position in `State::tile_base` (positions stay below 2^31) and the batch's offset in `State::batch_pos`.
 template <class Op, class = void> struct WantsTileBase : std::false_type {};
 template <class Op> struct WantsTileBase<Op, std::void_t<decltype(Op::kTileBase)>> : std::true_type {};
+
+// Ops whose begin(node) reads rows of node tensors declare `kNodeRows = true` and implement
+// prefetch_rows_l2(node): the walker calls it for every node that starts in a metadata block when the block
+// enters the window, 32 to 64 positions before the node is reached, so that begin() finds the rows in the L2
+// cache instead of paying a DRAM round trip per node (a graph with millions of short rows is otherwise bound
+// by exactly that latency).  One request per 128-byte line: a few per node, nothing beside the gathers.
+template <class Op, class = void> struct NodeRows : std::false_type {};
+template <class Op> struct NodeRows<Op, std::void_t<decltype(Op::kNodeRows)>> : std::true_type {};
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void prefetch_row_l2(const void* row, unsigned row_bytes) {
+  for (unsigned off = 0; off < row_bytes; off += 128) prefetch_l2(reinterpret_cast<const unsigned char*>(row) + off);
+}
+
+// U consecutive ints from shared memory (U a power of two up to 8, the address a multiple of 4 U bytes).
+template <int U>
+__device__ __forceinline__ void load_meta(int (&d)[U], const int* p) {
+  if constexpr (U == 1) {
+    d[0] = p[0];
+  } else if constexpr (U == 2) {
+    const int2 t = *reinterpret_cast<const int2*>(p);
+    d[0] = t.x; d[1] = t.y;
+  } else {
+#pragma unroll
+    for (int k = 0; k < U / 4; ++k) {
+      const int4 t = reinterpret_cast<const int4*>(p)[k];
+      d[4 * k] = t.x; d[4 * k + 1] = t.y; d[4 * k + 2] = t.z; d[4 * k + 3] = t.w;
+    }
+  }
+}
 
 template <class Op>
 __global__ void __launch_bounds__(Op::kWarps * 32, Op::kMinCtas)
@@ -120,7 +158,8 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
   constexpr int EB = Op::kEdgeBytes;
   constexpr bool kOut = Op::kRowOut;
   constexpr bool kShared = SharesEntries<Op>::value;
-  static_assert((DEPTH & (DEPTH - 1)) == 0 && DEPTH >= U && U <= 32, "ring depth: a power of two >= batch");
+  static_assert((U & (U - 1)) == 0 && DEPTH % U == 0 && DEPTH + U <= kWinBlock,
+                "batch: a power of two; ring: whole batches, look-ahead within one block");
   extern __shared__ uint4 gk_smem[];
   const int lane = threadIdx.x & 31;
   const int w = threadIdx.x >> 5;
@@ -138,123 +177,146 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
     }
   }
 
-  // per warp: node and other-endpoint (and, for ops that use it, edge id) of tile + kMetaPad
-  // positions, one byte of run length per position, then the ring
-  const int cap = tile + kMetaPad;
-  unsigned char* mine = reinterpret_cast<unsigned char*>(gk_smem) + (size_t)w * staged_warp_bytes<Op>(tile);
-  int* m_row = reinterpret_cast<int*>(mine);
-  int* m_oth = m_row + cap;
-  int* m_eid = m_oth + cap;  // present only when Op::kUsesEid
-  unsigned char* m_rem = reinterpret_cast<unsigned char*>(m_oth + (Op::kUsesEid ? 2 : 1) * cap);
-  unsigned char* ring = mine + staged_warp_bytes<Op>(tile) - (size_t)DEPTH * EB;
+  unsigned char* mine = reinterpret_cast<unsigned char*>(gk_smem) + (size_t)w * staged_warp_bytes<Op>();
+  int* w_row = reinterpret_cast<int*>(mine);
+  int* w_oth = w_row + kWin;
+  int* w_eid = w_oth + kWin;  // present only when Op::kUsesEid
+  unsigned char* w_rem = reinterpret_cast<unsigned char*>(w_oth + (Op::kUsesEid ? 2 : 1) * kWin);
+  unsigned char* ring = mine + staged_meta_bytes<Op>();
 
-  // Tile metadata -> shared memory.  m_rem[i] = number of consecutive positions from i on that have
-  // the same node as i (at most 255, never past the tile): blocks of 32 are filled from the last to
-  // the first so that a run that continues into the next block can add that block's first count.
-  // Positions past the tile get node -2, and every position without a node points at node 0 / edge 0,
-  // so that the prefetcher can issue its copies without looking at the node.
+  // Metadata window.  Block b (positions 32 b .. 32 b + 31 of the tile) occupies window entries
+  // (b & 1) * 32 + lane.  w_rem = number of consecutive positions from this one on that have the same node,
+  // never past the block's end: a batch never crosses a block.  Positions past the tile get node -2, and every
+  // position without a node points at node 0 / edge 0, so that the ring can be refilled without looking at the
+  // node.  One block is always held in registers ahead of the window.
   const int before = j0 > 0 ? __ldg(erow + j0 - 1) : -1;
-  {
-    // all global loads of the tile's metadata are issued before any is used: one memory latency
-    // per tile instead of one per 32 positions
-    constexpr int kMaxBlocks = (GK_TUNE_TILE + kMetaPad) / 32;
-    int r_[kMaxBlocks], o_[kMaxBlocks], e_[kMaxBlocks];
-#pragma unroll
-    for (int b = 0; b < kMaxBlocks; ++b) {
-      const int i = b * 32 + lane;
-      const bool inb = i < nt;
-      r_[b] = inb ? __ldg(erow + j0 + i) : -2;
-      o_[b] = (inb && other) ? __ldg(other + j0 + i) : 0;
-      e_[b] = (Op::kUsesEid && inb) ? (eid ? __ldg(eid + j0 + i) : (int)(j0 + i)) : 0;
+  int nr, no, ne;
+  auto fetch_block = [&](int b) {
+    const int i = b * kWinBlock + lane;
+    const bool inb = i < nt;
+    nr = inb ? __ldg(erow + j0 + i) : -2;
+    no = (inb && other) ? __ldg(other + j0 + i) : 0;
+    ne = (Op::kUsesEid && inb) ? (eid ? __ldg(eid + j0 + i) : (int)(j0 + i)) : 0;
+  };
+  auto publish_block = [&](int b) {
+    const int s = (b & 1) * kWinBlock + lane;
+    const int down = __shfl_down_sync(kFull, nr, 1);
+    const unsigned ends = __ballot_sync(kFull, lane == 31 || nr != down);  // bit l: a run ends at lane l
+    if constexpr (NodeRows<Op>::value) {
+      const int up = __shfl_up_sync(kFull, nr, 1);
+      if (nr >= 0 && (lane == 0 || nr != up)) op.prefetch_rows_l2(nr);  // a node starts (or goes on) here
     }
-    int next_first_row = -3, next_first_rem = 0;  // node and run length of the first position of block b + 1
-#pragma unroll
-    for (int b = kMaxBlocks - 1; b >= 0; --b) {
-      const int i = b * 32 + lane;
-      const int r = r_[b];
-      if (i < cap) {
-        m_row[i] = r;
-        m_oth[i] = r >= 0 ? o_[b] : 0;
-        if constexpr (Op::kUsesEid) m_eid[i] = r >= 0 ? e_[b] : 0;
-      }
-      int down = __shfl_down_sync(kFull, r, 1);
-      if (lane == 31) down = next_first_row;
-      const unsigned ends = __ballot_sync(kFull, r != down);   // bit l: the run ends at lane l
-      const unsigned at_or_after = ends >> lane;                // bit 0 <-> this lane
-      int rem;
-      if (at_or_after) rem = __ffs(at_or_after);               // run ends inside this block
-      else rem = (32 - lane) + next_first_rem;                  // runs on into block b + 1
-      rem = rem > 255 ? 255 : rem;
-      if (i < cap) m_rem[i] = (unsigned char)(i < nt ? rem : 1);
-      next_first_row = __shfl_sync(kFull, r, 0);
-      next_first_rem = __shfl_sync(kFull, rem, 0);
-    }
-  }
+    w_row[s] = nr;
+    w_oth[s] = nr >= 0 ? no : 0;
+    if constexpr (Op::kUsesEid) w_eid[s] = nr >= 0 ? ne : 0;
+    w_rem[s] = (unsigned char)__ffs(ends >> lane);
+  };
+  fetch_block(0);
+  publish_block(0);
+  fetch_block(1);
+  publish_block(1);
+  fetch_block(2);
   __syncwarp();
 
   typename Op::State st;
   op.setup(st, lane);
   if constexpr (WantsTileBase<Op>::value) st.tile_base = (int)j0;
-  const int first = m_row[0];
+  if constexpr (ScratchBytes<Op>::value != 0) st.scratch = ring + (size_t)DEPTH * EB;
+  const int first = w_row[0];
   const bool head_open = before >= 0 && before == first;
   bool first_seg = true;
   int cur = -1;
   int last_valid = before;
   int head_row = -1;
 
-  // one commit group per position, copies issued whether or not the position carries an edge
-  auto issue = [&](int i) {
-    op.stage(st, ring + (size_t)(i & (DEPTH - 1)) * EB, m_oth[i], Op::kUsesEid ? m_eid[i] : 0, lane);
+  // The ring is NG groups of U entries.  Group g of the tile (positions g U .. g U + U - 1) always occupies ring
+  // group g mod NG, so every entry of a batch sits at a compile-time offset from the group's base, and one
+  // cp.async commit group per refill maps commit groups one to one onto ring groups: waiting for all but the
+  // last NG - 1 commit groups is waiting for exactly the group about to be folded.  Copies are issued whether
+  // or not a position carries an edge.
+  constexpr int NG = DEPTH / U;
+  constexpr int kGroupBytes = U * EB;
+  auto refill = [&](int pos0, unsigned char* grp) {
+    const int wi = pos0 & (kWin - 1);
+    int oth[U], eds[U];
+    load_meta<U>(oth, w_oth + wi);
+    if constexpr (Op::kUsesEid) load_meta<U>(eds, w_eid + wi);
+#pragma unroll
+    for (int u = 0; u < U; ++u) op.stage(st, grp + u * EB, oth[u], Op::kUsesEid ? eds[u] : 0, lane);
     cp_async_commit();
   };
 #pragma unroll
-  for (int i = 0; i < DEPTH; ++i) issue(i);
+  for (int g = 0; g < NG; ++g) refill(g * U, ring + g * kGroupBytes);
 
-  bool new_seg = true;
-  int i = 0;
-  while (i < nt) {
-    const int r = m_row[i];
-    const int rem = m_rem[i];
-    if (new_seg) {  // a segment starts here
-      if (cur >= 0) {
-        if constexpr (kOut) {
-          if (first_seg && head_open) { op.store_carry(st, 2 * t, lane); head_row = cur; }
-          else op.store_row(st, cur, lane);
-          if (r < 0) op.zero_rows((long long)cur + 1, n_rows, lane);  // coverage ended
-        }
-        first_seg = false;
+  // a segment of node r starts at position `pos` (r < 0: positions without a node)
+  auto enter = [&](int r, int pos) {
+    if (cur >= 0) {
+      if constexpr (kOut) {
+        if (first_seg && head_open) { op.store_carry(st, 2 * t, lane); head_row = cur; }
+        else op.store_row(st, cur, lane);
+        if (r < 0) op.zero_rows((long long)cur + 1, n_rows, lane);  // coverage ended
       }
-      if (r >= 0) {
-        if constexpr (kOut) {
-          if (!(first_seg && head_open)) op.zero_rows((long long)last_valid + 1, r, lane);
-        }
-        op.begin(st, r, lane);
-        last_valid = r;
-        // the node that starts next in this tile: fetch its resident rows while this one is processed
-        const int nx = i + rem;
-        if (nx < nt) {
-          const int rn = m_row[nx];
-          if (rn >= 0 && rn != r) op.prefetch_node(st, rn, lane);
-        }
-      }
-      cur = r;
+      first_seg = false;
     }
-    cp_async_wait<DEPTH - U>();
-    if constexpr (kShared) __syncwarp();  // every lane's copies of these entries have landed
-    if (rem >= U) {  // the common case: a full batch of one node's edges
-      if (r >= 0) op.template consume_batch<true>(st, ring, i, U, Op::kUsesEid ? m_eid + i : nullptr, lane);
-      if constexpr (kShared) __syncwarp();  // all lanes have read the entries about to be refilled
+    if (r >= 0) {
+      if constexpr (kOut) {
+        if (!(first_seg && head_open)) op.zero_rows((long long)last_valid + 1, r, lane);
+      }
+      op.begin(st, r, lane);
+      last_valid = r;
+      // the node that starts next in this tile: fetch its resident rows while this one is processed
+      const int nx = pos + w_rem[pos & (kWin - 1)];
+      if (nx < nt) {
+        const int rn = w_row[nx & (kWin - 1)];
+        if (rn >= 0 && rn != r) op.prefetch_node(st, rn, lane);
+      }
+    }
+    cur = r;
+  };
+
+  int blk = 0;
+  unsigned char* grp = ring;  // ring group of the batch being folded
+  for (int i = 0; i < nt; i += U) {
+    if (i >= (blk + 1) * kWinBlock) {
+      // the walk enters block blk + 1: block blk's window entries are free for block blk + 2
+      __syncwarp();
+      ++blk;
+      publish_block(blk + 1);
+      fetch_block(blk + 2);
+      __syncwarp();
+    }
+    const int wi = i & (kWin - 1);
+    int rows[U];
+    load_meta<U>(rows, w_row + wi);
+    bool uniform = rows[0] == cur;
 #pragma unroll
-      for (int u = 0; u < U; ++u) issue(i + u + DEPTH);
-      new_seg = rem == U;
-      i += U;
+    for (int u = 1; u < U; ++u) uniform = uniform && rows[u] == rows[0];
+    cp_async_wait<NG - 1>();
+    if constexpr (kShared) __syncwarp();  // every lane's copies of these entries have landed
+    if (uniform) {  // the common case: a whole group of the current node's edges
+      if (cur >= 0) {
+        if constexpr (WantsTileBase<Op>::value) st.batch_pos = i;
+        op.template consume_batch<true>(st, grp, U, Op::kUsesEid ? w_eid + wi : nullptr, lane);
+      }
     } else {
-      if (r >= 0) op.template consume_batch<false>(st, ring, i, rem, Op::kUsesEid ? m_eid + i : nullptr, lane);
-      if constexpr (kShared) __syncwarp();
-      for (int u = 0; u < rem; ++u) issue(i + u + DEPTH);
-      new_seg = true;
-      i += rem;
+      // run by run: the group holds a node boundary, the tile's end or positions without a node
+      int u = 0;
+      while (u < U && i + u < nt) {
+        const int r = w_row[wi + u];
+        int run = w_rem[wi + u];
+        run = run < U - u ? run : U - u;
+        if (r != cur) enter(r, i + u);  // adjacent runs never share a node
+        if (r >= 0) {
+          if constexpr (WantsTileBase<Op>::value) st.batch_pos = i + u;
+          if (run == U) op.template consume_batch<true>(st, grp, U, Op::kUsesEid ? w_eid + wi : nullptr, lane);
+          else op.template consume_batch<false>(st, grp + u * EB, run, Op::kUsesEid ? w_eid + wi + u : nullptr, lane);
+        }
+        u += run;
+      }
     }
+    if constexpr (kShared) __syncwarp();  // all lanes have read the entries about to be refilled
+    refill(i + DEPTH, grp);
+    grp = (grp == ring + (NG - 1) * kGroupBytes) ? ring : grp + kGroupBytes;
   }
   cp_async_wait<0>();
 
@@ -279,36 +341,43 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
   }
 }
 
-// Ring geometry shared by the staged ops: entries of `kOperands` feature rows (32*R slots of
-// 16 bytes each) plus `kScalars` per-lane scalars of the accumulation type per register.
-// Ring depth: the largest power of two (<= 16) whose ring, next to the tile metadata, lets
-// `min_ctas` blocks of kWarpsPerCta warps share one SM's shared memory.
-constexpr int pick_depth(int edge_bytes, int min_ctas, bool uses_eid) {
-  const int budget = 216 * 1024 / min_ctas / kWarpsPerCta - (GK_TUNE_TILE + kMetaPad) * (uses_eid ? 13 : 9) - 16;
-  int d = 16;
-  while (d > 2 && d * edge_bytes > budget) d >>= 1;
-  return d;
+// Ring geometry shared by the staged ops: entries of `kOperands` feature rows (32*R slots of 16 bytes each) plus
+// `kMoreBytes`; the ring holds NG groups of U entries (U = batch).  What a warp may use: one SM's shared memory
+// (228 KB, of which every resident block costs 1 KB of its own) over `min_ctas` blocks of kWarpsPerCta warps,
+// less the metadata window and `extra` bytes of scratch.
+constexpr int ring_budget(int min_ctas, bool uses_eid, int extra) {
+  return (228 * 1024 - min_ctas * 1024) / min_ctas / kWarpsPerCta - (kWin * (uses_eid ? 13 : 9) + 15) / 16 * 16 - extra;
 }
-// Edges folded together; at most half the ring, so that the other half is in flight meanwhile.
-constexpr int pick_batch(int r, int depth) {
-  const int b0 = r == 1 ? 8 : (r == 2 ? 4 : 2);
-  const int b = b0 < GK_TUNE_BATCH_MAX ? b0 : GK_TUNE_BATCH_MAX;
-  const int half = depth / 2 > 1 ? depth / 2 : 1;
-  return b < half ? b : half;
+// Batch: the largest power of two <= umax of which the ring holds at least two groups (so that one group is in
+// flight while another is folded); 1 when even that does not fit twice.
+constexpr int pick_batch(int edge_bytes, int budget, int umax) {
+  for (int u = umax; u > 1; u >>= 1)
+    if (2 * u * edge_bytes <= budget) return u;
+  return 1;
+}
+// Groups: as many as fit, at most 4, the look-ahead (NG + 1) * U staying within one metadata block.
+constexpr int pick_groups(int edge_bytes, int budget, int u) {
+  int ng = budget / (u * edge_bytes);
+  const int cap = (kWinBlock - u) / u;
+  ng = ng > 4 ? 4 : ng;
+  ng = ng > cap ? cap : ng;
+  return ng < 1 ? 1 : ng;
 }
 
-template <typename T, int R, int kOperands, int kScalars, bool kEid, int kCtasNarrow = GK_TUNE_CTAS_NARROW>
+template <typename T, int R, int kOperands, bool kEid, int kCtasNarrow = GK_CTAS_NARROW, int kExtra = 0,
+          int kMoreBytes = 0, int kForceBatch = 0>
 struct RingShape {
   using A = typename AccOf<T>::type;
   static constexpr int kRowBytes = 32 * R * 16;
-  static constexpr int kScalarBytes = 32 * R * (int)sizeof(A);
-  static constexpr int kEdgeBytes = kOperands * kRowBytes + kScalars * kScalarBytes;
+  static constexpr int kEdgeBytes = kOperands * kRowBytes + kMoreBytes;
   // 4-byte elements: 16 bytes of accumulator per slot, 64 registers are enough; 2-byte elements
   // (8 accumulators per slot) and doubles need the 80 registers of 3 resident blocks
   static constexpr int kMinCtas = R == 1 ? (sizeof(T) == 4 ? kCtasNarrow : (kCtasNarrow < 3 ? kCtasNarrow : 3))
                                          : (R == 2 ? 2 : 1);
-  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, kEid);
-  static constexpr int kBatch = pick_batch(R, kDepth);
+  static constexpr int kBudget = ring_budget(kMinCtas, kEid, kExtra);
+  static constexpr int kBatch = kForceBatch ? kForceBatch : pick_batch(kEdgeBytes, kBudget, R == 1 ? 4 : (R == 2 ? 2 : 1));
+  static constexpr int kGroups = pick_groups(kEdgeBytes, kBudget, kBatch);
+  static constexpr int kDepth = kGroups * kBatch;
 };
 
 // Sum of per-register partial dot products over the lanes of one head, lanes-per-head known at
@@ -319,13 +388,65 @@ __device__ __forceinline__ void reduce_heads_ct(A (&p)[R], int lph) {
     reduce_heads<A, R>(p, lph);
   } else {
 #pragma unroll
-    for (int o = LPH >> 1; o; o >>= 1)
+    for (int o = 1; o < LPH; o <<= 1)
 #pragma unroll
       for (int i = 0; i < R; ++i) p[i] += __shfl_xor_sync(kFull, p[i], o);
   }
 }
 
-#define GK_RING_ENTRY(pos) (ring + (size_t)((pos) & (kDepth - 1)) * kEdgeBytes)
+// Sums U (2 or 4) per-lane partials over the LPH lanes of a head so that lane l ends up holding the total of
+// value (l & (U - 1)): exchange steps in which a lane keeps half of its values and hands the other half to its
+// partner, then butterfly steps over the remaining lane bits.  For four values log2(LPH) + 1 shuffles instead of
+// 4 * log2(LPH); every sum is formed in the order of an ascending butterfly (lane distance 1, 2, 4, ...).
+template <int LPH, int U, typename A>
+__device__ __forceinline__ A reduce_transposed(const A (&s)[U], int lane) {
+  static_assert((U == 2 || U == 4) && LPH >= U && (LPH & (LPH - 1)) == 0, "2 or 4 values, lanes per head a power of two");
+  const bool b0 = (lane & 1) != 0;
+  A keep;
+  if constexpr (U == 4) {
+    const bool b1 = (lane & 2) != 0;
+    A keep0 = b0 ? s[1] : s[0];
+    A keep1 = b0 ? s[3] : s[2];
+    const A send0 = b0 ? s[0] : s[1];
+    const A send1 = b0 ? s[2] : s[3];
+    keep0 += __shfl_xor_sync(kFull, send0, 1);
+    keep1 += __shfl_xor_sync(kFull, send1, 1);
+    keep = b1 ? keep1 : keep0;
+    const A send = b1 ? keep0 : keep1;
+    keep += __shfl_xor_sync(kFull, send, 2);
+  } else {
+    keep = b0 ? s[1] : s[0];
+    const A send = b0 ? s[0] : s[1];
+    keep += __shfl_xor_sync(kFull, send, 1);
+  }
+#pragma unroll
+  for (int o = U; o < LPH; o <<= 1) keep += __shfl_xor_sync(kFull, keep, o);
+  return keep;
+}
+// Batch size, scratch and lane roles of the ops that reduce with reduce_transposed: rows of one 16-byte slot
+// per lane, 8 / 16 / 32 lanes per head.  Lane l of a head's group owns edge l & (U - 1) of the batch; the first U
+// lanes of each group publish their edge's scalar in the warp's scratch, U consecutive values per head.
+constexpr int kFastBatch = GK_FAST_BATCH;
+constexpr int kFastScratch = 128;  // 4 values of 8 bytes for each of at most 4 heads
+template <int R, int LPH> struct FastShape {
+  static constexpr bool value = R == 1 && (LPH == 8 || LPH == 16 || LPH == 32);
+};
+template <int U, typename A>
+__device__ __forceinline__ void lds_batch(A (&d)[U], const A* p) {
+  if constexpr (sizeof(A) * U == 16) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    memcpy(d, &t, 16);
+  } else if constexpr (sizeof(A) * U == 8) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    memcpy(d, &t, 8);
+  } else {
+    const uint4 t0 = reinterpret_cast<const uint4*>(p)[0], t1 = reinterpret_cast<const uint4*>(p)[1];
+    memcpy(d, &t0, 16);
+    memcpy(reinterpret_cast<unsigned char*>(d) + 16, &t1, 16);
+  }
+}
+
+#define GK_RING_SLOT(u) (ring + (u) * kEdgeBytes)
 #define GK_BATCH_LOOP(u) _Pragma("unroll") for (int u = 0; u < kBatch; ++u) if (kFullBatch || u < cnt)
 
 // ---------------------------------------------------------------------------------------
@@ -338,18 +459,14 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   using Base = AggregateOp<T, V, R, kEdgeFeat>;
   using A = typename Base::A;
   struct State : Base::State { const unsigned char* xb[R]; };
-  using Ring = RingShape<T, R, 1, 0, true>;
-  // weights: one 4- or 8-byte word per lane and register (2-byte elements travel as the aligned
-  // 4-byte word that contains them; the word's last 2 bytes may lie past an odd-sized tensor's end,
-  // inside the allocation's padding)
+  // weights: one 4- or 8-byte word per lane and register (2-byte elements travel as the aligned 4-byte word
+  // that contains them, except the last element of a tensor with an odd element count, which is read alone)
   using WWord = typename std::conditional<sizeof(T) == 8, double, uint32_t>::type;
-  static constexpr int kEdgeBytes = Ring::kRowBytes + 32 * R * (int)sizeof(WWord);
-  static constexpr int kMinCtas = Ring::kMinCtas;
-  static constexpr int kWarps = kWarpsPerCta;
+  using Ring = RingShape<T, R, 1, true, GK_CTAS_NARROW, 0, 32 * R * (int)sizeof(WWord)>;
+  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
+                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = true;
   static constexpr bool kSharedEntry = true;  // in the packed modes lanes read weights that other lanes copied
-  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, true);
-  static constexpr int kBatch = pick_batch(R, kDepth);
   // How an edge's H weights reach the ring entry (set by the host):
   //   kWeightsPerLane  every lane copies the word of its own head (any H, any element size);
   //   kWeightsWords    lane j < H copies weight j, lanes read the weight of their head (4- and 8-byte
@@ -359,6 +476,17 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   // One scattered copy per edge instead of one per lane is what the packed modes buy.
   enum { kWeightsPerLane = 0, kWeightsWords = 1, kWeightsPieces = 2 };
   int wmode = kWeightsPerLane;
+  // 2-byte elements, per-lane mode: the two elements whose aligned 4-byte word would reach outside the tensor
+  // (the first one when the tensor starts in the upper half of a word, the last one when it ends in the lower
+  // half); they are copied alone.  Null when the tensor's ends are word-aligned.
+  const T* w_first_alone = nullptr;
+  const T* w_last_alone = nullptr;
+  __host__ void set_weight_bounds(long long n_elems) {
+    if (sizeof(T) != 2 || n_elems <= 0) return;
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(this->w), hi = lo + 2 * (uintptr_t)(n_elems - 1);
+    w_first_alone = (lo & 2) ? this->w : nullptr;
+    w_last_alone = (hi & 2) ? nullptr : this->w + (n_elems - 1);
+  }
   __device__ __forceinline__ int mode() const { return kMode >= 0 ? kMode : wmode; }
 
   __host__ static int pick_wmode(const void* w, int H, int feat0, int HD, int block_elems) {
@@ -392,19 +520,25 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
       } else {
         const T* wsrc = this->w + (long long)e * this->H + st.sm.head[i];
         WWord* wdst = reinterpret_cast<WWord*>(entry + Ring::kRowBytes) + lane + 32 * i;
-        if constexpr (sizeof(T) == 2)
-          cp_async_small<4>(wdst, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(wsrc) & ~uintptr_t(3)));
-        else
+        if constexpr (sizeof(T) == 2) {
+          if (wsrc == w_first_alone || wsrc == w_last_alone) {
+            const bool up = (reinterpret_cast<uintptr_t>(wsrc) & 2) != 0;
+            reinterpret_cast<uint16_t*>(wdst)[up ? 1 : 0] = __ldg(reinterpret_cast<const uint16_t*>(wsrc));
+          } else {
+            cp_async_small<4>(wdst, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(wsrc) & ~uintptr_t(3)));
+          }
+        } else {
           cp_async_small<sizeof(T)>(wdst, wsrc);
+        }
       }
     }
   }
   __device__ __forceinline__ void prefetch_node(State&, int, int) const {}
   template <bool kFullBatch>
-  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt,
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int cnt,
                                                 const int* eids, int lane) const {
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         A xv[V];
@@ -414,7 +548,7 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
           wv = to_acc<T>(reinterpret_cast<const T*>(entry + Ring::kRowBytes)[st.sm.head[i]]);
         } else if constexpr (sizeof(T) == 2) {
           const WWord word = reinterpret_cast<const WWord*>(entry + Ring::kRowBytes)[lane + 32 * i];
-          const bool hi = (((long long)eids[u] * this->H + st.sm.head[i]) & 1) != 0;
+          const bool hi = (reinterpret_cast<uintptr_t>(this->w + (long long)eids[u] * this->H + st.sm.head[i]) & 2) != 0;
           union { uint16_t b; T t; } cvt;
           cvt.b = (uint16_t)(hi ? (word >> 16) : (word & 0xffffu));
           wv = to_acc<T>(cvt.t);
@@ -441,7 +575,7 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
-  using Ring = RingShape<T, R, 1, 0, true>;
+  using Ring = RingShape<T, R, 1, true>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = true;
@@ -454,10 +588,11 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
       st.bb[i] = reinterpret_cast<const unsigned char*>(this->b + (kEdgeFeat ? st.sm.efeat[i] : st.sm.feat[i]));
   }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
-    if constexpr (!kPrefetch) return;
-#pragma unroll
-    for (int i = 0; i < R; ++i) load_acc<T, V>(st.an[i], this->a + (long long)node * this->HD + st.sm.feat[i]);
-    st.next_node = node;
+    if constexpr (kPrefetch) {
+  #pragma unroll
+      for (int i = 0; i < R; ++i) load_acc<T, V>(st.an[i], this->a + (long long)node * this->HD + st.sm.feat[i]);
+      st.next_node = node;
+    }
   }
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
     if (kPrefetch && st.next_node == node) {
@@ -477,11 +612,11 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
     }
   }
   template <bool kFullBatch>
-  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt,
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int cnt,
                                                 const int* eids, int lane) const {
     A p[kBatch][R];
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         A bv[V];
@@ -515,14 +650,18 @@ template <typename T, int V, int R, int LPH>
 struct AttnFwdStaged : AttnFwdOp<T, V, R> {
   using Base = AttnFwdOp<T, V, R>;
   using A = typename Base::A;
-  struct State : Base::State { A qn[R][V]; int next_node; const unsigned char* kb[R]; const unsigned char* vb[R]; };
+  struct State : Base::State {
+    A qn[R][V]; int next_node; const unsigned char* kb[R]; const unsigned char* vb[R]; unsigned char* scratch;
+  };
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
   using CarryIn = typename Base::CarryIn;
-  using Ring = RingShape<T, R, 2, 0, false>;
+  static constexpr bool kFast = FastShape<R, LPH>::value;
+  using Ring = RingShape<T, R, 2, false, GK_CTAS_NARROW, kFastScratch, 0, kFast ? kFastBatch : 0>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr int kScratchBytes = kFast ? kFastScratch : 0;
   static constexpr bool kUsesEid = false;
 
   __device__ __forceinline__ void setup(State& st, int lane) const {
@@ -535,10 +674,11 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
     }
   }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
-    if constexpr (!kPrefetch) return;
-#pragma unroll
-    for (int i = 0; i < R; ++i) load_acc<T, V>(st.qn[i], this->q + (long long)node * this->HD + st.sm.feat[i]);
-    st.next_node = node;
+    if constexpr (kPrefetch) {
+  #pragma unroll
+      for (int i = 0; i < R; ++i) load_acc<T, V>(st.qn[i], this->q + (long long)node * this->HD + st.sm.feat[i]);
+      st.next_node = node;
+    }
   }
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
     const A c = this->scale * A(kLog2e);
@@ -566,12 +706,64 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
       cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.vb[i], c, rowb));
     }
   }
+  // Batch of U = 2 or 4 with one 16-byte slot per lane: the U partial dot products of a lane are reduced
+  // "transposed" (lane l of the head ends up with the score of edge l & (U - 1)), the scores travel to the head's
+  // other lanes through the warp's scratch, and every lane then forms the U probabilities itself.
   template <bool kFullBatch>
-  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+  __device__ __forceinline__ void consume_fast(State& st, const unsigned char* ring, int cnt, int lane) const {
+    constexpr int U = kFastBatch;
+    A s[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      s[u] = A(0);
+      if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
+        A kv[V];
+        lds_acc<T, V>(kv, GK_RING_SLOT(u) + lane * 16);
+        s[u] = st.q[0][0] * kv[0];
+#pragma unroll
+        for (int e = 1; e < V; ++e) s[u] += st.q[0][e] * kv[e];
+      }
+    }
+    A mine = reduce_transposed<LPH, U, A>(s, lane);
+    if (!kFullBatch && (lane & (U - 1)) >= cnt) mine = neg_inf<A>();  // positions past the batch: probability 0
+    A* sc = reinterpret_cast<A*>(st.scratch) + (lane / LPH) * U;
+    if ((lane & (LPH - 1)) < U) sc[lane & (U - 1)] = mine;
+    __syncwarp();
+    A sv[U];
+    lds_batch<U, A>(sv, sc);
+    A mn = st.m[0];
+#pragma unroll
+    for (int u = 0; u < U; ++u) mn = sv[u] > mn ? sv[u] : mn;
+    const A corr = gk_exp2(st.m[0] - mn);  // m = -inf at a node's first batch: 2^-inf = 0
+    A p[U];
+    A psum = A(0);
+#pragma unroll
+    for (int u = 0; u < U; ++u) { p[u] = gk_exp2(sv[u] - mn); psum += p[u]; }
+    st.m[0] = mn;
+    st.l[0] = st.l[0] * corr + psum;
+#pragma unroll
+    for (int e = 0; e < V; ++e) st.acc[0][e] *= corr;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (kFullBatch || u < cnt) {
+        A vv[V];
+        lds_acc<T, V>(vv, GK_RING_SLOT(u) + Ring::kRowBytes + lane * 16);
+#pragma unroll
+        for (int e = 0; e < V; ++e) st.acc[0][e] += p[u] * vv[e];
+      }
+    }
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int cnt, const int*,
                                                 int lane) const {
+    if constexpr (kFast) consume_fast<kFullBatch>(st, ring, cnt, lane);
+    else consume_slow<kFullBatch>(st, ring, cnt, lane);
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_slow(State& st, const unsigned char* ring, int cnt, int lane) const {
     A s[kBatch][R];
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         A kv[V];
@@ -594,7 +786,7 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
       for (int e = 0; e < V; ++e) st.acc[i][e] *= corr;
     }
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u) + Ring::kRowBytes;
+      const unsigned char* entry = GK_RING_SLOT(u) + Ring::kRowBytes;
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const A p = gk_exp2(s[u][i] - st.m[i]);
@@ -645,20 +837,32 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   using Base = AttnBwdDstOp<T, V, R>;
   using A = typename Base::A;
   struct State : Base::State {
-    A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node; int tile_base;
+    A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node; int tile_base; int batch_pos;
     const unsigned char* kb[R]; const unsigned char* vb[R];
-    unsigned char* pdw[R];  // where this lane writes its head's (p, ds) of edge 0, or null: not the head's writer
+    unsigned char* pdw[R];  // where this lane writes its head's (p, ds) of edge 0, or null: not a writer
+    unsigned char* scratch;
   };
   static constexpr bool kTileBase = true;
   EdgePair<A>* __restrict__ pd = nullptr;  // (n_edges, Hp) out when not null: (p, ds) of every edge, by position
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
-  using Ring = RingShape<T, R, 2, 0, false>;
+  static constexpr bool kFast = FastShape<R, LPH>::value;
+  using Ring = RingShape<T, R, 2, false, GK_CTAS_DST, kFastScratch, 0, kFast ? kFastBatch : 0>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
+  static constexpr int kScratchBytes = kFast ? kFastScratch : 0;
   static constexpr bool kUsesEid = false;
+  static constexpr bool kNodeRows = true;
 
+  __device__ __forceinline__ void prefetch_rows_l2(int node) const {
+    const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
+    const long long at = (long long)node * this->HD;
+    prefetch_row_l2(this->q + at, rowb);
+    prefetch_row_l2(this->dout + at, rowb);
+    prefetch_row_l2(this->o + at, rowb);
+    prefetch_l2(this->lse + (long long)node * this->H);
+  }
   __device__ __forceinline__ void setup(State& st, int lane) const {
     Base::setup(st, lane);
     st.next_node = -1;
@@ -666,21 +870,76 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
     for (int i = 0; i < R; ++i) {
       st.kb[i] = reinterpret_cast<const unsigned char*>(this->k + st.sm.feat[i]);
       st.vb[i] = reinterpret_cast<const unsigned char*>(this->v + st.sm.feat[i]);
-      st.pdw[i] = (pd && st.sm.ok[i] && st.sm.efeat[i] == 0) ? reinterpret_cast<unsigned char*>(pd + st.sm.head[i])
-                                                              : nullptr;
+      // the slow path writes a head's pair from the lane that holds the head's first slot; the fast path from
+      // the first U lanes of the head's group, lane j writing edge j of the batch
+      const bool writer = kFast ? (lane & (LPH - 1)) < kFastBatch : st.sm.efeat[i] == 0;
+      st.pdw[i] = (pd && st.sm.ok[i] && writer)
+                      ? reinterpret_cast<unsigned char*>(pd + st.sm.head[i]) +
+                            (kFast ? (size_t)(lane & (kFastBatch - 1)) * (size_t)this->Hp * sizeof(EdgePair<A>) : (size_t)0)
+                      : nullptr;
+    }
+  }
+  // Batch of U = 2 or 4, one 16-byte slot per lane: q.k and dO.v of the U edges are reduced transposed, so lane l
+  // of a head holds both sums of edge l & (U - 1) and forms that edge's p and ds alone (one ex2 per lane and
+  // batch); the first U lanes of the head store the pairs (consecutive positions, consecutive heads: whole
+  // 32-byte sectors) and publish ds in the warp's scratch for the accumulation of dq.
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_fast(State& st, const unsigned char* ring, int cnt, int lane) const {
+    constexpr int U = kFastBatch;
+    A s[U], dp[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      s[u] = A(0);
+      dp[u] = A(0);
+      if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
+        const unsigned char* entry = GK_RING_SLOT(u);
+        A kv[V], vv[V];
+        lds_acc<T, V>(kv, entry + lane * 16);
+        lds_acc<T, V>(vv, entry + Ring::kRowBytes + lane * 16);
+        s[u] = st.q[0][0] * kv[0];
+        dp[u] = st.g[0][0] * vv[0];
+#pragma unroll
+        for (int e = 1; e < V; ++e) { s[u] += st.q[0][e] * kv[e]; dp[u] += st.g[0][e] * vv[e]; }
+      }
+    }
+    const A s_mine = reduce_transposed<LPH, U, A>(s, lane);
+    const A dp_mine = reduce_transposed<LPH, U, A>(dp, lane);
+    const A p = gk_exp2(s_mine - st.lse[0]);
+    A ds = p * (dp_mine - st.delta[0]) * this->scale;
+    const bool live = kFullBatch || (lane & (U - 1)) < cnt;
+    if (!live) ds = A(0);
+    if (st.pdw[0] && live) {
+      const unsigned pairb = (unsigned)this->Hp * (unsigned)sizeof(EdgePair<A>);
+      *reinterpret_cast<EdgePair<A>*>(st.pdw[0] + (unsigned long long)(unsigned)(st.tile_base + st.batch_pos) * pairb) =
+          EdgePair<A>{p, ds};
+    }
+    A* sc = reinterpret_cast<A*>(st.scratch) + (lane / LPH) * U;
+    if ((lane & (LPH - 1)) < U) sc[lane & (U - 1)] = ds;
+    __syncwarp();
+    A dsv[U];
+    lds_batch<U, A>(dsv, sc);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (kFullBatch || u < cnt) {
+        A kv[V];
+        lds_acc<T, V>(kv, GK_RING_SLOT(u) + lane * 16);
+#pragma unroll
+        for (int e = 0; e < V; ++e) st.acc[0][e] += dsv[u] * kv[e];
+      }
     }
   }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
-    if constexpr (!kPrefetch) return;
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const long long off = (long long)node * this->HD + st.sm.feat[i];
-      load_acc<T, V>(st.qn[i], this->q + off);
-      load_acc<T, V>(st.gn[i], this->dout + off);
-      load_acc<T, V>(st.on[i], this->o + off);
-      st.lsen[i] = __ldg(this->lse + (long long)node * this->H + st.sm.head[i]);
+    if constexpr (kPrefetch) {
+  #pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const long long off = (long long)node * this->HD + st.sm.feat[i];
+        load_acc<T, V>(st.qn[i], this->q + off);
+        load_acc<T, V>(st.gn[i], this->dout + off);
+        load_acc<T, V>(st.on[i], this->o + off);
+        st.lsen[i] = __ldg(this->lse + (long long)node * this->H + st.sm.head[i]);
+      }
+      st.next_node = node;
     }
-    st.next_node = node;
   }
   // q scaled to base-2 score units, lse converted to base 2
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
@@ -699,7 +958,10 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
           dl[i] += st.g[i][e] * st.on[i][e];
         }
       }
-      reduce_heads_ct<LPH, A, R>(dl, this->lph);
+      // the fast path sums dO.v in the ascending order: delta the same way, so that a node with a single edge
+      // gets dp - delta = 0 exactly
+      if constexpr (kFast) dl[0] = reduce_ascending<LPH, A>(dl[0]);
+      else reduce_heads_ct<LPH, A, R>(dl, this->lph);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         st.delta[i] = dl[i];
@@ -708,7 +970,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
       }
       return;
     }
-    Base::begin(st, node, lane);
+    Base::template begin_ordered<(kFast ? LPH : 0)>(st, node, lane);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       st.lse[i] *= A(kLog2e);
@@ -725,12 +987,17 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
     }
   }
   template <bool kFullBatch>
-  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int cnt, const int*,
                                                 int lane) const {
+    if constexpr (kFast) consume_fast<kFullBatch>(st, ring, cnt, lane);
+    else consume_slow<kFullBatch>(st, ring, cnt, lane);
+  }
+  template <bool kFullBatch>
+  __device__ __forceinline__ void consume_slow(State& st, const unsigned char* ring, int cnt, int lane) const {
     const unsigned pairb = (unsigned)this->Hp * (unsigned)sizeof(EdgePair<A>);
     A s[kBatch][R], dp[kBatch][R];
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         A kv[V], vv[V];
@@ -745,13 +1012,13 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
     GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
     // the k row is read again rather than kept: registers matter more than the second read
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const A p = gk_exp2(s[u][i] - st.lse[i]);
         const A ds = p * (dp[u][i] - st.delta[i]) * this->scale;
         if (st.pdw[i])
-          *reinterpret_cast<EdgePair<A>*>(st.pdw[i] + (unsigned long long)(unsigned)(st.tile_base + i0 + u) * pairb) =
+          *reinterpret_cast<EdgePair<A>*>(st.pdw[i] + (unsigned long long)(unsigned)(st.tile_base + st.batch_pos + u) * pairb) =
               EdgePair<A>{p, ds};
         A kv[V];
         lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
@@ -774,28 +1041,27 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
-  using Ring = RingShape<T, R, 2, 0, false, GK_TUNE_CTAS_SRC>;
   // (lse, delta) pairs of the most heads this instantiation can see: 32 * R / LPH (every head when the
   // lanes per head are only known at run time), at least one 16-byte piece
   static constexpr int kMaxHeads = LPH ? (32 * R / LPH > 2 ? 32 * R / LPH : 2) : 32 * R;
   static constexpr int kPairBytes = (kMaxHeads * (int)sizeof(StatPair<A>) + 15) / 16 * 16;
-  static constexpr int kEdgeBytes = 2 * Ring::kRowBytes + kPairBytes;
-  static constexpr int kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
-  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, false);
-  static constexpr int kBatch = pick_batch(R, kDepth);
+  using Ring = RingShape<T, R, 2, false, 3, 0, kPairBytes, R == 1 ? 2 : 0>;
+  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
+                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = false;
   static constexpr bool kSharedEntry = true;  // lanes read pair bytes that other lanes copied
 
   __device__ __forceinline__ void setup(State& st, int lane) const { Base::setup(st, lane); st.next_node = -1; }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
-    if constexpr (!kPrefetch) return;
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-      const long long off = (long long)node * this->HD + st.sm.feat[i];
-      load_acc<T, V>(st.kn[i], this->k + off);
-      load_acc<T, V>(st.vn[i], this->v + off);
+    if constexpr (kPrefetch) {
+  #pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const long long off = (long long)node * this->HD + st.sm.feat[i];
+        load_acc<T, V>(st.kn[i], this->k + off);
+        load_acc<T, V>(st.vn[i], this->v + off);
+      }
+      st.next_node = node;
     }
-    st.next_node = node;
   }
   // k scaled to base-2 score units
   __device__ __forceinline__ void begin(State& st, int node, int lane) const {
@@ -834,11 +1100,11 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
     }
   }
   template <bool kFullBatch>
-  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int cnt, const int*,
                                                 int lane) const {
     A s[kBatch][R], dp[kBatch][R];
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         A qv[V], gv[V];
@@ -853,7 +1119,7 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
     GK_BATCH_LOOP(u) { reduce_heads_ct<LPH, A, R>(s[u], this->lph); reduce_heads_ct<LPH, A, R>(dp[u], this->lph); }
     // the q and dout rows are read again rather than kept: registers matter more than the second read
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
       const StatPair<A>* sc = reinterpret_cast<const StatPair<A>*>(entry + 2 * Ring::kRowBytes);
 #pragma unroll
       for (int i = 0; i < R; ++i) {
@@ -884,16 +1150,15 @@ struct AttnBwdSrcPairsStaged : AttnBwdSrcOp<T, V, R> {
   using Base = AttnBwdSrcOp<T, V, R>;
   using A = typename Base::A;
   struct State : Base::State { const unsigned char* qb[R]; const unsigned char* gb[R]; };
-  using Ring = RingShape<T, R, 2, 0, true, GK_TUNE_CTAS_SRC>;
   static constexpr int kMaxHeads = LPH ? (32 * R / LPH > 2 ? 32 * R / LPH : 2) : 32 * R;
   static constexpr int kPairBytes = (kMaxHeads * (int)sizeof(EdgePair<A>) + 15) / 16 * 16;
-  static constexpr int kEdgeBytes = 2 * Ring::kRowBytes + kPairBytes;
-  static constexpr int kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
-  static constexpr int kDepth = pick_depth(kEdgeBytes, kMinCtas, true);
-  static constexpr int kBatch = pick_batch(R, kDepth);
+  using Ring = RingShape<T, R, 2, true, GK_CTAS_SRC, 0, kPairBytes>;
+  static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
+                       kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = true;
   static constexpr bool kSharedEntry = true;  // lanes read pair bytes that other lanes copied
   const EdgePair<A>* __restrict__ pd;          // (n_edges, Hp) by edge id, from the destination pass
+
 
   __device__ __forceinline__ void setup(State& st, int lane) const {
     Base::setup(st, lane);
@@ -924,10 +1189,10 @@ struct AttnBwdSrcPairsStaged : AttnBwdSrcOp<T, V, R> {
     }
   }
   template <bool kFullBatch>
-  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int i0, int cnt, const int*,
+  __device__ __forceinline__ void consume_batch(State& st, const unsigned char* ring, int cnt, const int*,
                                                 int lane) const {
     GK_BATCH_LOOP(u) {
-      const unsigned char* entry = GK_RING_ENTRY(i0 + u);
+      const unsigned char* entry = GK_RING_SLOT(u);
       const EdgePair<A>* pr = reinterpret_cast<const EdgePair<A>*>(entry + 2 * Ring::kRowBytes);
 #pragma unroll
       for (int i = 0; i < R; ++i) {

@@ -13,6 +13,8 @@ Differences from the reference, all supersets: index tensors may be int32 as wel
 and float64; ``dy`` is made contiguous instead of being read unchecked
 (graphop.cpp:120-130, 148-153); the source and destination node counts may differ.
 """
+import weakref
+
 import torch as th
 
 from . import _capi
@@ -157,35 +159,57 @@ def node_mul_edge_backward(row, indptr, eid, A, B, dy):
     return [dA, dB]
 
 
-def _softmax_nodes(e):
-    # The reference sizes its per-node scratch by the edge count and indexes it by node id
-    # (graphop_kernel.cu:420-427): node ids must stay below the number of edges.
-    return e
+_NODE_BOUNDS = {}   # id(row tensor) -> (weak reference, version counter, bound)
 
 
-def sparse_softmax_forward(row, indptr, eid, x):
-    """Softmax of x over the edges of each node, per head; x is (e,) or (e, h)."""
+def _softmax_nodes(row, num_nodes=None):
+    """Rows of the per-node statistics the softmax kernels index by node id: largest node id + 1.
+
+    The reference sizes that scratch by the edge count (graphop_kernel.cu:420-427), which wastes memory on
+    dense graphs and is too small for a graph whose node ids exceed its edge count.  ``row`` is non-decreasing,
+    so its last entry is the largest id: it is read back once per chunk table (a small device-to-host copy
+    that waits for the stream) and remembered while the tensor object lives unmodified.  Pass ``num_nodes`` to
+    skip the read."""
+    if num_nodes is not None:
+        return int(num_nodes)
+    if row.numel() == 0:
+        return 0
+    hit = _NODE_BOUNDS.get(id(row))
+    if hit is not None and hit[0]() is row and hit[1] == row._version:
+        return hit[2]
+    bound = int(row[-1].item()) + 1
+    if len(_NODE_BOUNDS) >= 256:
+        _NODE_BOUNDS.clear()
+    _NODE_BOUNDS[id(row)] = (weakref.ref(row), row._version, bound)
+    return bound
+
+
+def sparse_softmax_forward(row, indptr, eid, x, num_nodes=None):
+    """Softmax of x over the edges of each node, per head; x is (e,) or (e, h).  ``num_nodes`` (an addition):
+    a bound on node id + 1 when the caller knows it."""
     _check_all(row=row, indptr=indptr, eid=eid, x=x)
     elem, index = _elem(x), _index(row, indptr, eid)
     h = _heads(x, False)
     e, c = eid.size(0), _chunks(row, indptr)
     y = th.empty_like(x)
+    n = _softmax_nodes(row, num_nodes)
     with th.cuda.device(x.device):
-        _call("sparse_softmax_forward", elem, index, _capi.OP_SOFTMAX_FWD, e, _softmax_nodes(e), h, 1, x.device,
-              [_p(row), _p(indptr), _p(eid), _p(x), _p(y), c, e, _softmax_nodes(e), h])
+        _call("sparse_softmax_forward", elem, index, _capi.OP_SOFTMAX_FWD, e, n, h, 1, x.device,
+              [_p(row), _p(indptr), _p(eid), _p(x), _p(y), c, e, n, h])
     return y
 
 
-def sparse_softmax_backward(row, indptr, eid, y, dy):
+def sparse_softmax_backward(row, indptr, eid, y, dy, num_nodes=None):
     """dx = y * (dy - sum over the node of dy * y)."""
     _check_all(row=row, indptr=indptr, eid=eid, y=y, dy=dy)
     elem, index = _elem(y, dy), _index(row, indptr, eid)
     h = _heads(dy, False)
     e, c = eid.size(0), _chunks(row, indptr)
     dx = th.empty_like(dy)
+    n = _softmax_nodes(row, num_nodes)
     with th.cuda.device(y.device):
-        _call("sparse_softmax_backward", elem, index, _capi.OP_SOFTMAX_BWD, e, _softmax_nodes(e), h, 1, y.device,
-              [_p(row), _p(indptr), _p(eid), _p(y), _p(dy), _p(dx), c, e, _softmax_nodes(e), h])
+        _call("sparse_softmax_backward", elem, index, _capi.OP_SOFTMAX_BWD, e, n, h, 1, y.device,
+              [_p(row), _p(indptr), _p(eid), _p(y), _p(dy), _p(dx), c, e, n, h])
     return dx
 
 

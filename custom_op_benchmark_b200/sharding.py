@@ -12,7 +12,10 @@ module adds the split the large configurations need:
   all-gather of the source-feature shards (features are sharded evenly by node id);
 * the backward's dx uses the transposed CSR cut the same way by *source* node, with dy
   all-gathered, so every gradient row is owned by exactly one rank: no reduce-scatter and no
-  atomics, results stay bit-reproducible.  dedata needs no exchange at all.
+  atomics, results stay bit-reproducible.  dedata needs no exchange at all;
+* edge weights are sharded like the edges: a rank holds the weights of its own destination rows only.
+  The transposed shard reads weights of edges that other ranks own, so they travel every step (they are the
+  softmax output in training and change with every step): one more exchange, by edge id.
 
 All-gathering a node tensor delivers (P-1)/P of it to every rank whatever P is.  The alternative,
 built once per graph by ``plan_shard_exchange``, fetches from their owners only the rows a shard's
@@ -31,7 +34,7 @@ from .part_csr import partition_csr
 
 __all__ = ["balanced_bounds", "even_bounds", "GraphShard", "shard_graph", "all_gather_rows",
            "RowExchange", "ShardExchange", "plan_row_exchange", "plan_shard_exchange", "exchange_rows",
-           "sharded_spmm_forward", "sharded_spmm_backward"]
+           "gather_edge_weights", "sharded_spmm_forward", "sharded_spmm_backward"]
 
 
 def balanced_bounds(indptr, parts):
@@ -71,6 +74,7 @@ class GraphShard:
     eid_t: th.Tensor
     indices_t: th.Tensor
     edge_lo: int          # global edge id of the rank's first row-CSR edge
+    edge_bounds: th.Tensor = None  # (parts + 1,) global edge id ranges of the ranks' row shards
 
     @property
     def rows(self):
@@ -97,7 +101,8 @@ def shard_graph(g, rank, parts, chunk_size=32, index_dtype=th.int32):
     cv = lambda t: t.to(index_dtype).contiguous()
     return GraphShard(rank, parts, g.n_dst, g.n_src, db, sb,
                       cv(row), cv(ptr), cv(th.arange(hi - lo, device=ip.device)), cv(g.indices[lo:hi]),
-                      cv(col), cv(ptr_t), cv(g.eid_t[tlo:thi]), cv(g.indices_t[tlo:thi]), lo)
+                      cv(col), cv(ptr_t), cv(g.eid_t[tlo:thi]), cv(g.indices_t[tlo:thi]), lo,
+                      ip[db.to(ip.device)].to("cpu"))
 
 
 def all_gather_rows(local, bounds, group=None, async_op=False):
@@ -149,11 +154,13 @@ class RowExchange:
 
 @dataclass
 class ShardExchange:
-    """Both exchanges of a sharded SpMM step and the shard's indices renumbered into the received rows."""
+    """The exchanges of a sharded SpMM step and the shard's indices renumbered into the received rows."""
     x: RowExchange            # source features, owners by even_bounds(n_src)
     dy: RowExchange           # upstream gradient rows, owners by the shard's dst_bounds
+    w: RowExchange            # weights of the transposed shard's edges, owners by the shard's edge_bounds
     indices: th.Tensor        # sh.indices as positions in x.needed
     indices_t: th.Tensor      # sh.indices_t as positions in dy.needed
+    eid_t: th.Tensor          # sh.eid_t as positions in w.needed
 
 
 def plan_row_exchange(indices, owner_bounds, rank, group=None):
@@ -191,10 +198,11 @@ def plan_row_exchange(indices, owner_bounds, rank, group=None):
 
 
 def plan_shard_exchange(sh, group=None):
-    """The two exchanges of `sh` (collective; once per graph)."""
+    """The three exchanges of `sh` (collective; once per graph)."""
     x_plan, ic = plan_row_exchange(sh.indices, even_bounds(sh.n_src, sh.parts), sh.rank, group)
     dy_plan, itc = plan_row_exchange(sh.indices_t, sh.dst_bounds, sh.rank, group)
-    return ShardExchange(x_plan, dy_plan, ic.contiguous(), itc.contiguous())
+    w_plan, etc = plan_row_exchange(sh.eid_t, sh.edge_bounds, sh.rank, group)
+    return ShardExchange(x_plan, dy_plan, w_plan, ic.contiguous(), itc.contiguous(), etc.contiguous())
 
 
 def _torch_gather_rows(table, idx, out=None):
@@ -236,11 +244,22 @@ def sharded_spmm_forward(sh, edata_local, x_shard, ops=None, group=None, exchang
     return y, x_all
 
 
-def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all, ops=None, group=None, exchange=None):
+def gather_edge_weights(sh, edata_local, group=None, exchange=None):
+    """Weights of the transposed shard's edges.  With `exchange`: (weights of exactly those edges, fetched from
+    the ranks that own them, indexed by exchange.eid_t).  Without: (every rank's weights all-gathered, indexed by
+    global edge id, i.e. by sh.eid_t).  Returns (weights, edge ids to read them with)."""
+    if exchange is not None:
+        rows = exchange_rows(edata_local.reshape(edata_local.shape[0], -1), exchange.w, group)
+        return rows.reshape((rows.shape[0],) + tuple(edata_local.shape[1:])), exchange.eid_t
+    return all_gather_rows(edata_local, sh.edge_bounds, group), sh.eid_t
+
+
+def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all=None, ops=None, group=None, exchange=None):
     """(dedata_local, dx_owned): gradients of the owned edges' weights, and of the source rows this
-    rank owns in the transposed split.  `edata_all`: the weights of all edges by global edge id
-    (gathered once per graph by the caller; the transposed CSR reads them through eid_t).  `x_all`: what
-    the forward returned (with `exchange`: the referenced rows)."""
+    rank owns in the transposed split.  `x_all`: what the forward returned (with `exchange`: the referenced
+    rows).  The transposed shard needs the weights of edges other ranks own: they are exchanged here, every
+    call, unless the caller passes `edata_all` (all weights by global edge id, e.g. a graph whose weights never
+    change)."""
     ops = ops or _default_ops()
     # the rows of dy are only needed by dx: their transfer is enqueued first and travels while dedata is computed
     if exchange is not None:
@@ -250,11 +269,15 @@ def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all, ops=None,
     else:
         dy_rows, pending = all_gather_rows(dy_local, sh.dst_bounds, group, async_op=True)
         src_ids, dst_ids = sh.indices, sh.indices_t
+    if edata_all is not None:
+        w_t, eid_t = edata_all, sh.eid_t
+    else:
+        w_t, eid_t = gather_edge_weights(sh, edata_local, group, exchange)
     # dedata: sampled dot products of the owned rows of dy against the source rows; no exchange.
     # The op reads dy by destination id and the local chunk table names local rows 0..rows-1.
     dedata = ops.maskedmm_csr_forward(sh.row, sh.indptr, sh.eid, src_ids, dy_local, x_all)
     if pending is not None:
         pending.wait()
-    # dx: row-owned aggregation over the transposed shard, weights by global edge id
-    dx = ops.vector_spmm_forward(sh.col, sh.indptr_t, sh.eid_t, dst_ids, edata_all, dy_rows, num_dst=sh.cols)
+    # dx: row-owned aggregation over the transposed shard
+    dx = ops.vector_spmm_forward(sh.col, sh.indptr_t, eid_t, dst_ids, w_t, dy_rows, num_dst=sh.cols)
     return dedata, dx

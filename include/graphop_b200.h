@@ -70,29 +70,6 @@ const char* graphop_error_string(int code);
 /* cudaError_t of the most recent failed CUDA call made by this library on this thread. */
 int graphop_last_cuda_error(void);
 
-/* Number of kernels this library has launched in this process so far. */
-long long graphop_launch_count(void);
-
-/* Per-kernel device timing, for benchmarks.  Between graphop_profile_begin(stream) and
- * graphop_profile_end() every kernel the library launches is followed by a CUDA event on its
- * stream (all calls must use that one stream).  graphop_profile_end() waits for the last event
- * and returns the number n of kernels timed (-1 on a CUDA error): ms[i] is the device time of
- * the i-th kernel and `names` receives the n kernel names, one per line.  Not thread-safe.  The
- * reference has no counterpart; it times whole calls with time.time() (wrapper.py:154-160). */
-int graphop_profile_begin(graphop_stream_t stream);
-int graphop_profile_end(char* names, size_t names_bytes, float* ms, int max_entries);
-
-/* Gather ceiling, for benchmarks.  For every position k < n_edges a warp reads the row_bytes-byte
- * row table0[indices[k]] (and table1[indices[k]] when table1 is not NULL) and nothing else: no
- * arithmetic beyond a checksum that is never stored, no shared memory, every lane 16 bytes of each
- * row, four edges of loads in flight per warp at 64 warps per SM.  The time of this launch is what
- * gathering one row per edge from these tables through this index stream costs on the GPU at hand,
- * whatever is then done with the rows; the benchmark reports each walker kernel against it.
- * row_bytes: a multiple of 16, at most 512; tables 16-byte aligned; sink: 4 writable bytes (written
- * only if a warp's checksum hits one particular value; the rows are summed as floats, any bit pattern will do).  The reference has no counterpart. */
-int graphop_gather_probe_i32(const int32_t* indices, int64_t n_edges, const void* table0, const void* table1,
-                             int row_bytes, void* sink, graphop_stream_t stream);
-
 /* out[r, :] = table[idx[r], :] for r < n_rows, rows of row_bytes bytes (a multiple of 16; both tensors
  * 16-byte aligned).  Packs the rows a peer asked for before they are sent, and the rows a shard references
  * from its own block (sharded SpMM).  The reference runs on one device and has no counterpart. */

@@ -7,6 +7,9 @@ extension module exporting the reference's eight functions; tests and the golden
 load it with `load_reference()`.  Nothing in the product package touches it.
 
     python oracle/build_reference.py [reference_dir]
+
+The reference checkout is found, in this order, from the command line, from the environment
+variable GRAPHOP_REFERENCE_DIR, or as a directory named `reference` beside this repository.
 """
 import glob
 import importlib.util
@@ -18,8 +21,13 @@ OUT = os.path.join(HERE, "_ref")
 NAME = "graphop_ref"
 
 
-def build(ref_dir="/root/reference", verbose=False):
+def default_reference_dir():
+    return os.environ.get("GRAPHOP_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_dir=None, verbose=False):
     from torch.utils.cpp_extension import load
+    ref_dir = ref_dir or default_reference_dir()
     os.makedirs(OUT, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     src = os.path.join(ref_dir, "graphop")
@@ -42,7 +50,7 @@ def load_reference():
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else default_reference_dir()
     if not os.path.isdir(ref):
         print("reference checkout not found at", ref)
         sys.exit(0)

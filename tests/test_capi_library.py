@@ -20,7 +20,19 @@ def _header_symbols():
 
 def test_header_and_binding_agree():
     assert _header_symbols() == sorted(_capi.exported_symbols())
-    assert len(_header_symbols()) == 10 * 6 + 13
+    assert len(_header_symbols()) == 10 * 6 + 9
+
+
+def test_product_library_carries_no_benchmark_hooks():
+    """Launch accounting, per-kernel timing and the gather probe live in the benchmark's instrumented twin only."""
+    out = subprocess.run(["nm", "-D", "--defined-only", _capi.LIB_PATH], capture_output=True, text=True).stdout
+    assert not re.findall(r"graphop_bench_\w+|graphop_profile_\w+|graphop_launch_count|graphop_gather_probe", out)
+    twin = os.path.join(os.path.dirname(_capi.LIB_PATH), "libgraphop_b200_bench.so")
+    if os.path.exists(twin):
+        sym = subprocess.run(["nm", "-D", "--defined-only", twin], capture_output=True, text=True).stdout
+        for name in ("graphop_bench_launch_count", "graphop_bench_profile_begin", "graphop_bench_profile_end",
+                     "graphop_bench_gather_probe_i32", "graphop_attention_forward_f32_i32"):
+            assert " T %s" % name in sym, name
 
 
 def test_library_exports_every_declared_symbol():

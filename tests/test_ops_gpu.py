@@ -377,20 +377,23 @@ def test_gather_rows_is_an_exact_copy(shape, dtype, idt):
 
 
 def test_gather_probe_status_codes():
-    """The benchmark's gather probe: runs on valid arguments (it has no output to compare), refuses the rest."""
+    """The benchmark's gather probe (instrumented twin of the library): runs on valid arguments (it has no output
+    to compare), refuses the rest."""
+    import bench
     from custom_op_benchmark_b200 import _capi
-    lib = _capi.lib()
+    lib = bench.Twin().h
+    probe = lib.graphop_bench_gather_probe_i32
     table = th.randn(100, 128, device=DEV)
     narrow = th.randn(100, 12, device=DEV)      # 48-byte rows: allowed (a multiple of 16)
     idx = th.randint(0, 100, (1000,), dtype=th.int32, device=DEV)
     sink = th.zeros(1, dtype=th.int32, device=DEV)
     st = th.cuda.current_stream().cuda_stream
-    assert lib.graphop_gather_probe_i32(idx.data_ptr(), 1000, table.data_ptr(), table.data_ptr(), 512, sink.data_ptr(), st) == _capi.OK
-    assert lib.graphop_gather_probe_i32(idx.data_ptr(), 1000, table.data_ptr(), None, 512, sink.data_ptr(), st) == _capi.OK
-    assert lib.graphop_gather_probe_i32(idx.data_ptr(), 1000, narrow.data_ptr(), None, 48, sink.data_ptr(), st) == _capi.OK
-    assert lib.graphop_gather_probe_i32(idx.data_ptr(), 0, table.data_ptr(), None, 512, sink.data_ptr(), st) == _capi.OK
-    assert lib.graphop_gather_probe_i32(idx.data_ptr(), 1000, table.data_ptr(), None, 24, sink.data_ptr(), st) == _capi.ERR_UNSUPPORTED
-    assert lib.graphop_gather_probe_i32(idx.data_ptr(), 1000, table.data_ptr(), None, 1024, sink.data_ptr(), st) == _capi.ERR_UNSUPPORTED
-    assert lib.graphop_gather_probe_i32(None, 1000, table.data_ptr(), None, 512, sink.data_ptr(), st) == _capi.ERR_INVALID_ARGUMENT
+    assert probe(idx.data_ptr(), 1000, table.data_ptr(), table.data_ptr(), 512, sink.data_ptr(), st) == _capi.OK
+    assert probe(idx.data_ptr(), 1000, table.data_ptr(), None, 512, sink.data_ptr(), st) == _capi.OK
+    assert probe(idx.data_ptr(), 1000, narrow.data_ptr(), None, 48, sink.data_ptr(), st) == _capi.OK
+    assert probe(idx.data_ptr(), 0, table.data_ptr(), None, 512, sink.data_ptr(), st) == _capi.OK
+    assert probe(idx.data_ptr(), 1000, table.data_ptr(), None, 24, sink.data_ptr(), st) == _capi.ERR_UNSUPPORTED
+    assert probe(idx.data_ptr(), 1000, table.data_ptr(), None, 1024, sink.data_ptr(), st) == _capi.ERR_UNSUPPORTED
+    assert probe(None, 1000, table.data_ptr(), None, 512, sink.data_ptr(), st) == _capi.ERR_INVALID_ARGUMENT
     th.cuda.synchronize()
     assert int(sink.item()) == 0

@@ -93,7 +93,11 @@ def _worker(rank, world, port, out_dir):
     r0, r1 = int(sh.dst_bounds[rank]), int(sh.dst_bounds[rank + 1])
     y, x_all = sharding.sharded_spmm_forward(sh, w[lo:hi].contiguous(), x[int(xb[rank]):int(xb[rank + 1])].contiguous(),
                                              ops=orc)
-    dw, dx = sharding.sharded_spmm_backward(sh, w[lo:hi].contiguous(), dy[r0:r1].contiguous(), x_all, w, ops=orc)
+    # weights sharded like the edges: the transposed shard's weights are all-gathered inside the call
+    dw, dx = sharding.sharded_spmm_backward(sh, w[lo:hi].contiguous(), dy[r0:r1].contiguous(), x_all, ops=orc)
+    # ... or handed over by a caller that keeps every weight on every rank
+    dw0, dx0 = sharding.sharded_spmm_backward(sh, w[lo:hi].contiguous(), dy[r0:r1].contiguous(), x_all, w, ops=orc)
+    assert th.equal(dw0, dw) and th.equal(dx0, dx)
     # the same step fetching only the referenced rows
     ex = sharding.plan_shard_exchange(sh)
     assert th.equal(ex.x.needed[ex.indices.long()], sh.indices.long())
@@ -103,7 +107,11 @@ def _worker(rank, world, port, out_dir):
     y2, x_rows = sharding.sharded_spmm_forward(sh, w[lo:hi].contiguous(),
                                                x[int(xb[rank]):int(xb[rank + 1])].contiguous(), ops=orc, exchange=ex)
     assert th.equal(x_rows, x[ex.x.needed])
-    dw2, dx2 = sharding.sharded_spmm_backward(sh, w[lo:hi].contiguous(), dy[r0:r1].contiguous(), x_rows, w, ops=orc,
+    # the weights of the transposed shard's edges travel by edge id, from the ranks that own them
+    assert th.equal(ex.w.needed[ex.eid_t.long()], sh.eid_t.long())
+    w_t, ids = sharding.gather_edge_weights(sh, w[lo:hi].contiguous(), exchange=ex)
+    assert th.equal(w_t[ids.long()], w[sh.eid_t.long()])
+    dw2, dx2 = sharding.sharded_spmm_backward(sh, w[lo:hi].contiguous(), dy[r0:r1].contiguous(), x_rows, ops=orc,
                                               exchange=ex)
     th.save({"y": y, "dw": dw, "dx": dx, "y2": y2, "dw2": dw2, "dx2": dx2, "rows": (r0, r1), "edges": (lo, hi),
              "cols": (int(sh.src_bounds[rank]), int(sh.src_bounds[rank + 1]))}, os.path.join(out_dir, "r%d.pt" % rank))

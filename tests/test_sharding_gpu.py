@@ -41,13 +41,13 @@ def _worker(rank, world, port, out_dir):
     lo, hi = sh.edge_lo, sh.edge_lo + sh.indices.numel()
     r0, r1 = int(sh.dst_bounds[rank]), int(sh.dst_bounds[rank + 1])
     y, x_all = sharding.sharded_spmm_forward(sh, w[lo:hi].to(dev), x[int(xb[rank]):int(xb[rank + 1])].to(dev))
-    dw, dx = sharding.sharded_spmm_backward(sh, w[lo:hi].to(dev), dy[r0:r1].to(dev), x_all, w.to(dev))
+    dw, dx = sharding.sharded_spmm_backward(sh, w[lo:hi].to(dev), dy[r0:r1].to(dev), x_all)
     # the same step fetching only the rows the shard references
     ex = sharding.plan_shard_exchange(sh)
     y2, x_rows = sharding.sharded_spmm_forward(sh, w[lo:hi].to(dev), x[int(xb[rank]):int(xb[rank + 1])].to(dev),
                                                exchange=ex)
     assert th.equal(x_rows.cpu(), x[ex.x.needed.cpu()])
-    dw2, dx2 = sharding.sharded_spmm_backward(sh, w[lo:hi].to(dev), dy[r0:r1].to(dev), x_rows, w.to(dev), exchange=ex)
+    dw2, dx2 = sharding.sharded_spmm_backward(sh, w[lo:hi].to(dev), dy[r0:r1].to(dev), x_rows, exchange=ex)
     assert th.equal(y2, y) and th.equal(dw2, dw) and th.equal(dx2, dx)   # same rows, same order of summation
     th.save({"y": y.cpu(), "dw": dw.cpu(), "dx": dx.cpu(), "rows": (r0, r1), "edges": (lo, hi),
              "cols": (int(sh.src_bounds[rank]), int(sh.src_bounds[rank + 1]))}, os.path.join(out_dir, "r%d.pt" % rank))
