@@ -36,7 +36,35 @@ SIGNATURES = {
                           + [_INT] * 2 + _TAIL,
 }
 
+class Plan(ctypes.Structure):
+    """graphop_plan_t of include/graphop_b200.h."""
+    _fields_ = [("n_chunks", ctypes.c_int64), ("n_edges", ctypes.c_int64), ("n_nodes", ctypes.c_int64),
+                ("header", ctypes.c_void_p), ("erow", ctypes.c_void_p), ("other", ctypes.c_void_p),
+                ("eid", ctypes.c_void_p), ("node_lo", ctypes.c_void_p), ("node_deg", ctypes.c_void_p),
+                ("flags", ctypes.c_int32), ("band_span", ctypes.c_int32)]
+
+
+PLAN_DENSE_BAND = 1
+_PP = ctypes.POINTER(Plan)
+
+# argument lists of the plan forms (one per element type), in the order of include/graphop_b200.h
+PLANNED_SIGNATURES = {
+    "maskedmm_csr_forward_planned": [_PP] + [_P] * 3 + [_I64] * 2 + [_INT] * 2 + _TAIL,
+    "maskedmm_csr_backward_planned": [_PP] * 2 + [_P] * 5 + [_I64] * 2 + [_INT] * 2 + _TAIL,
+    "node_mul_edge_forward_planned": [_PP] + [_P] * 3 + [_I64] + [_INT] * 2 + _TAIL,
+    "node_mul_edge_backward_planned": [_PP] + [_P] * 5 + [_I64] + [_INT] * 2 + _TAIL,
+    "sparse_softmax_forward_planned": [_PP] + [_P] * 2 + [_INT] + _TAIL,
+    "sparse_softmax_backward_planned": [_PP] + [_P] * 3 + [_INT] + _TAIL,
+    "vector_spmm_forward_planned": [_PP] + [_P] * 3 + [_I64] * 2 + [_INT] * 2 + _TAIL,
+    "vector_spmm_backward_planned": [_PP] * 2 + [_P] * 5 + [_I64] * 2 + [_INT] * 2 + _TAIL,
+    "attention_forward_planned": [_PP] + [_P] * 3 + [_DBL] + [_P] * 2 + [_I64] * 2 + [_INT] * 2 + _TAIL,
+    "attention_backward_planned": [_PP] * 2 + [_P] * 6 + [_DBL] + [_P] * 3 + [_I64] * 2 + [_INT] * 2 + _TAIL,
+}
+
 UNTYPED = {
+    "graphop_plan_bytes": ([_I64, _I64, _I64, _INT], _SZ),
+    "graphop_plan_build_i32": ([_P] * 4 + [_I64] * 3 + [_P, _SZ, _PP, _P], _INT),
+    "graphop_plan_build_i64": ([_P] * 4 + [_I64] * 3 + [_P, _SZ, _PP, _P], _INT),
     "graphop_version": ([], _INT),
     "graphop_error_string": ([_INT], ctypes.c_char_p),
     "graphop_last_cuda_error": ([], _INT),
@@ -56,6 +84,9 @@ def exported_symbols():
         for e in ELEM_SUFFIXES:
             for i in INDEX_SUFFIXES:
                 names.append("graphop_%s_%s_%s" % (op, e, i))
+    for op in PLANNED_SIGNATURES:
+        for e in ELEM_SUFFIXES:
+            names.append("graphop_%s_%s" % (op, e))
     return names
 
 
@@ -76,6 +107,12 @@ def bind(handle, strict=True):
                 fn = getattr(handle, name, None) if not strict else getattr(handle, name)
                 if fn is not None:
                     fn.argtypes, fn.restype = args, _INT
+    for op, args in PLANNED_SIGNATURES.items():
+        for e in ELEM_SUFFIXES:
+            name = "graphop_%s_%s" % (op, e)
+            fn = getattr(handle, name, None) if not strict else getattr(handle, name)
+            if fn is not None:
+                fn.argtypes, fn.restype = args, _INT
     return handle
 
 

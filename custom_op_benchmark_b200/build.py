@@ -21,8 +21,10 @@ UNITS = ["graphop_capi_f32.cu", "graphop_capi_f64.cu", "graphop_capi_bf16.cu", "
 BENCH_UNITS = ["graphop_capi_f32.cu", "graphop_capi_attn_f32.cu", "graphop_capi_attn_bf16.cu", "graphop_capi_misc.cu",
                os.path.join("bench", "graphop_bench.cu")]
 BENCH_FLAG = "-DGK_BENCH_HOOKS"
+# -fno-gnu-unique: the twin library holds the same templates as the product library; without it the dynamic linker
+# merges their function-local statics (the "shared memory limit already raised" flags) across the two libraries
 NVCC_FLAGS = ["-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
-              "-Xcompiler", "-fPIC"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-gnu-unique"]
 
 
 def _sources():

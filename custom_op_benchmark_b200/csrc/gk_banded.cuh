@@ -1,0 +1,366 @@
+// Fused attention forward for dense-band graphs on the sm_100a tensor cores.
+//
+// The reference expresses batched dense attention as a graph (512 fully connected blocks, wrapper.py:79-112) and
+// runs it through the same one-thread-per-edge kernels as any other graph (graphop_kernel.cu:40-55, 170-202,
+// 118-130).  When a plan says that every node's neighbours are one run of consecutive ids (GRAPHOP_PLAN_DENSE_BAND:
+// sliding-window attention, block-diagonal attention), the edge list carries no information beyond a (first, count)
+// pair per node, and the chain
+//     scores = Q K^T on the band,  P = softmax(scale * scores),  O = P V
+// is two small dense matrix products per tile of 128 query nodes and head:
+//   * TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) brings the tile's 128 q rows and the up to 384 k and v
+//     rows its band reaches into shared memory;
+//   * tcgen05.mma (kind::f16, bf16 in, fp32 out) forms the 128 x 384 scores in tensor memory;
+//   * each of the 128 threads owns one query row: it reads the row from tensor memory (tcgen05.ld), masks the columns
+//     outside its node's range, takes max and sum, and writes the probabilities as bf16 into shared memory;
+//   * a second tcgen05.mma chain multiplies them with V; the thread scales its output row by 1 / sum and stores it.
+// Everything a tile needs lives on chip: 208 KB of shared memory and 448 of the 512 tensor-memory columns.
+// Every wait on an mbarrier is bounded; a tile whose wait runs out writes NaN to its rows of O instead of hanging.
+#pragma once
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <limits.h>
+
+#include "gk_host.cuh"
+
+namespace gk {
+namespace banded {
+
+constexpr int kTileM = 128;                 // query nodes per block = threads per block = tensor-memory lanes
+constexpr int kD = 64;                      // features per head: one 128-byte swizzle row of bf16
+constexpr int kSpan = GRAPHOP_BAND_MAX_SPAN;  // key rows a tile reaches at most
+constexpr int kKeyBlock = 128;              // key rows per TMA box and per score MMA
+constexpr int kRowBytes = kD * 2;           // 128
+constexpr int kBlockBytes = kKeyBlock * kRowBytes;          // 16 KB: 128 rows of 128 bytes
+constexpr int kPanelKeys = 64;              // keys per probability panel (one swizzle row)
+constexpr int kPanels = kSpan / kPanelKeys;
+constexpr int kOffQ = 0;
+constexpr int kOffK = kOffQ + kBlockBytes;
+constexpr int kOffV = kOffK + (kSpan / kKeyBlock) * kBlockBytes;
+constexpr int kOffP = kOffV + (kSpan / kKeyBlock) * kBlockBytes;
+constexpr int kOffBar = kOffP + kPanels * kBlockBytes;
+constexpr int kSmemBytes = kOffBar + 64 + 1024;             // barriers, tensor-memory address, alignment slack
+constexpr int kTmemCols = 512;
+constexpr int kColO = kSpan;                // scores in columns [0, 384), the output in [384, 448)
+constexpr unsigned kWaitLimit = 400000u;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// bounded: false when the phase did not complete within kWaitLimit polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned it = 0; it < kWaitLimit; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets in 16-byte units,
+// descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor of kind::f16: fp32 accumulator, bf16 A and B, A K-major, B K-major or MN-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Params {
+  __nv_bfloat16* o;          // (n_dst, H, 64)
+  float* lse;                // (n_dst, H)
+  const int32_t* node_lo;    // first neighbour of every destination node
+  const int32_t* node_deg;   // neighbours of every destination node
+  long long n_dst;
+  int H;
+  float scale;
+};
+
+__global__ void __launch_bounds__(kTileM, 1)
+attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+  extern __shared__ unsigned char raw_smem[];
+  // the swizzled tiles want a 1024-byte aligned base
+  unsigned char* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_load = s_base + kOffBar, bar_s = bar_load + 8, bar_o = bar_load + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 32);
+  int* s_red = reinterpret_cast<int*>(smem + kOffBar + 40);   // 4 ints: per-warp minima of the first neighbour
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.y;
+  const long long r0 = (long long)blockIdx.x * kTileM;
+  const long long r = r0 + tid;
+
+  // this thread's node: first neighbour and count
+  int lo = INT_MAX, deg = 0;
+  if (r < p.n_dst) {
+    deg = p.node_deg[r];
+    if (deg > 0) lo = p.node_lo[r];
+  }
+  int wmin = lo;
+#pragma unroll
+  for (int o = 16; o; o >>= 1) wmin = min(wmin, __shfl_xor_sync(kFull, wmin, o));
+  if (lane == 0) s_red[warp] = wmin;
+  if (tid == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  const int kmin = min(min(s_red[0], s_red[1]), min(s_red[2], s_red[3]));
+  bool ok = true;
+
+  if (kmin != INT_MAX) {  // some node of the tile has neighbours
+    if (tid == 0) {
+      mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * (1 + 2 * (kSpan / kKeyBlock))));
+      tma_load_3d(s_base + kOffQ, &map_q, bar_load, 0, head, (int)r0);
+#pragma unroll
+      for (int b = 0; b < kSpan / kKeyBlock; ++b) {
+        tma_load_3d(s_base + kOffK + b * kBlockBytes, &map_k, bar_load, 0, head, kmin + b * kKeyBlock);
+        tma_load_3d(s_base + kOffV + b * kBlockBytes, &map_v, bar_load, 0, head, kmin + b * kKeyBlock);
+      }
+    }
+    ok = __syncthreads_and(mbar_wait(bar_load, 0));   // the same verdict in every thread
+    if (ok && tid == 0) {
+      // scores: for each block of 128 keys, 4 steps of 16 features
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      constexpr uint32_t idesc = umma_idesc(kTileM, kKeyBlock, false);
+#pragma unroll
+      for (int b = 0; b < kSpan / kKeyBlock; ++b) {
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint64_t a = umma_desc(s_base + kOffQ + kk * 32, 16, 1024);
+          const uint64_t bd = umma_desc(s_base + kOffK + b * kBlockBytes + kk * 32, 16, 1024);
+          umma_f16(tmem + b * kKeyBlock, a, bd, idesc, kk > 0);
+        }
+      }
+      umma_commit(bar_s);
+    }
+    ok = __syncthreads_and(ok && mbar_wait(bar_s, 0));
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // this thread's row: columns [jlo, jhi] are its node's neighbours
+    const int jlo = deg > 0 ? lo - kmin : 1, jhi = deg > 0 ? lo - kmin + deg - 1 : 0;
+    int wlo = deg > 0 ? jlo : INT_MAX, whi = deg > 0 ? jhi : -1;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      wlo = min(wlo, __shfl_xor_sync(kFull, wlo, o));
+      whi = max(whi, __shfl_xor_sync(kFull, whi, o));
+    }
+    const int c_first = wlo == INT_MAX ? 0 : wlo / 32, c_last = whi < 0 ? -1 : whi / 32;   // warp-uniform chunk range
+    const uint32_t row_taddr = tmem + ((uint32_t)(warp * 32) << 16);
+    const float sl2 = p.scale * 1.4426950408889634f;
+    float m = -INFINITY;
+    if (ok) {
+      for (int c = c_first; c <= c_last; ++c) {
+        float v[32];
+        tmem_ld32(row_taddr + c * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = c * 32 + j;
+          if (col >= jlo && col <= jhi) m = fmaxf(m, v[j]);
+        }
+      }
+    }
+    const float msl2 = deg > 0 ? m * sl2 : 0.f;
+    float l = 0.f;
+    unsigned char* prow = smem + kOffP + tid * kRowBytes;   // this row inside each 64-key panel
+    for (int c = 0; c < kSpan / 32; ++c) {
+      float v[32];
+      const bool live = ok && c >= c_first && c <= c_last;
+      if (live) tmem_ld32(row_taddr + c * 32, v);
+      uint32_t packed[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float p0 = 0.f, p1 = 0.f;
+        if (live) {
+          const int col = c * 32 + j;
+          if (col >= jlo && col <= jhi) p0 = exp2f(fmaf(v[j], sl2, -msl2));
+          if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2f(fmaf(v[j + 1], sl2, -msl2));
+        }
+        l += p0 + p1;
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+        packed[j / 2] = *reinterpret_cast<uint32_t*>(&h2);
+      }
+      // 32 keys = 4 chunks of 16 bytes in panel c / 2, at chunk index (c & 1) * 4 + q, swizzled by the row
+      unsigned char* panel = prow + (c >> 1) * kBlockBytes;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int chunk = ((c & 1) * 4 + q) ^ (tid & 7);
+        *reinterpret_cast<uint4*>(panel + chunk * 16) =
+            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      }
+    }
+    // the probabilities were written through the generic proxy; the tensor core reads through the async proxy
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && tid == 0) {
+      constexpr uint32_t idesc = umma_idesc(kTileM, kD, true);
+#pragma unroll
+      for (int ks = 0; ks < kSpan / 16; ++ks) {
+        const uint64_t a = umma_desc(s_base + kOffP + (ks >> 2) * kBlockBytes + (ks & 3) * 32, 16, 1024);
+        const uint64_t bd = umma_desc(s_base + kOffV + ks * 16 * kRowBytes, 16, 1024);
+        umma_f16(tmem + kColO, a, bd, idesc, ks > 0);
+      }
+      umma_commit(bar_o);
+    }
+    ok = __syncthreads_and(ok && mbar_wait(bar_o, 0));
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    __nv_bfloat16* orow = p.o + ((long long)r * p.H + head) * kD;
+    const float inv = deg > 0 ? 1.f / l : 0.f;
+#pragma unroll
+    for (int c = 0; c < kD / 32; ++c) {
+      float v[32];
+      if (ok) {  // every lane of the warp reads, whether or not its row exists: the load is warp-wide
+        tmem_ld32(row_taddr + kColO + c * 32, v);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = NAN;
+      }
+      if (r < p.n_dst) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float a0 = ok ? (deg > 0 ? v[8 * q + 2 * e] * inv : 0.f) : NAN;
+            const float a1 = ok ? (deg > 0 ? v[8 * q + 2 * e + 1] * inv : 0.f) : NAN;
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(a0, a1);
+            w[e] = *reinterpret_cast<uint32_t*>(&h2);
+          }
+          *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    if (r < p.n_dst) p.lse[(long long)r * p.H + head] = !ok ? NAN : (deg > 0 ? m * p.scale + logf(l) : -INFINITY);
+  } else if (r < p.n_dst) {  // no node of the tile has a neighbour
+    __nv_bfloat16* orow = p.o + ((long long)r * p.H + head) * kD;
+#pragma unroll
+    for (int q = 0; q < kD / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
+    p.lse[(long long)r * p.H + head] = -INFINITY;
+  }
+
+  // every thread is done with tensor memory: hand it back
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// cuTensorMapEncodeTiled, fetched from the driver at run time (no link dependency on libcuda)
+inline PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return (PFN_cuTensorMapEncodeTiled_v12000)ptr;
+  }();
+  return fn;
+}
+
+// (n, H, 64) bf16 node tensor as a 3-D map (feature, head, node), boxes of 128 nodes of one head, 128-byte swizzle
+inline bool make_map(CUtensorMap* map, const void* base, long long n, int H) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)H, (cuuint64_t)n};
+  const cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, (cuuint64_t)H * kRowBytes};
+  const cuuint32_t box[3] = {(cuuint32_t)kD, 1u, (cuuint32_t)kKeyBlock};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace banded
+
+template <>
+inline int banded_attention_forward<__nv_bfloat16>(const graphop_plan_t* plan, const __nv_bfloat16* q,
+                                                   const __nv_bfloat16* k, const __nv_bfloat16* v, double scale,
+                                                   __nv_bfloat16* o, void* lse, long long n_dst, long long n_src, int H,
+                                                   int D, cudaStream_t st) {
+  using namespace banded;
+  if (D != kD || H < 1 || H > 65535 || n_dst < 1 || n_src < 1 || n_dst > plan->n_nodes) return GRAPHOP_ERR_UNSUPPORTED;
+  if (!(plan->flags & GRAPHOP_PLAN_DENSE_BAND) || plan->band_span > kSpan || !plan->node_lo || !plan->node_deg)
+    return GRAPHOP_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return GRAPHOP_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  if (!make_map(&mq, q, n_dst, H) || !make_map(&mk, k, n_src, H) || !make_map(&mv, v, n_src, H))
+    return GRAPHOP_ERR_UNSUPPORTED;
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  GK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+    GK_CUDA(cudaFuncSetAttribute(attention_forward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
+  }
+  Params p;
+  p.o = o; p.lse = (float*)lse; p.node_lo = plan->node_lo; p.node_deg = plan->node_deg; p.n_dst = n_dst; p.H = H;
+  p.scale = (float)scale;
+  const dim3 grid((unsigned)((n_dst + kTileM - 1) / kTileM), (unsigned)H);
+  attention_forward_kernel<<<grid, kTileM, kSmemBytes, st>>>(mq, mk, mv, p);
+  GK_LAUNCHED("attention_fwd_banded");
+  return GRAPHOP_OK;
+}
+
+}  // namespace gk

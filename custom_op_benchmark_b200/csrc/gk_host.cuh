@@ -177,6 +177,29 @@ inline int prepare_graph(Arena& ar, const I* row, const I* indptr, const I* eid,
   return GRAPHOP_OK;
 }
 
+// Where an op's GraphView comes from: expanded on the spot from the caller's chunk table (into the workspace), or
+// taken from a plan that graphop_plan_build_* made once for the graph.
+template <typename I>
+struct FromChunks {
+  const I* row; const I* indptr; const I* eid; const I* indices; long long C, E;
+  bool valid(bool need_indices) const { return row && indptr && (!need_indices || indices); }
+  int operator()(Arena& ar, cudaStream_t st, GraphView* g) const {
+    return prepare_graph<I>(ar, row, indptr, eid, indices, C, E, st, g);
+  }
+};
+struct FromPlan {
+  const graphop_plan_t* p;
+  bool valid(bool need_indices) const { return p && p->erow && p->header && (!need_indices || p->other); }
+  int operator()(Arena&, cudaStream_t, GraphView* g) const {
+    g->hdr = (const PlanHeader*)p->header;
+    g->erow = p->erow;
+    g->other = p->other;
+    g->eid = p->eid;
+    g->E = p->n_edges;
+    return GRAPHOP_OK;
+  }
+};
+
 inline int zero_uncovered(const GraphView& g, void* out, size_t bytes, cudaStream_t st) {
   const long long words = (long long)(bytes / 4);
   if (words == 0) return GRAPHOP_OK;
@@ -502,26 +525,24 @@ inline int check_ws(const void* ws) {
 // ---------------------------------------------------------------------------------------
 // the ten operations
 // ---------------------------------------------------------------------------------------
-template <typename T, typename I>
-inline int maskedmm_forward(const I* row, const I* indptr, const I* eid, const I* indices, const T* A_, const T* B_,
-                            T* y, long long C, long long E, long long n_dst, long long n_src, int H, int D, void* ws,
-                            size_t wsb, cudaStream_t st) {
+template <typename T, class GS>
+inline int maskedmm_forward(const GS& gs, const T* A_, const T* B_, T* y, long long C, long long E, long long n_dst,
+                            long long n_src, int H, int D, void* ws, size_t wsb, cudaStream_t st) {
   GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
   if (E == 0) return GRAPHOP_OK;
-  if (!row || !indptr || !indices || !A_ || !B_ || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (!gs.valid(true) || !A_ || !B_ || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, indices, C, E, st, &g));
+  GK_TRY(gs(ar, st, &g));
   GK_TRY(zero_uncovered(g, y, (size_t)E * H * sizeof(T), st));
   return run_edge_dot<T, false>(g, A_, B_, y, H, D, st);
 }
 
-template <typename T, typename I>
-inline int maskedmm_backward(const I* row, const I* indptr_r, const I* eid_r, const I* indices_r, long long Cr,
-                             const I* col, const I* indptr_c, const I* eid_c, const I* indices_c, long long Cc,
-                             const T* A_, const T* B_, const T* dy, T* dA, T* dB, long long E, long long n_dst,
-                             long long n_src, int H, int D, void* ws, size_t wsb, cudaStream_t st) {
+template <typename T, class GS>
+inline int maskedmm_backward(const GS& gs_r, const GS& gs_c, long long Cr, long long Cc, const T* A_, const T* B_,
+                             const T* dy, T* dA, T* dB, long long E, long long n_dst, long long n_src, int H, int D,
+                             void* ws, size_t wsb, cudaStream_t st) {
   GK_TRY(check_sizes(Cr, E, n_dst, n_src, H, D));
   if (Cc < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
   const size_t HD = (size_t)H * D;
@@ -530,106 +551,100 @@ inline int maskedmm_backward(const I* row, const I* indptr_r, const I* eid_r, co
     if (n_src) GK_CUDA(cudaMemsetAsync(dB, 0, (size_t)n_src * HD * sizeof(T), st));
     return GRAPHOP_OK;
   }
-  if (!row || !indptr_r || !indices_r || !col || !indptr_c || !indices_c || !A_ || !B_ || !dy || !dA || !dB)
-    return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (!gs_r.valid(true) || !gs_c.valid(true) || !A_ || !B_ || !dy || !dA || !dB) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
   {
     GraphView g;
-    GK_TRY(prepare_graph<I>(ar, row, indptr_r, eid_r, indices_r, Cr, E, st, &g));
+    GK_TRY(gs_r(ar, st, &g));
     GK_TRY((run_aggregate<T, false>(ar, g, dy, B_, dA, n_dst, H, D, st)));
   }
   ar.used = 0;  // the second pass runs after the first on the same stream: reuse the scratch
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, col, indptr_c, eid_c, indices_c, Cc, E, st, &g));
+  GK_TRY(gs_c(ar, st, &g));
   return run_aggregate<T, false>(ar, g, dy, A_, dB, n_src, H, D, st);
 }
 
-template <typename T, typename I>
-inline int node_mul_edge_forward(const I* row, const I* indptr, const I* eid, const T* A_, const T* B_, T* y,
-                                 long long C, long long E, long long n_dst, int H, int D, void* ws, size_t wsb,
-                                 cudaStream_t st) {
+template <typename T, class GS>
+inline int node_mul_edge_forward(const GS& gs, const T* A_, const T* B_, T* y, long long C, long long E,
+                                 long long n_dst, int H, int D, void* ws, size_t wsb, cudaStream_t st) {
   GK_TRY(check_sizes(C, E, n_dst, 0, H, D));
   if (E == 0) return GRAPHOP_OK;
-  if (!row || !indptr || !A_ || !B_ || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (!gs.valid(false) || !A_ || !B_ || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, (const I*)nullptr, C, E, st, &g));
+  GK_TRY(gs(ar, st, &g));
   GK_TRY(zero_uncovered(g, y, (size_t)E * H * sizeof(T), st));
   return run_edge_dot<T, true>(g, A_, B_, y, H, D, st);
 }
 
-template <typename T, typename I>
-inline int node_mul_edge_backward(const I* row, const I* indptr, const I* eid, const T* A_, const T* B_, const T* dy,
-                                  T* dA, T* dB, long long C, long long E, long long n_dst, int H, int D, void* ws,
-                                  size_t wsb, cudaStream_t st) {
+template <typename T, class GS>
+inline int node_mul_edge_backward(const GS& gs, const T* A_, const T* B_, const T* dy, T* dA, T* dB, long long C,
+                                  long long E, long long n_dst, int H, int D, void* ws, size_t wsb, cudaStream_t st) {
   GK_TRY(check_sizes(C, E, n_dst, 0, H, D));
   if (E == 0) {
     if (n_dst) GK_CUDA(cudaMemsetAsync(dA, 0, (size_t)n_dst * H * D * sizeof(T), st));
     return GRAPHOP_OK;
   }
-  if (!row || !indptr || !A_ || !B_ || !dy || !dA || !dB) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (!gs.valid(false) || !A_ || !B_ || !dy || !dA || !dB) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, (const I*)nullptr, C, E, st, &g));
+  GK_TRY(gs(ar, st, &g));
   GK_TRY((run_aggregate<T, true>(ar, g, dy, B_, dA, n_dst, H, D, st)));
   if (!ar.base) return GRAPHOP_OK;
   GK_TRY(zero_uncovered(g, dB, (size_t)E * D * sizeof(T), st));
   return run_edge_mix<T>(g, dy, A_, dB, H, D, st);
 }
 
-template <typename T, typename I, bool kBackward>
-inline int sparse_softmax(const I* row, const I* indptr, const I* eid, const T* in0, const T* in1, T* out,
-                          long long C, long long E, long long n_nodes, int H, void* ws, size_t wsb, cudaStream_t st) {
+template <typename T, bool kBackward, class GS>
+inline int sparse_softmax(const GS& gs, const T* in0, const T* in1, T* out, long long C, long long E,
+                          long long n_nodes, int H, void* ws, size_t wsb, cudaStream_t st) {
   GK_TRY(check_sizes(C, E, n_nodes, 0, H, 1));
   if (E == 0) return GRAPHOP_OK;
-  if (!row || !indptr || !in0 || !out || (kBackward && !in1)) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (!gs.valid(false) || !in0 || !out || (kBackward && !in1)) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, (const I*)nullptr, C, E, st, &g));
+  GK_TRY(gs(ar, st, &g));
   GK_TRY(zero_uncovered(g, out, (size_t)E * H * sizeof(T), st));
   return run_softmax<T, kBackward>(ar, g, in0, in1, out, n_nodes, H, st);
 }
 
-template <typename T, typename I>
-inline int spmm_forward(const I* row, const I* indptr, const I* eid, const I* indices, const T* edata, const T* x,
-                        T* y, long long C, long long E, long long n_dst, long long n_src, int H, int D, void* ws,
-                        size_t wsb, cudaStream_t st) {
+template <typename T, class GS>
+inline int spmm_forward(const GS& gs, const T* edata, const T* x, T* y, long long C, long long E, long long n_dst,
+                        long long n_src, int H, int D, void* ws, size_t wsb, cudaStream_t st) {
   GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
   if (n_dst == 0) return GRAPHOP_OK;
   if (E == 0) {
     GK_CUDA(cudaMemsetAsync(y, 0, (size_t)n_dst * H * D * sizeof(T), st));
     return GRAPHOP_OK;
   }
-  if (!row || !indptr || !indices || !edata || !x || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (!gs.valid(true) || !edata || !x || !y) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, row, indptr, eid, indices, C, E, st, &g));
+  GK_TRY(gs(ar, st, &g));
   return run_aggregate<T, false>(ar, g, edata, x, y, n_dst, H, D, st);
 }
 
-template <typename T, typename I>
-inline int spmm_backward(const I* row, const I* indptr, const I* eid, const I* indices, long long C, const I* col,
-                         const I* indptr_t, const I* eid_t, const I* indices_t, long long Ct, const T* edata,
-                         const T* dy, const T* x, T* dedata, T* dx, long long E, long long n_dst, long long n_src,
-                         int H, int D, void* ws, size_t wsb, cudaStream_t st) {
+template <typename T, class GS>
+inline int spmm_backward(const GS& gs_r, const GS& gs_c, long long C, long long Ct, const T* edata, const T* dy,
+                         const T* x, T* dedata, T* dx, long long E, long long n_dst, long long n_src, int H, int D,
+                         void* ws, size_t wsb, cudaStream_t st) {
   GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
   if (Ct < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
   if (E == 0) {
     if (n_src) GK_CUDA(cudaMemsetAsync(dx, 0, (size_t)n_src * H * D * sizeof(T), st));
     return GRAPHOP_OK;
   }
-  if (!row || !indptr || !indices || !col || !indptr_t || !indices_t || !edata || !dy || !x || !dedata || !dx)
-    return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (!gs_r.valid(true) || !gs_c.valid(true) || !edata || !dy || !x || !dedata || !dx) return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
   {
     GraphView g;
-    GK_TRY(prepare_graph<I>(ar, row, indptr, eid, indices, C, E, st, &g));
+    GK_TRY(gs_r(ar, st, &g));
     if (ar.base) {
       GK_TRY(zero_uncovered(g, dedata, (size_t)E * H * sizeof(T), st));
       GK_TRY((run_edge_dot<T, false>(g, dy, x, dedata, H, D, st)));
@@ -637,7 +652,7 @@ inline int spmm_backward(const I* row, const I* indptr, const I* eid, const I* i
   }
   ar.used = 0;
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, col, indptr_t, eid_t, indices_t, Ct, E, st, &g));
+  GK_TRY(gs_c(ar, st, &g));
   return run_aggregate<T, false>(ar, g, edata, dy, dx, n_src, H, D, st);
 }
 
@@ -656,10 +671,10 @@ inline bool attention_shape_ok(int H, int D, bool al, VecShape* s) {
   return s->V == VecMax<T>::value && s->R != 0 && is_pow2(D / s->V);
 }
 
-template <typename T, typename I>
-inline int attention_forward(const I* row, const I* indptr, const I* indices, long long C, const T* q, const T* k,
-                             const T* v, double scale, T* o, void* lse, long long E, long long n_dst, long long n_src,
-                             int H, int D, void* ws, size_t wsb, cudaStream_t st) {
+template <typename T, class GS>
+inline int attention_forward(const GS& gs, long long C, const T* q, const T* k, const T* v, double scale, T* o,
+                             void* lse, long long E, long long n_dst, long long n_src, int H, int D, void* ws,
+                             size_t wsb, cudaStream_t st) {
   using A = typename AccOf<T>::type;
   GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
   VecShape s;
@@ -680,8 +695,8 @@ inline int attention_forward(const I* row, const I* indptr, const I* indices, lo
     GK_LAUNCHED("fill");
     return GRAPHOP_OK;
   }
-  if (!row || !indptr || !indices) return GRAPHOP_ERR_INVALID_ARGUMENT;
-  GK_TRY(prepare_graph<I>(ar, row, indptr, (const I*)nullptr, indices, C, E, st, &g));
+  if (!gs.valid(true)) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(gs(ar, st, &g));
   const int tile0 = pick_tile(E);
   return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
@@ -700,13 +715,36 @@ inline int attention_forward(const I* row, const I* indptr, const I* indices, lo
   });
 }
 
-template <typename T, typename I>
-inline int attention_backward(const I* row, const I* indptr, const I* indices, long long C, const I* col,
-                              const I* indptr_t, const I* eid_t, const I* indices_t, long long Ct, const T* q,
-                              const T* k, const T* v,
-                              const T* o, const void* lse, const T* dout, double scale, T* dq, T* dk, T* dv,
-                              long long E, long long n_dst, long long n_src, int H, int D, void* ws, size_t wsb,
-                              cudaStream_t st) {
+// Defined in gk_banded.cuh for bfloat16: the tensor-core kernel for dense-band graphs.  Returns
+// GRAPHOP_ERR_UNSUPPORTED when the shape is not one it takes (the caller then runs the walker).
+template <typename T>
+int banded_attention_forward(const graphop_plan_t* plan, const T* q, const T* k, const T* v, double scale, T* o,
+                             void* lse, long long n_dst, long long n_src, int H, int D, cudaStream_t st);
+template <typename T>
+inline int banded_attention_forward(const graphop_plan_t*, const T*, const T*, const T*, double, T*, void*, long long,
+                                    long long, int, int, cudaStream_t) {
+  return GRAPHOP_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+inline int attention_forward_planned(const graphop_plan_t* plan, const T* q, const T* k, const T* v, double scale,
+                                     T* o, void* lse, long long n_dst, long long n_src, int H, int D, void* ws,
+                                     size_t wsb, cudaStream_t st) {
+  if (!plan) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if ((plan->flags & GRAPHOP_PLAN_DENSE_BAND) && q && k && v && o && lse) {
+    const int rc = banded_attention_forward<T>(plan, q, k, v, scale, o, lse, n_dst, n_src, H, D, st);
+    if (rc != GRAPHOP_ERR_UNSUPPORTED) return rc;
+  }
+  return attention_forward<T>(FromPlan{plan}, plan->n_chunks, q, k, v, scale, o, lse, plan->n_edges, n_dst, n_src, H,
+                              D, ws, wsb, st);
+}
+
+// has_eid_t: the transposed source carries edge ids (the positions of its edges in the row CSR)
+template <typename T, class GS>
+inline int attention_backward(const GS& gs_r, const GS& gs_c, bool has_eid_t, long long C, long long Ct, const T* q,
+                              const T* k, const T* v, const T* o, const void* lse, const T* dout, double scale, T* dq,
+                              T* dk, T* dv, long long E, long long n_dst, long long n_src, int H, int D, void* ws,
+                              size_t wsb, cudaStream_t st) {
   using A = typename AccOf<T>::type;
   GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
   if (Ct < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
@@ -722,8 +760,7 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
     if (n_src) GK_CUDA(cudaMemsetAsync(dv, 0, (size_t)n_src * rowb, st));
     return GRAPHOP_OK;
   }
-  if (!row || !indptr || !indices || !col || !indptr_t || !indices_t || !q || !k || !v || !o || !lse || !dout || !dq ||
-      !dk || !dv)
+  if (!gs_r.valid(true) || !gs_c.valid(true) || !q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv)
     return GRAPHOP_ERR_INVALID_ARGUMENT;
   GK_TRY(check_ws(ws));
   Arena ar(ws, wsb);
@@ -732,11 +769,11 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
   const int Hp = stat_heads(H, (int)sizeof(A));
   StatPair<A>* stat = (StatPair<A>*)ar.take((size_t)n_dst * Hp * sizeof(StatPair<A>));  // survives both passes
   // with the transposed CSR's edge ids the destination pass leaves (p, ds) of every edge for the source pass
-  EdgePair<A>* pd = eid_t ? (EdgePair<A>*)ar.take((size_t)E * Hp * sizeof(EdgePair<A>)) : nullptr;
+  EdgePair<A>* pd = has_eid_t ? (EdgePair<A>*)ar.take((size_t)E * Hp * sizeof(EdgePair<A>)) : nullptr;
   const size_t mark = ar.used;
   {
     GraphView g;
-    GK_TRY(prepare_graph<I>(ar, row, indptr, (const I*)nullptr, indices, C, E, st, &g));
+    GK_TRY(gs_r(ar, st, &g));
     GK_TRY((dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
       constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
       if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
@@ -755,7 +792,7 @@ inline int attention_backward(const I* row, const I* indptr, const I* indices, l
   }
   ar.used = mark;
   GraphView g;
-  GK_TRY(prepare_graph<I>(ar, col, indptr_t, eid_t, indices_t, Ct, E, st, &g));
+  GK_TRY(gs_c(ar, st, &g));
   return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
     if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;

@@ -2,3 +2,4 @@
 #include "graphop_capi_impl.cuh"
 GRAPHOP_DEFINE_OPS(f64_i32, double, double, int32_t)
 GRAPHOP_DEFINE_OPS(f64_i64, double, double, int64_t)
+GRAPHOP_DEFINE_PLANNED_OPS(f64, double, double)

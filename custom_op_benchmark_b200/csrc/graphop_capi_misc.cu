@@ -1,6 +1,7 @@
 // C ABI entry points that do not depend on the element type: version, error text, the
 // workspace size query and the graph-contract checker.
 #include "gk_host.cuh"
+#include "gk_plan.cuh"
 
 namespace gk {
 namespace {
@@ -187,4 +188,23 @@ extern "C" int graphop_check_graph_i64(const int64_t* row, const int64_t* indptr
                                        int64_t n_other, int* violations, graphop_stream_t stream) {
   return gk::check_graph<int64_t>(row, indptr, eid, indices, n_chunks, n_edges, n_nodes, n_other, violations,
                                   (cudaStream_t)stream);
+}
+
+extern "C" size_t graphop_plan_bytes(int64_t n_chunks, int64_t n_edges, int64_t n_nodes, int index_bytes) {
+  if (n_chunks < 0 || n_edges < 0 || n_nodes < 0) return 0;
+  return gk::plan_bytes(n_chunks, n_edges, n_nodes, index_bytes);
+}
+extern "C" int graphop_plan_build_i32(const int32_t* row, const int32_t* indptr, const int32_t* eid,
+                                      const int32_t* indices, int64_t n_chunks, int64_t n_edges, int64_t n_nodes,
+                                      void* memory, size_t memory_bytes, graphop_plan_t* plan,
+                                      graphop_stream_t stream) {
+  return gk::plan_build<int32_t>(row, indptr, eid, indices, n_chunks, n_edges, n_nodes, memory, memory_bytes, plan,
+                                 (cudaStream_t)stream);
+}
+extern "C" int graphop_plan_build_i64(const int64_t* row, const int64_t* indptr, const int64_t* eid,
+                                      const int64_t* indices, int64_t n_chunks, int64_t n_edges, int64_t n_nodes,
+                                      void* memory, size_t memory_bytes, graphop_plan_t* plan,
+                                      graphop_stream_t stream) {
+  return gk::plan_build<int64_t>(row, indptr, eid, indices, n_chunks, n_edges, n_nodes, memory, memory_bytes, plan,
+                                 (cudaStream_t)stream);
 }

@@ -23,6 +23,10 @@ __all__ = [
     "maskedmm_csr_forward", "maskedmm_csr_backward", "node_mul_edge_forward", "node_mul_edge_backward",
     "sparse_softmax_forward", "sparse_softmax_backward", "vector_spmm_forward", "vector_spmm_backward",
     "attention_forward", "attention_backward", "attention_supported", "check_graph", "gather_rows",
+    "GraphPlan", "maskedmm_csr_forward_planned", "maskedmm_csr_backward_planned", "vector_spmm_forward_planned",
+    "vector_spmm_backward_planned", "sparse_softmax_forward_planned", "sparse_softmax_backward_planned",
+    "node_mul_edge_forward_planned", "node_mul_edge_backward_planned", "attention_forward_planned",
+    "attention_backward_planned",
 ]
 
 _ELEM = {th.float32: ("f32", 4), th.float64: ("f64", 8), th.bfloat16: ("bf16", 2)}
@@ -352,3 +356,191 @@ def check_graph(row, indptr, eid, indices, n_nodes, n_other):
     if rc not in (_capi.OK, _capi.ERR_INVALID_ARGUMENT):
         raise RuntimeError("graphop_check_graph: %s" % _capi.error_message(rc))
     return flags.value
+
+
+# ------------------------------------------------------------------------------------------
+# graph plans (an addition): what the ops rebuild from the index tensors on every call, built once
+# ------------------------------------------------------------------------------------------
+class GraphPlan:
+    """One CSR orientation prepared once: the owner node of every position, 32-bit copies of int64 index tensors,
+    per-node ranges and the shape flags (``dense_band``).  The reference prepares its graphs on the host in Python
+    loops before any op runs (part_csr.py:18-21, wrapper.py:93-112); this is that step for the kernels here, on
+    the device.  Building a plan waits for the device once; the ``*_planned`` ops then take the plan in place
+    of ``(row, indptr, eid, indices)`` and skip the per-call expansion.
+
+    ``indices`` may be None for ops without a second endpoint (sparse_softmax, node_mul_edge), ``eid`` None for
+    the identity.  The plan keeps the index tensors it refers to alive."""
+
+    def __init__(self, row, indptr, eid, indices, n_nodes):
+        import ctypes
+        given = dict(row=row, indptr=indptr)
+        if eid is not None:
+            given["eid"] = eid
+        if indices is not None:
+            given["indices"] = indices
+        _check_all(**given)
+        index = _index(*given.values())
+        self.n_chunks, self.n_nodes = _chunks(row, indptr), int(n_nodes)
+        self.n_edges = int(indices.size(0) if indices is not None else (eid.size(0) if eid is not None else 0))
+        if eid is not None and indices is not None and eid.size(0) != indices.size(0):
+            raise RuntimeError("eid and indices disagree on the number of edges")
+        self.device = row.device
+        lib = _capi.lib()
+        need = lib.graphop_plan_bytes(self.n_chunks, self.n_edges, self.n_nodes, index[1])
+        self._memory = th.empty(need + 256, dtype=th.uint8, device=self.device)
+        base = (self._memory.data_ptr() + 255) // 256 * 256
+        self._keep = (row, indptr, eid, indices)
+        self.c = _capi.Plan()
+        fn = getattr(lib, "graphop_plan_build_%s" % index[0])
+        with th.cuda.device(self.device):
+            rc = fn(_p(row), _p(indptr), _p(eid), _p(indices), self.n_chunks, self.n_edges, self.n_nodes, base, need,
+                    ctypes.byref(self.c), th.cuda.current_stream(self.device).cuda_stream)
+        if rc != _capi.OK:
+            raise RuntimeError("graphop_plan_build: %s" % _capi.error_message(rc))
+
+    @property
+    def dense_band(self):
+        return bool(self.c.flags & _capi.PLAN_DENSE_BAND)
+
+    @property
+    def band_span(self):
+        return int(self.c.band_span)
+
+    def ref(self):
+        import ctypes
+        return ctypes.byref(self.c)
+
+
+def _call_planned(name, elem, op_id, plans, n_nodes, h, d, device, args):
+    lib = _capi.lib()
+    need = lib.graphop_workspace_bytes(op_id, plans[0].n_edges, n_nodes, h, d, elem[1], 4)
+    ws = th.empty(need + 256, dtype=th.uint8, device=device)
+    aligned = (ws.data_ptr() + 255) // 256 * 256
+    fn = getattr(lib, "graphop_%s_planned_%s" % (name, elem[0]))
+    rc = fn(*[p.ref() for p in plans], *args, aligned, need, th.cuda.current_stream(device).cuda_stream)
+    if rc != _capi.OK:
+        raise RuntimeError("graphop_%s_planned: %s" % (name, _capi.error_message(rc)))
+
+
+def maskedmm_csr_forward_planned(plan, A, B):
+    _check_all(A=A, B=B)
+    elem = _elem(A, B)
+    h, d = _heads(A, True)
+    y = th.empty((plan.n_edges,) if h == 1 else (plan.n_edges, h), dtype=A.dtype, device=A.device)
+    with th.cuda.device(A.device):
+        _call_planned("maskedmm_csr_forward", elem, _capi.OP_MASKEDMM_FWD, [plan], max(A.size(0), B.size(0)), h, d,
+                      A.device, [_p(A), _p(B), _p(y), A.size(0), B.size(0), h, d])
+    return y
+
+
+def maskedmm_csr_backward_planned(plan_r, plan_c, A, B, dy):
+    dy = dy.contiguous()
+    _check_all(A=A, B=B, dy=dy)
+    elem = _elem(A, B, dy)
+    h, d = _heads(A, True)
+    dA, dB = th.empty_like(A), th.empty_like(B)
+    with th.cuda.device(A.device):
+        _call_planned("maskedmm_csr_backward", elem, _capi.OP_MASKEDMM_BWD, [plan_r, plan_c],
+                      max(A.size(0), B.size(0)), h, d, A.device,
+                      [_p(A), _p(B), _p(dy), _p(dA), _p(dB), A.size(0), B.size(0), h, d])
+    return [dA, dB]
+
+
+def node_mul_edge_forward_planned(plan, A, B):
+    _check_all(A=A, B=B)
+    elem = _elem(A, B)
+    h, d = _heads(A, True)
+    y = th.empty((plan.n_edges,) if h == 1 else (plan.n_edges, h), dtype=A.dtype, device=A.device)
+    with th.cuda.device(A.device):
+        _call_planned("node_mul_edge_forward", elem, _capi.OP_NODE_MUL_EDGE_FWD, [plan], A.size(0), h, d, A.device,
+                      [_p(A), _p(B), _p(y), A.size(0), h, d])
+    return y
+
+
+def node_mul_edge_backward_planned(plan, A, B, dy):
+    dy = dy.contiguous()
+    _check_all(A=A, B=B, dy=dy)
+    elem = _elem(A, B, dy)
+    h, d = _heads(A, True)
+    dA, dB = th.empty_like(A), th.empty_like(B)
+    with th.cuda.device(A.device):
+        _call_planned("node_mul_edge_backward", elem, _capi.OP_NODE_MUL_EDGE_BWD, [plan], A.size(0), h, d, A.device,
+                      [_p(A), _p(B), _p(dy), _p(dA), _p(dB), A.size(0), h, d])
+    return [dA, dB]
+
+
+def sparse_softmax_forward_planned(plan, x):
+    _check_all(x=x)
+    elem, h = _elem(x), _heads(x, False)
+    y = th.empty_like(x)
+    with th.cuda.device(x.device):
+        _call_planned("sparse_softmax_forward", elem, _capi.OP_SOFTMAX_FWD, [plan], plan.n_nodes, h, 1, x.device,
+                      [_p(x), _p(y), h])
+    return y
+
+
+def sparse_softmax_backward_planned(plan, y, dy):
+    _check_all(y=y, dy=dy)
+    elem, h = _elem(y, dy), _heads(dy, False)
+    dx = th.empty_like(dy)
+    with th.cuda.device(y.device):
+        _call_planned("sparse_softmax_backward", elem, _capi.OP_SOFTMAX_BWD, [plan], plan.n_nodes, h, 1, y.device,
+                      [_p(y), _p(dy), _p(dx), h])
+    return dx
+
+
+def vector_spmm_forward_planned(plan, edata, x, num_dst=None):
+    _check_all(edata=edata, x=x)
+    elem = _elem(edata, x)
+    h, d = _heads(x, True)
+    n_dst = x.size(0) if num_dst is None else int(num_dst)
+    y = th.empty((n_dst,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    with th.cuda.device(x.device):
+        _call_planned("vector_spmm_forward", elem, _capi.OP_SPMM_FWD, [plan], max(n_dst, x.size(0)), h, d, x.device,
+                      [_p(edata), _p(x), _p(y), n_dst, x.size(0), h, d])
+    return y
+
+
+def vector_spmm_backward_planned(plan_r, plan_t, edata, dy, x):
+    _check_all(edata=edata, dy=dy, x=x)
+    elem = _elem(edata, dy, x)
+    h, d = _heads(x, True)
+    dedata, dx = th.empty_like(edata), th.empty_like(x)
+    with th.cuda.device(x.device):
+        _call_planned("vector_spmm_backward", elem, _capi.OP_SPMM_BWD, [plan_r, plan_t], max(dy.size(0), x.size(0)),
+                      h, d, x.device, [_p(edata), _p(dy), _p(x), _p(dedata), _p(dx), dy.size(0), x.size(0), h, d])
+    return [dedata, dx]
+
+
+def attention_forward_planned(plan, q, k, v, scale):
+    """attention_forward on a plan of the row CSR; a dense-band graph with bfloat16 tensors of 64 features per
+    head runs on the tensor cores."""
+    _check_all(q=q, k=k, v=v)
+    elem = _elem(q, k, v)
+    h, d = _heads(q, True)
+    o = th.empty_like(q)
+    lse = th.empty((q.size(0), h), dtype=_lse_dtype(q), device=q.device)
+    if plan.n_edges == 0:
+        return o.zero_(), lse.fill_(float("-inf"))
+    with th.cuda.device(q.device):
+        _call_planned("attention_forward", elem, _capi.OP_ATTENTION_FWD, [plan], max(q.size(0), k.size(0)), h, d,
+                      q.device, [_p(q), _p(k), _p(v), float(scale), _p(o), _p(lse), q.size(0), k.size(0), h, d])
+    return o, lse
+
+
+def attention_backward_planned(plan_r, plan_t, q, k, v, o, lse, d_o, scale):
+    """attention_backward on plans of both CSR orientations (plan_t built with the transposed CSR's edge ids lets
+    the row pass hand every edge's probability to the transposed pass)."""
+    d_o = d_o.contiguous()
+    _check_all(q=q, k=k, v=v, o=o, lse=lse, d_o=d_o)
+    elem = _elem(q, k, v, o, d_o)
+    h, d = _heads(q, True)
+    dq, dk, dv = th.empty_like(q), th.empty_like(k), th.empty_like(v)
+    if plan_r.n_edges == 0:
+        return [dq.zero_(), dk.zero_(), dv.zero_()]
+    with th.cuda.device(q.device):
+        op_id = _capi.OP_ATTENTION_BWD_PAIRS if plan_t.c.eid else _capi.OP_ATTENTION_BWD
+        _call_planned("attention_backward", elem, op_id, [plan_r, plan_t], max(q.size(0), k.size(0)), h, d, q.device,
+                      [_p(q), _p(k), _p(v), _p(o), _p(lse), _p(d_o), float(scale), _p(dq), _p(dk), _p(dv), q.size(0),
+                       k.size(0), h, d])
+    return [dq, dk, dv]

@@ -8,8 +8,8 @@ from torch.autograd import Function
 from . import graphop as _g
 from .part_csr import partition_csr  # noqa: F401  (the reference wrapper re-exports it, wrapper.py:4)
 
-__all__ = ["SparseSoftmax", "MaskedMMCSR", "NodeMulEdge", "VectorSPMM", "GraphAttention", "graph_attention",
-           "partition_csr", "chunk_size"]
+__all__ = ["SparseSoftmax", "MaskedMMCSR", "NodeMulEdge", "VectorSPMM", "GraphAttention", "GraphAttentionPlanned",
+           "graph_attention", "partition_csr", "chunk_size"]
 
 chunk_size = 32  # wrapper.py:6
 
@@ -99,6 +99,25 @@ class GraphAttention(Function):
         dq, dk, dv = _g.attention_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse, d_o,
                                            ctx.scale, eid_t=ctx.eid_t)
         return None, None, None, None, None, None, dq, dk, dv, None, None
+
+
+class GraphAttentionPlanned(Function):
+    """GraphAttention on graph plans: ``apply(plan_r, plan_t, Q, K, V, scale)`` with ``graphop.GraphPlan`` objects of
+    the row CSR and of the transposed CSR (the latter built with its edge ids).  Nothing that depends on the graph
+    alone is recomputed per call."""
+
+    @staticmethod
+    def forward(ctx, plan_r, plan_t, Q, K, V, scale):
+        o, lse = _g.attention_forward_planned(plan_r, Q, K, V, scale)
+        ctx.save_for_backward(Q, K, V, o, lse)
+        ctx.plans, ctx.scale = (plan_r, plan_t), scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        Q, K, V, o, lse = ctx.saved_tensors
+        dq, dk, dv = _g.attention_backward_planned(ctx.plans[0], ctx.plans[1], Q, K, V, o, lse, d_o, ctx.scale)
+        return None, None, dq, dk, dv, None
 
 
 def graph_attention(row, indptr, eid, indices, col, indptr_t, eid_t, indices_t, Q, K, V, scale):

@@ -4,9 +4,11 @@
  * This is the boundary a host binding links against.  It replaces the host launchers of the
  * reference extension (graphop/graphop_kernel.cu:235-600, the eight *_cuda_forward /
  * *_cuda_backward functions that graphop/graphop.cpp:8-214 declares and wraps for Python)
- * with plain pointers and sizes: no torch types, no allocation, no exceptions.  Every entry
- * point enqueues its kernels on `stream` and returns at once with a status code; nothing
- * synchronises the device.
+ * with plain pointers and sizes: no torch types, no allocation, no exceptions.  Every operator
+ * entry point enqueues its kernels on `stream` and returns at once with a status code; nothing
+ * synchronises the device.  Two set-up / debugging calls are the exceptions and say so below:
+ * graphop_check_graph_* (allocates one word with cudaMallocAsync and waits for its verdict) and
+ * graphop_plan_build_* (waits once for the graph's shape flags).
  *
  * Graph arguments follow the reference contract (graphop_kernel.cu:20, 41, ...): `row` holds
  * one owner node per chunk (length n_chunks), `indptr` the n_chunks + 1 chunk boundaries as
@@ -14,7 +16,8 @@
  * NULL means the identity), `indices` gives the other endpoint of a position.  Chunks come
  * from partition_csr (part_csr.py:13-27) or are the plain CSR rows (row = 0..N-1).  Required
  * of the caller: indptr non-decreasing, chunks of one node consecutive, node ids
- * non-decreasing along `row`, eid injective, n_edges < 2^31.  Under that contract every
+ * non-decreasing along `row` and below the node count passed with them, eid injective,
+ * n_edges < 2^31 (graphop_check_graph_* verifies all of it).  Under that contract every
  * reduction is computed by exactly one owner in a fixed order: results are bit-reproducible
  * (the reference accumulates with atomics, graphop/atomic.cuh:57-96).
  *
@@ -93,6 +96,91 @@ int graphop_check_graph_i32(const int32_t* row, const int32_t* indptr, const int
 int graphop_check_graph_i64(const int64_t* row, const int64_t* indptr, const int64_t* eid, const int64_t* indices,
                             int64_t n_chunks, int64_t n_edges, int64_t n_nodes, int64_t n_other, int* violations,
                             graphop_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Graph plans.  Every entry point above rebuilds, per call, what depends on the graph alone: the owner node of
+ * every CSR position (from the chunk table) and, for 64-bit indices, 32-bit copies of `indices` and `eid`.  A plan
+ * holds those once per graph, in memory the caller provides, and the *_planned entry points take plans in place of
+ * the (row, indptr, eid, indices) arguments.  The reference does its graph preprocessing on the host in Python
+ * loops before any op runs (part_csr.py:18-21, wrapper.py:93-112); a plan is the same one-time step, on the device.
+ *
+ * graphop_plan_build_* also looks at the graph's shape: GRAPHOP_PLAN_DENSE_BAND is set when every node's
+ * neighbours are one run of consecutive ids and any 128 consecutive nodes reach at most
+ * GRAPHOP_BAND_MAX_SPAN different neighbours (sliding-window attention written as a graph, the reference's
+ * block-diagonal test graph of wrapper.py:79-112): graphop_attention_forward_planned_bf16 then runs such a graph on
+ * the tensor cores.
+ *
+ * A plan refers to the caller's `indices` / `eid` arrays when they are 32-bit (they must outlive the plan) and to
+ * plan memory otherwise.  graphop_plan_build_* enqueues its kernels on `stream` and waits for them once, to read
+ * the shape flags back: it is a set-up call, not a per-step one.
+ * --------------------------------------------------------------------------------------------------------- */
+enum { GRAPHOP_PLAN_DENSE_BAND = 1 };
+#define GRAPHOP_BAND_MAX_SPAN 384
+
+typedef struct graphop_plan {
+  int64_t n_chunks;        /* chunks of the table the plan was built from */
+  int64_t n_edges;         /* CSR positions */
+  int64_t n_nodes;         /* bound on the owner node ids (rows of the per-node arrays below) */
+  const void* header;      /* device: first / one-past-last position any chunk covers */
+  const int32_t* erow;     /* device, n_edges: owner node of every position, -1 where no chunk covers it */
+  const int32_t* other;    /* device, n_edges: the other endpoint of every position; NULL when built without */
+  const int32_t* eid;      /* device, n_edges: edge id of every position; NULL: the identity */
+  const int32_t* node_lo;  /* device, n_nodes: first neighbour of every node (dense-band graphs; else undefined) */
+  const int32_t* node_deg; /* device, n_nodes: number of positions every node owns */
+  int32_t flags;           /* GRAPHOP_PLAN_* */
+  int32_t band_span;       /* most different neighbours any 128 consecutive nodes reach (dense-band graphs) */
+} graphop_plan_t;
+
+/* Bytes of device memory (256-byte aligned) a plan of these sizes needs. */
+size_t graphop_plan_bytes(int64_t n_chunks, int64_t n_edges, int64_t n_nodes, int index_bytes);
+/* Builds a plan in `memory`.  `indices` may be NULL for ops without a second endpoint (then no shape analysis is
+ * made), `eid` NULL for the identity.  Synchronises `stream` once. */
+int graphop_plan_build_i32(const int32_t* row, const int32_t* indptr, const int32_t* eid, const int32_t* indices,
+                           int64_t n_chunks, int64_t n_edges, int64_t n_nodes, void* memory, size_t memory_bytes,
+                           graphop_plan_t* plan, graphop_stream_t stream);
+int graphop_plan_build_i64(const int64_t* row, const int64_t* indptr, const int64_t* eid, const int64_t* indices,
+                           int64_t n_chunks, int64_t n_edges, int64_t n_nodes, void* memory, size_t memory_bytes,
+                           graphop_plan_t* plan, graphop_stream_t stream);
+
+/* The ten operations on plans: same results, same workspace query, argument meaning as in GRAPHOP_DECLARE below.
+ * plan_r: plan of the row (destination) CSR, plan_c / plan_t: plan of the column / transposed CSR (built with
+ * its `eid`: for the fused attention backward that is what lets the row pass hand (p, ds) to the transposed one). */
+#define GRAPHOP_DECLARE_PLANNED(SUF, T)                                                                              \
+  int graphop_maskedmm_csr_forward_planned_##SUF(const graphop_plan_t* plan, const T* A, const T* B, T* y,           \
+                                                 int64_t n_dst, int64_t n_src, int H, int D, void* workspace,        \
+                                                 size_t workspace_bytes, graphop_stream_t stream);                   \
+  int graphop_maskedmm_csr_backward_planned_##SUF(const graphop_plan_t* plan_r, const graphop_plan_t* plan_c,        \
+                                                  const T* A, const T* B, const T* dy, T* dA, T* dB, int64_t n_dst,  \
+                                                  int64_t n_src, int H, int D, void* workspace,                      \
+                                                  size_t workspace_bytes, graphop_stream_t stream);                  \
+  int graphop_node_mul_edge_forward_planned_##SUF(const graphop_plan_t* plan, const T* A, const T* B, T* y,          \
+                                                  int64_t n_dst, int H, int D, void* workspace,                      \
+                                                  size_t workspace_bytes, graphop_stream_t stream);                  \
+  int graphop_node_mul_edge_backward_planned_##SUF(const graphop_plan_t* plan, const T* A, const T* B, const T* dy,  \
+                                                   T* dA, T* dB, int64_t n_dst, int H, int D, void* workspace,       \
+                                                   size_t workspace_bytes, graphop_stream_t stream);                 \
+  int graphop_sparse_softmax_forward_planned_##SUF(const graphop_plan_t* plan, const T* x, T* y, int H,              \
+                                                   void* workspace, size_t workspace_bytes,                          \
+                                                   graphop_stream_t stream);                                         \
+  int graphop_sparse_softmax_backward_planned_##SUF(const graphop_plan_t* plan, const T* y, const T* dy, T* dx,      \
+                                                    int H, void* workspace, size_t workspace_bytes,                  \
+                                                    graphop_stream_t stream);                                        \
+  int graphop_vector_spmm_forward_planned_##SUF(const graphop_plan_t* plan, const T* edata, const T* x, T* y,        \
+                                                int64_t n_dst, int64_t n_src, int H, int D, void* workspace,         \
+                                                size_t workspace_bytes, graphop_stream_t stream);                    \
+  int graphop_vector_spmm_backward_planned_##SUF(const graphop_plan_t* plan_r, const graphop_plan_t* plan_t,         \
+                                                 const T* edata, const T* dy, const T* x, T* dedata, T* dx,          \
+                                                 int64_t n_dst, int64_t n_src, int H, int D, void* workspace,        \
+                                                 size_t workspace_bytes, graphop_stream_t stream);                   \
+  int graphop_attention_forward_planned_##SUF(const graphop_plan_t* plan, const T* q, const T* k, const T* v,        \
+                                              double scale, T* o, void* lse, int64_t n_dst, int64_t n_src, int H,    \
+                                              int D, void* workspace, size_t workspace_bytes,                        \
+                                              graphop_stream_t stream);                                              \
+  int graphop_attention_backward_planned_##SUF(const graphop_plan_t* plan_r, const graphop_plan_t* plan_t,           \
+                                               const T* q, const T* k, const T* v, const T* o, const void* lse,      \
+                                               const T* d_o, double scale, T* dq, T* dk, T* dv, int64_t n_dst,       \
+                                               int64_t n_src, int H, int D, void* workspace, size_t workspace_bytes, \
+                                               graphop_stream_t stream);
 
 #define GRAPHOP_DECLARE(SUF, T, I)                                                                                   \
   /* y[eid[k], h] = sum_d A[row(k), h, d] * B[indices[k], h, d]; edge ids no chunk covers get 0.                  \
@@ -194,6 +282,9 @@ GRAPHOP_DECLARE(f64_i32, double, int32_t)
 GRAPHOP_DECLARE(f64_i64, double, int64_t)
 GRAPHOP_DECLARE(bf16_i32, uint16_t, int32_t)
 GRAPHOP_DECLARE(bf16_i64, uint16_t, int64_t)
+GRAPHOP_DECLARE_PLANNED(f32, float)
+GRAPHOP_DECLARE_PLANNED(f64, double)
+GRAPHOP_DECLARE_PLANNED(bf16, uint16_t)
 
 #ifdef __cplusplus
 }

@@ -67,3 +67,24 @@ def assert_close(actual, expected, rtol, atol, what=""):
         raise AssertionError("%s: %d of %d elements out of tolerance (rtol %g atol %g); worst |%g - %g| = %g"
                              % (what, int(bad.sum()), a.numel(), rtol, atol, a.view(-1)[i], b.view(-1)[i],
                                 err.view(-1)[i]))
+
+
+def assert_rows_close(actual, expected, degree, rtol, atol, what=""):
+    """Row r of `actual` against `expected`: |diff| <= rtol |expected| + atol * max(1, degree[r] / 256).
+
+    Rows of at most 256 edges are held to (rtol, atol) as given; longer rows get an absolute allowance that grows
+    with their edge count: an fp32 sum of n signed terms of size s picks up a rounding error of the order
+    eps * n * s whatever order it is formed in (the reference's atomicAdd order included)."""
+    a = actual.detach().to("cpu", th.float64)
+    b = expected.detach().to("cpu", th.float64)
+    assert a.shape == b.shape, "%s: shape %s vs %s" % (what, tuple(a.shape), tuple(b.shape))
+    deg = th.as_tensor(degree).to("cpu", th.float64).clamp(min=256.0) / 256.0
+    tol = rtol * b.abs() + atol * deg.view(-1, *([1] * (b.dim() - 1)))
+    err = (a - b).abs()
+    bad = err > tol
+    if bad.any():
+        i = int(th.argmax((err - tol).reshape(-1)))
+        r = i // max(1, b[0].numel())
+        raise AssertionError("%s: %d of %d elements out of tolerance (rtol %g atol %g); worst at row %d (degree %d): "
+                             "|%g - %g| = %g" % (what, int(bad.sum()), a.numel(), rtol, atol, r, int(degree[r]),
+                                                 a.reshape(-1)[i], b.reshape(-1)[i], err.reshape(-1)[i]))

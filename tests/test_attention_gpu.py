@@ -3,14 +3,15 @@ float64 attention, and the autograd wiring of every Function against torch autog
 import pytest
 import torch as th
 
-from helpers import assert_close, chunked, graph_zoo
+from helpers import assert_close, assert_rows_close, chunked, graph_zoo
 from custom_op_benchmark_b200 import graphop, graphs, wrapper
 from oracle import graphop_oracle as orc
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 ZOO = graph_zoo()
-TOL = {th.float64: (1e-9, 1e-11), th.float32: (2e-5, 2e-6), th.bfloat16: (2e-2, 2e-2)}
+# relative / absolute tolerance on outputs of size O(1): fp32 as the specification states it (rel 1e-5 / abs 1e-6)
+TOL = {th.float64: (1e-9, 1e-11), th.float32: (1e-5, 1e-6), th.bfloat16: (2e-2, 2e-2)}
 
 
 def _qkv(g, h, d, dtype, seed, mag=1.0):
@@ -57,11 +58,12 @@ def test_fused_attention_matches_oracle_chain(name, g, cs, h, d, dtype, idt, mag
     if dtype == th.bfloat16:
         # o was rounded to bf16 before the backward read it: compare with a looser absolute floor
         at = 5e-2
-    # gradients are sums over a node's edges: fp32 round-off grows with sqrt(degree) beyond 256 edges
-    deg_max = max(int((g.indptr[1:] - g.indptr[:-1]).max()), int((g.indptr_t[1:] - g.indptr_t[:-1]).max()))
-    at = at * max(1.0, (deg_max / 256.0) ** 0.5)
-    for got, want, what in ((dq, want_dq, "dq"), (dk, want_dk, "dk"), (dv, want_dv, "dv")):
-        assert_close(got, want, rt * 5, at * max(1.0, float(want.abs().max())), what)
+    # Gradients are sums of products of two or three inputs: their absolute tolerance scales with the size of those
+    # products (4x for dO . v against delta, two sums that cancel), and only rows above 256 edges get the
+    # degree allowance of assert_rows_close.
+    deg, deg_t = g.indptr[1:] - g.indptr[:-1], g.indptr_t[1:] - g.indptr_t[:-1]
+    for got, want, dd, what in ((dq, want_dq, deg, "dq"), (dk, want_dk, deg_t, "dk"), (dv, want_dv, deg_t, "dv")):
+        assert_rows_close(got, want, dd, rt, 4 * at * max(1.0, float(want.abs().max())), what)
     # the same backward with the transposed CSR's edge ids: (p, ds) handed from the destination pass to the
     # source pass instead of recomputed (valid when the row CSR's edge ids are its positions)
     assert th.equal(r[2].long(), th.arange(g.n_edges))
@@ -69,7 +71,7 @@ def test_fused_attention_matches_oracle_chain(name, g, cs, h, d, dtype, idt, mag
                                                V.to(DEV), o, lse, dO.to(DEV), scale, eid_t=cc[2])
     assert th.equal(dq2, dq)
     for got, want, what in ((dk2, want_dk, "dk (pairs)"), (dv2, want_dv, "dv (pairs)")):
-        assert_close(got, want, rt * 5, at * max(1.0, float(want.abs().max())), what)
+        assert_rows_close(got, want, deg_t, rt, 4 * at * max(1.0, float(want.abs().max())), what)
 
 
 def test_fused_attention_matches_dense_masked_config1():

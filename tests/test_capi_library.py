@@ -10,17 +10,21 @@ from custom_op_benchmark_b200 import _capi
 
 def _header_symbols():
     text = open(os.path.join(ROOT, "include", "graphop_b200.h")).read()
-    body = text[text.index("#define GRAPHOP_DECLARE"):text.index("GRAPHOP_DECLARE(f32_i32")]
+    body = text[text.index("#define GRAPHOP_DECLARE(SUF"):text.index("GRAPHOP_DECLARE(f32_i32")]
     ops = re.findall(r"int (graphop_\w+)_##SUF", body)
     suffixes = re.findall(r"^GRAPHOP_DECLARE\((\w+),", text, re.M)
     names = ["%s_%s" % (op, s) for op in ops for s in suffixes]
+    planned = text[text.index("#define GRAPHOP_DECLARE_PLANNED"):text.index("#define GRAPHOP_DECLARE(SUF")]
+    pops = re.findall(r"int (graphop_\w+)_##SUF", planned)
+    psuf = re.findall(r"^GRAPHOP_DECLARE_PLANNED\((\w+),", text, re.M)
+    names += ["%s_%s" % (op, s) for op in pops for s in psuf]
     names += re.findall(r"^(?:int|size_t|long long|const char\*) (graphop_\w+)\(", text, re.M)
     return sorted(set(names))
 
 
 def test_header_and_binding_agree():
     assert _header_symbols() == sorted(_capi.exported_symbols())
-    assert len(_header_symbols()) == 10 * 6 + 9
+    assert len(_header_symbols()) == 10 * 6 + 10 * 3 + 12
 
 
 def test_product_library_carries_no_benchmark_hooks():
