@@ -171,6 +171,16 @@ class Workload:
         self.R = [row.to(th.int32), ptr.to(th.int32), g.eid, g.indices]
         self.C = [col.to(th.int32), ptr_t.to(th.int32), g.eid_t, g.indices_t]
         self.g, self.e, self.n_dst, self.n_src = g, g.n_edges, g.n_dst, g.n_src
+        # graph plans: what depends on the graph alone (owner of every position, shape flags), built once like the
+        # chunk tables above; `planned` = False times the chunk-table entry points, which rebuild it in every call
+        from custom_op_benchmark_b200 import graphop
+        th.cuda.synchronize()
+        t0 = time.time()
+        self.plan_r = graphop.GraphPlan(*self.R, g.n_dst)
+        self.plan_t = graphop.GraphPlan(*self.C, g.n_src)
+        th.cuda.synchronize()
+        self.plan_build_ms = (time.time() - t0) * 1e3
+        self.planned = True
         self.gen = th.Generator().manual_seed(1000 + rank)
 
     def _host(self, *shape, mag=1.0):
@@ -250,6 +260,10 @@ class AttentionWorkload(Workload):
         self.alg = {
             # q, k, v read, o written, indices, lse written
             "attention_fwd": z["F_dst"] + 2 * z["F_src"] + z["F_dst"] + z["I"] + z["stat"],
+            # the tensor-core kernel of dense-band graphs reads (first, count) per node instead of the edge list
+            "attention_fwd_banded": z["F_dst"] + 2 * z["F_src"] + z["F_dst"] + 2 * self.n_dst * 4 + z["stat"],
+            "attention_bwd_dst_banded": 3 * z["F_dst"] + 2 * z["F_src"] + z["F_dst"] + 2 * self.n_dst * 4 + 3 * z["stat"],
+            "attention_bwd_src_banded": 2 * z["F_src"] + 2 * z["F_dst"] + 2 * z["F_src"] + 2 * self.n_src * 4 + 2 * z["stat"],
             # q, o, dO, k, v read, dq written, indices, lse read, delta written
             "attention_bwd_dst": 3 * z["F_dst"] + 2 * z["F_src"] + z["F_dst"] + z["I"] + 2 * z["stat"],
             # k, v, q, dO read, dk, dv written, transposed indices, lse and delta read
@@ -266,11 +280,17 @@ class AttentionWorkload(Workload):
     def forward(self):
         from custom_op_benchmark_b200 import graphop
         R = self.R
-        self.o, self.lse = graphop.attention_forward(R[0], R[1], R[3], self.Q, self.K, self.V, self.scale)
+        if self.planned:
+            self.o, self.lse = graphop.attention_forward_planned(self.plan_r, self.Q, self.K, self.V, self.scale)
+        else:
+            self.o, self.lse = graphop.attention_forward(R[0], R[1], R[3], self.Q, self.K, self.V, self.scale)
 
     def backward(self):
         from custom_op_benchmark_b200 import graphop
         R, C = self.R, self.C
+        if self.planned:
+            return graphop.attention_backward_planned(self.plan_r, self.plan_t, self.Q, self.K, self.V, self.o,
+                                                      self.lse, self.dO, self.scale)
         return graphop.attention_backward(R[0], R[1], R[3], C[0], C[1], C[3], self.Q, self.K, self.V, self.o, self.lse,
                                           self.dO, self.scale, eid_t=C[2])
 
@@ -291,7 +311,10 @@ class AttentionWorkload(Workload):
         from custom_op_benchmark_b200 import wrapper
         R, C = self.R, self.C
         q, k, v = (t.detach().requires_grad_(True) for t in stage[:3])
-        out = wrapper.GraphAttention.apply(R[0], R[1], R[3], C[0], C[1], C[3], q, k, v, self.scale, C[2])
+        if self.planned:
+            out = wrapper.GraphAttentionPlanned.apply(self.plan_r, self.plan_t, q, k, v, self.scale)
+        else:
+            out = wrapper.GraphAttention.apply(R[0], R[1], R[3], C[0], C[1], C[3], q, k, v, self.scale, C[2])
         out.backward(stage[3])
         return [out.detach(), q.grad, k.grad, v.grad]
 
@@ -321,13 +344,21 @@ class GatWorkload(Workload):
 
     def forward(self):
         from custom_op_benchmark_b200 import graphop
-        self.y1 = graphop.node_mul_edge_forward(*self.R[:3], self.X, self.Be)
-        self.y2 = graphop.vector_spmm_forward(*self.R, self.w, self.X)
+        if self.planned:
+            self.y1 = graphop.node_mul_edge_forward_planned(self.plan_r, self.X, self.Be)
+            self.y2 = graphop.vector_spmm_forward_planned(self.plan_r, self.w, self.X)
+        else:
+            self.y1 = graphop.node_mul_edge_forward(*self.R[:3], self.X, self.Be)
+            self.y2 = graphop.vector_spmm_forward(*self.R, self.w, self.X)
 
     def backward(self):
         from custom_op_benchmark_b200 import graphop
-        a = graphop.node_mul_edge_backward(*self.R[:3], self.X, self.Be, self.dY1)
-        b = graphop.vector_spmm_backward(*self.R, *self.C, self.w, self.dY2, self.X)
+        if self.planned:
+            a = graphop.node_mul_edge_backward_planned(self.plan_r, self.X, self.Be, self.dY1)
+            b = graphop.vector_spmm_backward_planned(self.plan_r, self.plan_t, self.w, self.dY2, self.X)
+        else:
+            a = graphop.node_mul_edge_backward(*self.R[:3], self.X, self.Be, self.dY1)
+            b = graphop.vector_spmm_backward(*self.R, *self.C, self.w, self.dY2, self.X)
         return a + b
 
     def max_err(self):
@@ -371,11 +402,18 @@ class SddmmSoftmaxWorkload(Workload):
 
     def forward(self):
         from custom_op_benchmark_b200 import graphop
-        self.s = graphop.maskedmm_csr_forward(*self.R, self.Q, self.K)
-        self.p = graphop.sparse_softmax_forward(*self.R[:3], self.s)
+        if self.planned:
+            self.s = graphop.maskedmm_csr_forward_planned(self.plan_r, self.Q, self.K)
+            self.p = graphop.sparse_softmax_forward_planned(self.plan_r, self.s)
+        else:
+            self.s = graphop.maskedmm_csr_forward(*self.R, self.Q, self.K)
+            self.p = graphop.sparse_softmax_forward(*self.R[:3], self.s)
 
     def backward(self):
         from custom_op_benchmark_b200 import graphop
+        if self.planned:
+            ds = graphop.sparse_softmax_backward_planned(self.plan_r, self.p, self.dP)
+            return graphop.maskedmm_csr_backward_planned(self.plan_r, self.plan_t, self.Q, self.K, ds)
         ds = graphop.sparse_softmax_backward(*self.R[:3], self.p, self.dP)
         return graphop.maskedmm_csr_backward(*self.R, *self.C, self.Q, self.K, ds)
 
@@ -866,6 +904,17 @@ def run_gpu(args):
     sampler.stop()
     clocks = sampler.summary(t_wall0, t_wall1)
 
+    # -- the same steps through the chunk-table entry points (the reference's argument lists: no plan) ----------
+    chunk_api = None
+    if getattr(wl, "planned", False):
+        wl.planned = False
+        step_device()
+        cms, cf, cb, _, _ = time_steps(wl, max(2, min(args.steps, 5)), world)
+        wl.planned = True
+        chunk_api = {"ms_per_step": cms / max(2, min(args.steps, 5)), "forward_ms": cf, "backward_ms": cb,
+                     "what": "the same step through the entry points that take (row, indptr, eid, indices): the owner "
+                             "table is rebuilt from the chunk table in every call"}
+
     # -- end to end: the autograd Functions a user calls, host buffers copied in and out every step
     e2e_ms = EndToEnd(wl, dev).time(max(3, min(args.steps, 6)), world)
     th.cuda.empty_cache()
@@ -913,7 +962,10 @@ def run_gpu(args):
                        "per_rank": "a row shard of one graph" if spec["ops"] == "sharded_spmm" else "own graph",
                        "l2": "inputs (%.2f GB) %s the 126 MB L2" % (
                            in_bytes / 1e9, "larger than" if in_bytes > 2 * 126e6 else "NOT larger than"),
-                       "resident": wl.resident},
+                       "resident": wl.resident,
+                       "plans": ("graph plans built once per graph beside the chunk tables (%.1f ms for both CSR "
+                                 "orientations), not per step" % wl.plan_build_ms) if getattr(wl, "planned", False)
+                       else "none"},
             "e2e": {"value": units / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "how": "pinned host buffers, copies in / compute / copies out on three streams, two staging sets"},
@@ -934,6 +986,8 @@ def run_gpu(args):
         if traffic_step:
             out["roofline"]["step_dram_traffic"] = traffic_step
             out["roofline"]["step_dram_frac"] = traffic_step / (ms_per_step * 1e-3) / 1e9 / peak
+        if chunk_api:
+            out["chunk_table_api"] = chunk_api
         if graph_ms is not None:
             out["cuda_graph"] = graph_ms if isinstance(graph_ms, dict) else {
                 "ms_per_step": graph_ms, "value": units / (graph_ms * 1e-3), "unit": UNIT,

@@ -77,9 +77,15 @@ UNTYPED = {
 }
 
 
+DLPACK_ENTRY_POINTS = ["graphop_dl_" + op for op in (
+    "maskedmm_csr_forward", "maskedmm_csr_backward", "node_mul_edge_forward", "node_mul_edge_backward",
+    "sparse_softmax_forward", "sparse_softmax_backward", "vector_spmm_forward", "vector_spmm_backward",
+    "attention_forward", "attention_backward")]   # include/graphop_dlpack.h; bound in dlpack_ops.py
+
+
 def exported_symbols():
-    """Every symbol include/graphop_b200.h declares."""
-    names = list(UNTYPED)
+    """Every symbol include/graphop_b200.h and include/graphop_dlpack.h declare."""
+    names = list(UNTYPED) + list(DLPACK_ENTRY_POINTS)
     for op in SIGNATURES:
         for e in ELEM_SUFFIXES:
             for i in INDEX_SUFFIXES:

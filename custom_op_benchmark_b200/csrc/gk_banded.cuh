@@ -25,7 +25,9 @@
 namespace gk {
 namespace banded {
 
-constexpr int kTileM = 128;                 // query nodes per block = threads per block = tensor-memory lanes
+constexpr int kTileM = 128;                 // nodes per block = tensor-memory lanes
+constexpr int kColGroups = 4;               // threads per node row: each takes every fourth 32-column chunk
+constexpr int kThreads = kTileM * kColGroups;   // 16 warps: warp w works on lanes 32 (w % 4) .. + 31, chunks w / 4 + 4 i
 constexpr int kD = 64;                      // features per head: one 128-byte swizzle row of bf16
 constexpr int kSpan = GRAPHOP_BAND_MAX_SPAN;  // key rows a tile reaches at most
 constexpr int kKeyBlock = 128;              // key rows per TMA box and per score MMA
@@ -38,7 +40,8 @@ constexpr int kOffK = kOffQ + kBlockBytes;
 constexpr int kOffV = kOffK + (kSpan / kKeyBlock) * kBlockBytes;
 constexpr int kOffP = kOffV + (kSpan / kKeyBlock) * kBlockBytes;
 constexpr int kOffBar = kOffP + kPanels * kBlockBytes;
-constexpr int kSmemBytes = kOffBar + 64 + 1024;             // barriers, tensor-memory address, alignment slack
+constexpr int kOffRed = kOffBar + 64;                       // per-row partial maxima and sums of the column groups
+constexpr int kSmemBytes = kOffRed + 2 * kColGroups * kTileM * 4 + 1024;   // + alignment slack
 constexpr int kTmemCols = 512;
 constexpr int kColO = kSpan;                // scores in columns [0, 384), the output in [384, 448)
 constexpr unsigned kWaitLimit = 400000u;
@@ -110,6 +113,34 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 16 consecutive fp32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h2 = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h2);
+}
+// 16 fp32 values -> bf16 -> 32 bytes of global memory (NaN when the tile's waits ran out)
+__device__ __forceinline__ void store_out16(__nv_bfloat16* dst, const float (&v)[16], float mul, bool ok) {
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) w[e] = pack_bf16(ok ? v[8 * q + 2 * e] * mul : NAN, ok ? v[8 * q + 2 * e + 1] * mul : NAN);
+    *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 struct Params {
   __nv_bfloat16* o;          // (n_dst, H, 64)
   float* lse;                // (n_dst, H)
@@ -120,7 +151,7 @@ struct Params {
   float scale;
 };
 
-__global__ void __launch_bounds__(kTileM, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ unsigned char raw_smem[];
@@ -129,12 +160,16 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const uint32_t s_base = smem_u32(smem);
   const uint32_t bar_load = s_base + kOffBar, bar_s = bar_load + 8, bar_o = bar_load + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 32);
-  int* s_red = reinterpret_cast<int*>(smem + kOffBar + 40);   // 4 ints: per-warp minima of the first neighbour
+  int* s_red = reinterpret_cast<int*>(smem + kOffBar + 40);   // 4 ints: per-quarter minima of the first neighbour
+  float* s_max = reinterpret_cast<float*>(smem + kOffRed);     // [column group][row]
+  float* s_sum = s_max + kColGroups * kTileM;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, cg = warp >> 2;                // tensor-memory lane quarter, column group
+  const int row = quarter * 32 + lane;                         // row of the tile = tensor-memory lane
   const int head = blockIdx.y;
   const long long r0 = (long long)blockIdx.x * kTileM;
-  const long long r = r0 + tid;
+  const long long r = r0 + row;
 
   // this thread's node: first neighbour and count
   int lo = INT_MAX, deg = 0;
@@ -145,7 +180,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   int wmin = lo;
 #pragma unroll
   for (int o = 16; o; o >>= 1) wmin = min(wmin, __shfl_xor_sync(kFull, wmin, o));
-  if (lane == 0) s_red[warp] = wmin;
+  if (lane == 0 && cg == 0) s_red[quarter] = wmin;
   if (tid == 0) {
     mbar_init(bar_load, 1);
     mbar_init(bar_s, 1);
@@ -194,7 +229,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     ok = __syncthreads_and(ok && mbar_wait(bar_s, 0));
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // this thread's row: columns [jlo, jhi] are its node's neighbours
+    // this thread's row: columns [jlo, jhi] are its node's neighbours; it handles chunks cg, cg + 4, cg + 8
     const int jlo = deg > 0 ? lo - kmin : 1, jhi = deg > 0 ? lo - kmin + deg - 1 : 0;
     int wlo = deg > 0 ? jlo : INT_MAX, whi = deg > 0 ? jhi : -1;
 #pragma unroll
@@ -203,11 +238,11 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       whi = max(whi, __shfl_xor_sync(kFull, whi, o));
     }
     const int c_first = wlo == INT_MAX ? 0 : wlo / 32, c_last = whi < 0 ? -1 : whi / 32;   // warp-uniform chunk range
-    const uint32_t row_taddr = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t row_taddr = tmem + ((uint32_t)(quarter * 32) << 16);
     const float sl2 = p.scale * 1.4426950408889634f;
     float m = -INFINITY;
-    if (ok) {
-      for (int c = c_first; c <= c_last; ++c) {
+    for (int c = cg; c < kSpan / 32; c += kColGroups) {
+      if (ok && c >= c_first && c <= c_last) {
         float v[32];
         tmem_ld32(row_taddr + c * 32, v);
 #pragma unroll
@@ -217,10 +252,14 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
       }
     }
+    s_max[cg * kTileM + row] = m;
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < kColGroups; ++g) m = fmaxf(m, s_max[g * kTileM + row]);
     const float msl2 = deg > 0 ? m * sl2 : 0.f;
     float l = 0.f;
-    unsigned char* prow = smem + kOffP + tid * kRowBytes;   // this row inside each 64-key panel
-    for (int c = 0; c < kSpan / 32; ++c) {
+    unsigned char* prow = smem + kOffP + row * kRowBytes;   // this row inside each 64-key panel
+    for (int c = cg; c < kSpan / 32; c += kColGroups) {
       float v[32];
       const bool live = ok && c >= c_first && c <= c_last;
       if (live) tmem_ld32(row_taddr + c * 32, v);
@@ -234,23 +273,26 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2f(fmaf(v[j + 1], sl2, -msl2));
         }
         l += p0 + p1;
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-        packed[j / 2] = *reinterpret_cast<uint32_t*>(&h2);
+        packed[j / 2] = pack_bf16(p0, p1);
       }
       // 32 keys = 4 chunks of 16 bytes in panel c / 2, at chunk index (c & 1) * 4 + q, swizzled by the row
       unsigned char* panel = prow + (c >> 1) * kBlockBytes;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const int chunk = ((c & 1) * 4 + q) ^ (tid & 7);
+        const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
         *reinterpret_cast<uint4*>(panel + chunk * 16) =
             make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
       }
     }
+    s_sum[cg * kTileM + row] = l;
     // the probabilities were written through the generic proxy; the tensor core reads through the async proxy
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    l = 0.f;
+#pragma unroll
+    for (int g = 0; g < kColGroups; ++g) l += s_sum[g * kTileM + row];
     if (ok && tid == 0) {
       constexpr uint32_t idesc = umma_idesc(kTileM, kD, true);
 #pragma unroll
@@ -264,34 +306,18 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     ok = __syncthreads_and(ok && mbar_wait(bar_o, 0));
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    __nv_bfloat16* orow = p.o + ((long long)r * p.H + head) * kD;
-    const float inv = deg > 0 ? 1.f / l : 0.f;
+    // this thread's 16 of the row's 64 output features
+    float v[16];
+    if (ok) tmem_ld16(row_taddr + kColO + cg * 16, v);   // warp-wide, whether or not the lane's row exists
+    if (r < p.n_dst) {
+      if (ok && deg == 0) {
 #pragma unroll
-    for (int c = 0; c < kD / 32; ++c) {
-      float v[32];
-      if (ok) {  // every lane of the warp reads, whether or not its row exists: the load is warp-wide
-        tmem_ld32(row_taddr + kColO + c * 32, v);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = NAN;
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
       }
-      if (r < p.n_dst) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float a0 = ok ? (deg > 0 ? v[8 * q + 2 * e] * inv : 0.f) : NAN;
-            const float a1 = ok ? (deg > 0 ? v[8 * q + 2 * e + 1] * inv : 0.f) : NAN;
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(a0, a1);
-            w[e] = *reinterpret_cast<uint32_t*>(&h2);
-          }
-          *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
+      store_out16(p.o + ((long long)r * p.H + head) * kD + cg * 16, v, deg > 0 ? 1.f / l : 0.f, ok);
+      if (cg == 0) p.lse[(long long)r * p.H + head] = !ok ? NAN : (deg > 0 ? m * p.scale + logf(l) : -INFINITY);
     }
-    if (r < p.n_dst) p.lse[(long long)r * p.H + head] = !ok ? NAN : (deg > 0 ? m * p.scale + logf(l) : -INFINITY);
-  } else if (r < p.n_dst) {  // no node of the tile has a neighbour
+  } else if (r < p.n_dst && cg == 0) {  // no node of the tile has a neighbour
     __nv_bfloat16* orow = p.o + ((long long)r * p.H + head) * kD;
 #pragma unroll
     for (int q = 0; q < kD / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
@@ -299,6 +325,270 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   }
 
   // every thread is done with tensor memory: hand it back
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Backward.  Two kernels with the forward's structure, one per side, so that every gradient row has one owner
+// (no atomics, as everywhere else):
+//   destination side, a tile of 128 query nodes:  S = Q K^T and dP = dO V^T per block of 128 keys,
+//       p = exp(scale S - lse), dS = p (dP - delta) scale,  dQ += dS K;   delta = dO . O is formed per row first
+//       and left, with lse, in `stat` for the other side;
+//   source side, a tile of 128 key nodes:  S^T = K Q^T and dP^T = V dO^T per block of 128 queries,
+//       the same p and dS (transposed: a thread is a key, a column a query),  dV += P^T dO,  dK += dS^T Q.
+// Shared memory per tile: the four operand tiles, one 128 x 128 bf16 staging tile per product (32 KB each),
+// the queries' (lse, delta) pairs; tensor memory: 2 x 128 score columns and 64 per gradient.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kBlocks = kSpan / kKeyBlock;   // blocks of 128 along the band
+constexpr int kStageBytes = 2 * kBlockBytes; // a 128 x 128 bf16 tile: two 64-column panels
+
+// 32 columns of one 128 x 128 staging tile row: 4 chunks of 16 bytes at chunk (c & 1) * 4 + q of panel c >> 1
+__device__ __forceinline__ void store_stage_row(unsigned char* row_in_panel0, int c, int row, const uint32_t (&packed)[16]) {
+  unsigned char* panel = row_in_panel0 + (c >> 1) * kBlockBytes;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
+    *reinterpret_cast<uint4*>(panel + chunk * 16) =
+        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+  }
+}
+struct BwdParams {
+  const __nv_bfloat16* o;     // (n_dst, H, 64): destination side only
+  const __nv_bfloat16* d_o;   // (n_dst, H, 64): destination side only (delta)
+  const float* lse;           // (n_dst, H): destination side only
+  float2* stat;               // (n_dst, H) (lse, delta): written by the destination side, read by the source side
+  __nv_bfloat16* out0;        // dq (destination side) / dk (source side)
+  __nv_bfloat16* out1;        // dv (source side)
+  const int32_t* node_lo;     // first neighbour of every owned node
+  const int32_t* node_deg;
+  long long n_own;            // nodes on the owning side
+  long long n_other;          // nodes on the other side
+  int H;
+  float scale;
+};
+
+constexpr int kBOffA = 0;                          // owned tile, first operand (q | k)
+constexpr int kBOffB = kBOffA + kBlockBytes;       // owned tile, second operand (dO | v)
+constexpr int kBOffC = kBOffB + kBlockBytes;       // band, first operand (k | q)
+constexpr int kBOffD = kBOffC + kBlocks * kBlockBytes;   // band, second operand (v | dO)
+constexpr int kBOffS0 = kBOffD + kBlocks * kBlockBytes;  // staging tile 0 (dS | P^T)
+constexpr int kBOffS1 = kBOffS0 + kStageBytes;           // staging tile 1 (dS^T, source side)
+constexpr int kBOffStat = kBOffS1 + kStageBytes;         // (lse, delta) of the band's queries (source side)
+constexpr int kBOffBar = kBOffStat + kSpan * 8;
+constexpr int kBSmemBytes = kBOffBar + 64 + 1024;
+
+// kSrc = false: destination side (owned = queries); true: source side (owned = keys)
+template <bool kSrc>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_d,
+                          const BwdParams p) {
+  extern __shared__ unsigned char raw_smem[];
+  unsigned char* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
+  const uint32_t s_base = smem_u32(smem);
+  const uint32_t bar_load = s_base + kBOffBar, bar_s = bar_load + 8, bar_g = bar_load + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBOffBar + 32);
+  int* s_red = reinterpret_cast<int*>(smem + kBOffBar + 40);
+  float2* s_stat = reinterpret_cast<float2*>(smem + kBOffStat);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, cg = warp >> 2;   // tensor-memory lane quarter; which 32 of a block's 128 columns
+  const int row = quarter * 32 + lane;
+  const int head = blockIdx.y;
+  const long long r0 = (long long)blockIdx.x * kTileM;
+  const long long r = r0 + row;
+  int lo = INT_MAX, deg = 0;
+  if (r < p.n_own) {
+    deg = p.node_deg[r];
+    if (deg > 0) lo = p.node_lo[r];
+  }
+  int wmin = lo;
+#pragma unroll
+  for (int o = 16; o; o >>= 1) wmin = min(wmin, __shfl_xor_sync(kFull, wmin, o));
+  if (lane == 0 && cg == 0) s_red[quarter] = wmin;
+  if (tid == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_g, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  const int bmin = min(min(s_red[0], s_red[1]), min(s_red[2], s_red[3]));   // first node of the band
+  bool ok = true;
+  constexpr int kColS = 0, kColP = kKeyBlock, kColG0 = 2 * kKeyBlock, kColG1 = 2 * kKeyBlock + kD;
+
+  if (bmin != INT_MAX) {
+    if (tid == 0) {
+      mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * (2 + 2 * kBlocks)));
+      tma_load_3d(s_base + kBOffA, &map_a, bar_load, 0, head, (int)r0);
+      tma_load_3d(s_base + kBOffB, &map_b, bar_load, 0, head, (int)r0);
+#pragma unroll
+      for (int b = 0; b < kBlocks; ++b) {
+        tma_load_3d(s_base + kBOffC + b * kBlockBytes, &map_c, bar_load, 0, head, bmin + b * kKeyBlock);
+        tma_load_3d(s_base + kBOffD + b * kBlockBytes, &map_d, bar_load, 0, head, bmin + b * kKeyBlock);
+      }
+    }
+    // per-row scalars while the tiles travel
+    float lse2 = 0.f, delta = 0.f;
+    const float kL2e = 1.4426950408889634f;
+    if constexpr (!kSrc) {
+      if (r < p.n_own) {
+        const uint4* orow = reinterpret_cast<const uint4*>(p.o + ((long long)r * p.H + head) * kD);
+        const uint4* grow = reinterpret_cast<const uint4*>(p.d_o + ((long long)r * p.H + head) * kD);
+#pragma unroll
+        for (int q = 0; q < kD / 8; ++q) {
+          const uint4 ov = __ldg(orow + q), gv = __ldg(grow + q);
+          const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+          const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 of = __bfloat1622float2(o2[e]), gf = __bfloat1622float2(g2[e]);
+            delta += of.x * gf.x + of.y * gf.y;
+          }
+        }
+        const float l = p.lse[(long long)r * p.H + head];
+        lse2 = l * kL2e;
+        if (cg == 0) p.stat[(long long)r * p.H + head] = make_float2(l, delta);
+      }
+    } else {
+      // (lse, delta) of the band's queries: column j of the scores is query bmin + j
+      for (int i = tid; i < kSpan; i += kThreads) {
+        const long long qn = (long long)bmin + i;
+        s_stat[i] = qn < p.n_other ? p.stat[qn * p.H + head] : make_float2(0.f, 0.f);
+      }
+    }
+    ok = __syncthreads_and(mbar_wait(bar_load, 0));
+
+    const int jlo = deg > 0 ? lo - bmin : 1, jhi = deg > 0 ? lo - bmin + deg - 1 : 0;
+    int wlo = deg > 0 ? jlo : INT_MAX, whi = deg > 0 ? jhi : -1;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      wlo = min(wlo, __shfl_xor_sync(kFull, wlo, o));
+      whi = max(whi, __shfl_xor_sync(kFull, whi, o));
+    }
+    const uint32_t row_taddr = tmem + ((uint32_t)(quarter * 32) << 16);
+    const float sl2 = p.scale * kL2e;
+    unsigned char* stage0 = smem + kBOffS0 + row * kRowBytes;
+    unsigned char* stage1 = smem + kBOffS1 + row * kRowBytes;
+
+    for (int b = 0; b < kBlocks; ++b) {
+      if (ok && tid == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        constexpr uint32_t idesc = umma_idesc(kTileM, kKeyBlock, false);
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {   // scores: owned first operand x band first operand
+          umma_f16(tmem + kColS, umma_desc(s_base + kBOffA + kk * 32, 16, 1024),
+                   umma_desc(s_base + kBOffC + b * kBlockBytes + kk * 32, 16, 1024), idesc, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {   // dP: owned second operand x band second operand
+          umma_f16(tmem + kColP, umma_desc(s_base + kBOffB + kk * 32, 16, 1024),
+                   umma_desc(s_base + kBOffD + b * kBlockBytes + kk * 32, 16, 1024), idesc, kk > 0);
+        }
+        umma_commit(bar_s);
+      }
+      ok = __syncthreads_and(ok && mbar_wait(bar_s, b & 1));
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+      {
+        const int c = cg;   // this thread's 32 of the block's 128 columns
+        const int col0 = b * kKeyBlock + c * 32;
+        const bool live = ok && col0 <= whi && col0 + 31 >= wlo;   // warp-uniform
+        uint32_t pk0[16], pk1[16];
+        if (live) {
+          float sv[32], dv[32];
+          tmem_ld32(row_taddr + kColS + c * 32, sv);
+          tmem_ld32(row_taddr + kColP + c * 32, dv);
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float pa = 0.f, pb = 0.f, da = 0.f, db = 0.f;
+            const int col = col0 + j;
+            if (col >= jlo && col <= jhi) {
+              const float l2 = kSrc ? s_stat[col].x * kL2e : lse2, dl = kSrc ? s_stat[col].y : delta;
+              pa = exp2f(fmaf(sv[j], sl2, -l2));
+              da = pa * (dv[j] - dl) * p.scale;
+            }
+            if (col + 1 >= jlo && col + 1 <= jhi) {
+              const float l2 = kSrc ? s_stat[col + 1].x * kL2e : lse2, dl = kSrc ? s_stat[col + 1].y : delta;
+              pb = exp2f(fmaf(sv[j + 1], sl2, -l2));
+              db = pb * (dv[j + 1] - dl) * p.scale;
+            }
+            pk0[j / 2] = kSrc ? pack_bf16(pa, pb) : pack_bf16(da, db);
+            pk1[j / 2] = pack_bf16(da, db);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { pk0[j] = 0u; pk1[j] = 0u; }
+        }
+        store_stage_row(stage0, c, row, pk0);
+        if constexpr (kSrc) store_stage_row(stage1, c, row, pk1);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncthreads();
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ok && tid == 0) {
+        constexpr uint32_t idesc = umma_idesc(kTileM, kD, true);
+#pragma unroll
+        for (int ks = 0; ks < kKeyBlock / 16; ++ks) {
+          const uint32_t a_off = (ks >> 2) * kBlockBytes + (ks & 3) * 32;
+          if constexpr (!kSrc) {   // dQ += dS K_b
+            umma_f16(tmem + kColG0, umma_desc(s_base + kBOffS0 + a_off, 16, 1024),
+                     umma_desc(s_base + kBOffC + b * kBlockBytes + ks * 16 * kRowBytes, 16, 1024), idesc, (b | ks) != 0);
+          } else {                 // dV += P^T dO_b,  dK += dS^T Q_b
+            umma_f16(tmem + kColG1, umma_desc(s_base + kBOffS0 + a_off, 16, 1024),
+                     umma_desc(s_base + kBOffD + b * kBlockBytes + ks * 16 * kRowBytes, 16, 1024), idesc, (b | ks) != 0);
+            umma_f16(tmem + kColG0, umma_desc(s_base + kBOffS1 + a_off, 16, 1024),
+                     umma_desc(s_base + kBOffC + b * kBlockBytes + ks * 16 * kRowBytes, 16, 1024), idesc, (b | ks) != 0);
+          }
+        }
+        umma_commit(bar_g);
+      }
+      ok = __syncthreads_and(ok && mbar_wait(bar_g, b & 1));
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+
+    // gradients of the owned rows: this thread's 16 of the 64 features
+    {
+      float g0[16], g1[16];
+      if (ok) {
+        tmem_ld16(row_taddr + kColG0 + cg * 16, g0);
+        if constexpr (kSrc) tmem_ld16(row_taddr + kColG1 + cg * 16, g1);
+      }
+      if (r < p.n_own) {
+        const long long at = ((long long)r * p.H + head) * kD + cg * 16;
+        const float keep = deg > 0 ? 1.f : 0.f;
+        if (ok && deg == 0) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { g0[j] = 0.f; g1[j] = 0.f; }
+        }
+        store_out16(p.out0 + at, g0, keep, ok);
+        if constexpr (kSrc) store_out16(p.out1 + at, g1, keep, ok);
+      }
+    }
+  } else if (r < p.n_own && cg == 0) {  // no owned node of the tile has a neighbour: zero gradients
+    const long long at = ((long long)r * p.H + head) * kD;
+#pragma unroll
+    for (int q = 0; q < kD / 8; ++q) {
+      *reinterpret_cast<uint4*>(p.out0 + at + q * 8) = make_uint4(0, 0, 0, 0);
+      if constexpr (kSrc) *reinterpret_cast<uint4*>(p.out1 + at + q * 8) = make_uint4(0, 0, 0, 0);
+    }
+    if constexpr (!kSrc) p.stat[(long long)r * p.H + head] = make_float2(p.lse[(long long)r * p.H + head], 0.f);
+  }
+
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
@@ -358,8 +648,55 @@ inline int banded_attention_forward<__nv_bfloat16>(const graphop_plan_t* plan, c
   p.o = o; p.lse = (float*)lse; p.node_lo = plan->node_lo; p.node_deg = plan->node_deg; p.n_dst = n_dst; p.H = H;
   p.scale = (float)scale;
   const dim3 grid((unsigned)((n_dst + kTileM - 1) / kTileM), (unsigned)H);
-  attention_forward_kernel<<<grid, kTileM, kSmemBytes, st>>>(mq, mk, mv, p);
+  attention_forward_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
   GK_LAUNCHED("attention_fwd_banded");
+  return GRAPHOP_OK;
+}
+
+// Both gradients' kernels for a dense-band graph; `stat` needs n_dst * H * 8 bytes of workspace.
+template <>
+inline int banded_attention_backward<__nv_bfloat16>(const graphop_plan_t* plan_r, const graphop_plan_t* plan_t,
+                                                    const __nv_bfloat16* q, const __nv_bfloat16* k,
+                                                    const __nv_bfloat16* v, const __nv_bfloat16* o, const void* lse,
+                                                    const __nv_bfloat16* d_o, double scale, __nv_bfloat16* dq,
+                                                    __nv_bfloat16* dk, __nv_bfloat16* dv, long long n_dst,
+                                                    long long n_src, int H, int D, void* ws, size_t wsb,
+                                                    cudaStream_t st) {
+  using namespace banded;
+  if (D != kD || H < 1 || H > 65535 || n_dst < 1 || n_src < 1) return GRAPHOP_ERR_UNSUPPORTED;
+  for (const graphop_plan_t* pl : {plan_r, plan_t})
+    if (!(pl->flags & GRAPHOP_PLAN_DENSE_BAND) || pl->band_span > kSpan || !pl->node_lo || !pl->node_deg)
+      return GRAPHOP_ERR_UNSUPPORTED;
+  if (n_dst > plan_r->n_nodes || n_src > plan_t->n_nodes) return GRAPHOP_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)d_o | (uintptr_t)dq | (uintptr_t)dk |
+       (uintptr_t)dv) & 15)
+    return GRAPHOP_ERR_UNSUPPORTED;
+  GK_TRY(check_ws(ws));
+  if (wsb < (size_t)n_dst * H * sizeof(float2)) return GRAPHOP_ERR_WORKSPACE;
+  CUtensorMap mq, mk, mv, mg;
+  if (!make_map(&mq, q, n_dst, H) || !make_map(&mk, k, n_src, H) || !make_map(&mv, v, n_src, H) ||
+      !make_map(&mg, d_o, n_dst, H))
+    return GRAPHOP_ERR_UNSUPPORTED;
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  GK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+    GK_CUDA(cudaFuncSetAttribute(attention_backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBSmemBytes));
+    GK_CUDA(cudaFuncSetAttribute(attention_backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBSmemBytes));
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
+  }
+  BwdParams p;
+  p.o = o; p.d_o = d_o; p.lse = (const float*)lse; p.stat = (float2*)ws; p.H = H; p.scale = (float)scale;
+  p.out0 = dq; p.out1 = nullptr; p.node_lo = plan_r->node_lo; p.node_deg = plan_r->node_deg; p.n_own = n_dst;
+  p.n_other = n_src;
+  attention_backward_kernel<false><<<dim3((unsigned)((n_dst + kTileM - 1) / kTileM), (unsigned)H), kThreads, kBSmemBytes,
+                                     st>>>(mq, mg, mk, mv, p);
+  GK_LAUNCHED("attention_bwd_dst_banded");
+  p.out0 = dk; p.out1 = dv; p.node_lo = plan_t->node_lo; p.node_deg = plan_t->node_deg; p.n_own = n_src;
+  p.n_other = n_dst;
+  attention_backward_kernel<true><<<dim3((unsigned)((n_src + kTileM - 1) / kTileM), (unsigned)H), kThreads, kBSmemBytes,
+                                    st>>>(mk, mv, mq, mg, p);
+  GK_LAUNCHED("attention_bwd_src_banded");
   return GRAPHOP_OK;
 }
 

@@ -727,6 +727,17 @@ inline int banded_attention_forward(const graphop_plan_t*, const T*, const T*, c
 }
 
 template <typename T>
+int banded_attention_backward(const graphop_plan_t* plan_r, const graphop_plan_t* plan_t, const T* q, const T* k,
+                              const T* v, const T* o, const void* lse, const T* d_o, double scale, T* dq, T* dk, T* dv,
+                              long long n_dst, long long n_src, int H, int D, void* ws, size_t wsb, cudaStream_t st);
+template <typename T>
+inline int banded_attention_backward(const graphop_plan_t*, const graphop_plan_t*, const T*, const T*, const T*,
+                                     const T*, const void*, const T*, double, T*, T*, T*, long long, long long, int, int,
+                                     void*, size_t, cudaStream_t) {
+  return GRAPHOP_ERR_UNSUPPORTED;
+}
+
+template <typename T>
 inline int attention_forward_planned(const graphop_plan_t* plan, const T* q, const T* k, const T* v, double scale,
                                      T* o, void* lse, long long n_dst, long long n_src, int H, int D, void* ws,
                                      size_t wsb, cudaStream_t st) {
@@ -818,6 +829,22 @@ inline int attention_backward(const GS& gs_r, const GS& gs_c, bool has_eid_t, lo
       return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, generic);
     });
   });
+}
+
+template <typename T>
+inline int attention_backward_planned(const graphop_plan_t* plan_r, const graphop_plan_t* plan_t, const T* q,
+                                      const T* k, const T* v, const T* o, const void* lse, const T* dout, double scale,
+                                      T* dq, T* dk, T* dv, long long n_dst, long long n_src, int H, int D, void* ws,
+                                      size_t wsb, cudaStream_t st) {
+  if (!plan_r || !plan_t) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if ((plan_r->flags & plan_t->flags & GRAPHOP_PLAN_DENSE_BAND) && q && k && v && o && lse && dout && dq && dk && dv) {
+    const int rc = banded_attention_backward<T>(plan_r, plan_t, q, k, v, o, lse, dout, scale, dq, dk, dv, n_dst, n_src,
+                                                H, D, ws, wsb, st);
+    if (rc != GRAPHOP_ERR_UNSUPPORTED) return rc;
+  }
+  return attention_backward<T>(FromPlan{plan_r}, FromPlan{plan_t}, plan_t->eid != nullptr, plan_r->n_chunks,
+                               plan_t->n_chunks, q, k, v, o, lse, dout, scale, dq, dk, dv, plan_r->n_edges, n_dst,
+                               n_src, H, D, ws, wsb, st);
 }
 
 }  // namespace gk

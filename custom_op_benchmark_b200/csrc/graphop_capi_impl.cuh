@@ -169,8 +169,7 @@
       const graphop_plan_t* plan_r, const graphop_plan_t* plan_t, const CT* q, const CT* k, const CT* v,             \
       const CT* o, const void* lse, const CT* d_o, double scale, CT* dq, CT* dk, CT* dv, int64_t n_dst,              \
       int64_t n_src, int H, int D, void* ws, size_t wsb, graphop_stream_t stream) {                                  \
-    return gk::attention_backward<T>(GK_PL(plan_r), GK_PL(plan_t), plan_t && plan_t->eid != nullptr, GK_PC(plan_r),  \
-                                     GK_PC(plan_t), (const T*)q, (const T*)k, (const T*)v, (const T*)o, lse,         \
-                                     (const T*)d_o, scale, (T*)dq, (T*)dk, (T*)dv, GK_PE(plan_r), n_dst, n_src, H,   \
-                                     D, ws, wsb, GK_ST);                                                             \
+    return gk::attention_backward_planned<T>(plan_r, plan_t, (const T*)q, (const T*)k, (const T*)v, (const T*)o,     \
+                                             lse, (const T*)d_o, scale, (T*)dq, (T*)dk, (T*)dv, n_dst, n_src, H, D,  \
+                                             ws, wsb, GK_ST);                                                        \
   }

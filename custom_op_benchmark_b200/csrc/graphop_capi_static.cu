@@ -16,7 +16,11 @@
 // The array's name is a host-side handle here, not a device address, so the address the kernels
 // receive comes from cudaGetSymbolAddress.  That lookup happens on the first call made with a
 // given device current, and is remembered per device.  Make that first call outside any stream
-// capture: it is an ordinary synchronous runtime query.
+// capture: it is an ordinary synchronous runtime query.  If this library's module has not been
+// loaded on that device yet (lazy loading), the lookup loads it, and loading it is what places the
+// 32 MiB array in that device's memory: so the first call on a device is the one call that can
+// fail for lack of device memory, and "allocation-free" is a property of every call after it.
+// Call it once with a tiny problem at start-up to have that behind you.
 //
 // All calls on one GPU share the one array.  The kernels write every scratch word before they
 // read it (the owner table, the per-tile carry slots and the slot directory are produced afresh
@@ -25,7 +29,10 @@
 // host threads) would overwrite each other's scratch: run them one after the other.
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "../../include/graphop_b200.h"
+#include "gk_host.cuh"
 
 namespace {
 
@@ -33,18 +40,21 @@ constexpr size_t kStaticScratchBytes = (size_t)GRAPHOP_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_address[kMaxDevices] = {};
+std::atomic<void*> g_scratch_address[kMaxDevices];   // zero-initialised; two threads may both resolve, to the same value
 
-// Device address of the array on the current device, resolved once per device.
+// Device address of the array on the current device, resolved once per device.  A failing runtime call
+// leaves its code where graphop_last_cuda_error() finds it, like every other entry point's.
 int scratch_for_current_device(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return GRAPHOP_ERR_CUDA;
-  if (!g_scratch_address[dev]) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return GRAPHOP_ERR_CUDA;
-    g_scratch_address[dev] = p;
+  GK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return GRAPHOP_ERR_UNSUPPORTED;
+  void* p = g_scratch_address[dev].load(std::memory_order_acquire);
+  if (!p) {
+    GK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (!p) return GRAPHOP_ERR_CUDA;
+    g_scratch_address[dev].store(p, std::memory_order_release);
   }
-  *out = g_scratch_address[dev];
+  *out = p;
   return GRAPHOP_OK;
 }
 

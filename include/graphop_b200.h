@@ -267,7 +267,10 @@ int graphop_plan_build_i64(const int64_t* row, const int64_t* indptr, const int6
  * by every GPU that loads it.  Returns GRAPHOP_ERR_UNSUPPORTED, launching nothing, when
  * graphop_workspace_bytes(GRAPHOP_OP_SPMM_FWD, ...) for the sizes exceeds that.  Calls no cudaMalloc
  * / cudaFree or any allocating routine.  The first call on each device resolves the array's device
- * address (make it before any stream capture).  All calls on a GPU share the array: calls that
+ * address (make it before any stream capture); where the CUDA runtime loads modules lazily that
+ * lookup is also what loads this library's module on the device and so places the array in its
+ * memory - the one moment this entry point can fail for lack of device memory.  Make one small
+ * call at start-up; every later call touches no allocator.  All calls on a GPU share the array: calls that
  * overlap on the device race; stale contents are harmless, every scratch word is rewritten. */
 #define GRAPHOP_STATIC_SCRATCH_BYTES (32u << 20)
 size_t graphop_static_scratch_bytes(void);

@@ -22,7 +22,8 @@ def random_graph(n_dst, n_src, degs, seed, index_dtype=th.int64, dedup=False):
 
 def graph_zoo():
     """(name, Graph) pairs covering: empty rows, one-edge rows, rows spanning many chunks and
-    tiles, a single huge row, rectangular shapes, no edges in the first / last nodes."""
+    tiles, a single huge row, rectangular shapes, no edges in the first / last nodes, node ids
+    larger than the number of edges."""
     g = th.Generator().manual_seed(123)
     zoo = []
     zoo.append(("er64", graphs.er_graph(64, 5, seed=1, index_dtype=th.int64)))
@@ -41,6 +42,10 @@ def graph_zoo():
     zoo.append(("one_huge_row", random_graph(3, 50, [0, 5000, 0], 4)))
     zoo.append(("all_single", random_graph(300, 300, [1] * 300, 5)))
     zoo.append(("rect_wide", random_graph(20, 500, th.randint(0, 90, (20,), generator=g), 6)))
+    # more nodes than edges, and the one long row (several chunks) sits at a node id above the edge count
+    degs = th.zeros(1000, dtype=th.int64)
+    degs[3], degs[400], degs[900], degs[999] = 7, 20, 300, 2
+    zoo.append(("ids_above_edge_count", random_graph(1000, 1000, degs, 7)))
     return zoo
 
 

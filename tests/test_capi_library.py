@@ -1,4 +1,4 @@
-"""The C-ABI shared library loads and exports every symbol include/graphop_b200.h declares.
+"""The C-ABI shared library loads and exports every symbol include/graphop_b200.h and include/graphop_dlpack.h declare.
 No compute call is made here (no GPU needed)."""
 import os
 import re
@@ -19,12 +19,14 @@ def _header_symbols():
     psuf = re.findall(r"^GRAPHOP_DECLARE_PLANNED\((\w+),", text, re.M)
     names += ["%s_%s" % (op, s) for op in pops for s in psuf]
     names += re.findall(r"^(?:int|size_t|long long|const char\*) (graphop_\w+)\(", text, re.M)
+    dl = open(os.path.join(ROOT, "include", "graphop_dlpack.h")).read()
+    names += re.findall(r"^int (graphop_dl_\w+)\(", dl, re.M)
     return sorted(set(names))
 
 
 def test_header_and_binding_agree():
     assert _header_symbols() == sorted(_capi.exported_symbols())
-    assert len(_header_symbols()) == 10 * 6 + 10 * 3 + 12
+    assert len(_header_symbols()) == 10 * 6 + 10 * 3 + 12 + 10
 
 
 def test_product_library_carries_no_benchmark_hooks():

@@ -21,8 +21,8 @@ DEV = "cuda:0"
 def _case(seed, n, h, d):
     g = th.Generator().manual_seed(seed)
     degs = th.randint(0, 40, (n,), generator=g)
-    degs[n // 3] = 900            # a node that spans several tiles: exercises the carry scratch
     degs[th.rand(n, generator=g) < 0.2] = 0
+    degs[n // 3] = 900            # after the zeroing: a node that spans several tiles, so the carry scratch is used
     gr = random_graph(n, n, degs, seed)
     r = [t.to(DEV) for t in chunked(gr, 32, dtype=th.int32)]
     w = th.rand(gr.n_edges, h, generator=g).to(DEV)
@@ -44,6 +44,7 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
     assert lib.graphop_static_scratch_bytes() == 32 << 20
     for seed, n, h, d in ((1, 700, 4, 32), (2, 1500, 2, 64)):
         gr, r, w, x = _case(seed, n, h, d)
+        assert int((gr.indptr[1:] - gr.indptr[:-1]).max()) >= 900
         want = graphop.vector_spmm_forward(*r, w, x)
         rc, got = _static(gr, r, w, x, h, d)
         th.cuda.synchronize()
