@@ -141,6 +141,14 @@ __device__ __forceinline__ void store_out16(__nv_bfloat16* dst, const float (&v)
   }
 }
 
+// 2^x for x <= 0 (a score minus its row maximum, or minus the row's log-sum): one MUFU instruction; results below
+// the normal range flush to zero
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Params {
   __nv_bfloat16* o;          // (n_dst, H, 64)
   float* lse;                // (n_dst, H)
@@ -158,7 +166,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   // the swizzled tiles want a 1024-byte aligned base
   unsigned char* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   const uint32_t s_base = smem_u32(smem);
-  const uint32_t bar_load = s_base + kOffBar, bar_s = bar_load + 8, bar_o = bar_load + 16;
+  const uint32_t bar_load = s_base + kOffBar, bar_s = bar_load + 8, bar_o = bar_load + 16, bar_v = bar_load + 24;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 32);
   int* s_red = reinterpret_cast<int*>(smem + kOffBar + 40);   // 4 ints: per-quarter minima of the first neighbour
   float* s_max = reinterpret_cast<float*>(smem + kOffRed);     // [column group][row]
@@ -185,6 +193,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     mbar_init(bar_load, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
+    mbar_init(bar_v, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -202,13 +211,16 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (kmin != INT_MAX) {  // some node of the tile has neighbours
     if (tid == 0) {
-      mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * (1 + 2 * (kSpan / kKeyBlock))));
+      // queries and keys first: the scores start as soon as they are in; the values land during the softmax
+      mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * (1 + kSpan / kKeyBlock)));
       tma_load_3d(s_base + kOffQ, &map_q, bar_load, 0, head, (int)r0);
 #pragma unroll
-      for (int b = 0; b < kSpan / kKeyBlock; ++b) {
+      for (int b = 0; b < kSpan / kKeyBlock; ++b)
         tma_load_3d(s_base + kOffK + b * kBlockBytes, &map_k, bar_load, 0, head, kmin + b * kKeyBlock);
-        tma_load_3d(s_base + kOffV + b * kBlockBytes, &map_v, bar_load, 0, head, kmin + b * kKeyBlock);
-      }
+      mbar_expect_tx(bar_v, (uint32_t)(kBlockBytes * (kSpan / kKeyBlock)));
+#pragma unroll
+      for (int b = 0; b < kSpan / kKeyBlock; ++b)
+        tma_load_3d(s_base + kOffV + b * kBlockBytes, &map_v, bar_v, 0, head, kmin + b * kKeyBlock);
     }
     ok = __syncthreads_and(mbar_wait(bar_load, 0));   // the same verdict in every thread
     if (ok && tid == 0) {
@@ -269,8 +281,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         float p0 = 0.f, p1 = 0.f;
         if (live) {
           const int col = c * 32 + j;
-          if (col >= jlo && col <= jhi) p0 = exp2f(fmaf(v[j], sl2, -msl2));
-          if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2f(fmaf(v[j + 1], sl2, -msl2));
+          if (col >= jlo && col <= jhi) p0 = exp2_fast(fmaf(v[j], sl2, -msl2));
+          if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2_fast(fmaf(v[j + 1], sl2, -msl2));
         }
         l += p0 + p1;
         packed[j / 2] = pack_bf16(p0, p1);
@@ -288,7 +300,7 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // the probabilities were written through the generic proxy; the tensor core reads through the async proxy
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    ok = __syncthreads_and(ok && mbar_wait(bar_v, 0));   // probabilities written by all, values landed
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     l = 0.f;
 #pragma unroll
@@ -379,7 +391,7 @@ constexpr int kBOffS0 = kBOffD + kBlocks * kBlockBytes;  // staging tile 0 (dS |
 constexpr int kBOffS1 = kBOffS0 + kStageBytes;           // staging tile 1 (dS^T, source side)
 constexpr int kBOffStat = kBOffS1 + kStageBytes;         // (lse, delta) of the band's queries (source side)
 constexpr int kBOffBar = kBOffStat + kSpan * 8;
-constexpr int kBSmemBytes = kBOffBar + 64 + 1024;
+constexpr int kBSmemBytes = kBOffBar + 128 + 1024;
 
 // kSrc = false: destination side (owned = queries); true: source side (owned = keys)
 template <bool kSrc>
@@ -390,10 +402,12 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   extern __shared__ unsigned char raw_smem[];
   unsigned char* smem = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   const uint32_t s_base = smem_u32(smem);
-  const uint32_t bar_load = s_base + kBOffBar, bar_s = bar_load + 8, bar_g = bar_load + 16;
+  // bar_load: the owned tiles and the band's first block; bar_more + 8 (b - 1): the band's block b
+  const uint32_t bar_load = s_base + kBOffBar, bar_s = bar_load + 8, bar_g = bar_load + 16, bar_more = bar_load + 64;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kBOffBar + 32);
   int* s_red = reinterpret_cast<int*>(smem + kBOffBar + 40);
   float2* s_stat = reinterpret_cast<float2*>(smem + kBOffStat);
+  float* s_part = reinterpret_cast<float*>(smem + kBOffStat);   // destination side: [column group][row] parts of delta
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int quarter = warp & 3, cg = warp >> 2;   // tensor-memory lane quarter; which 32 of a block's 128 columns
@@ -414,6 +428,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     mbar_init(bar_load, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_g, 1);
+#pragma unroll
+    for (int b = 1; b < kBlocks; ++b) mbar_init(bar_more + 8 * (b - 1), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -432,37 +448,41 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
   if (bmin != INT_MAX) {
     if (tid == 0) {
-      mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * (2 + 2 * kBlocks)));
+      mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * 4));
       tma_load_3d(s_base + kBOffA, &map_a, bar_load, 0, head, (int)r0);
       tma_load_3d(s_base + kBOffB, &map_b, bar_load, 0, head, (int)r0);
 #pragma unroll
-      for (int b = 0; b < kBlocks; ++b) {
-        tma_load_3d(s_base + kBOffC + b * kBlockBytes, &map_c, bar_load, 0, head, bmin + b * kKeyBlock);
-        tma_load_3d(s_base + kBOffD + b * kBlockBytes, &map_d, bar_load, 0, head, bmin + b * kKeyBlock);
+      for (int b = 0; b < kBlocks; ++b) {   // later blocks land while the first is worked on
+        const uint32_t bar = b == 0 ? bar_load : bar_more + 8 * (b - 1);
+        if (b > 0) mbar_expect_tx(bar, (uint32_t)(kBlockBytes * 2));
+        tma_load_3d(s_base + kBOffC + b * kBlockBytes, &map_c, bar, 0, head, bmin + b * kKeyBlock);
+        tma_load_3d(s_base + kBOffD + b * kBlockBytes, &map_d, bar, 0, head, bmin + b * kKeyBlock);
       }
     }
     // per-row scalars while the tiles travel
-    float lse2 = 0.f, delta = 0.f;
+    float lse2 = 0.f, delta = 0.f, lrow = 0.f;
     const float kL2e = 1.4426950408889634f;
     if constexpr (!kSrc) {
+      // delta = <o, dO> of the row: each of its four threads takes 16 of the 64 features
+      float part = 0.f;
       if (r < p.n_own) {
-        const uint4* orow = reinterpret_cast<const uint4*>(p.o + ((long long)r * p.H + head) * kD);
-        const uint4* grow = reinterpret_cast<const uint4*>(p.d_o + ((long long)r * p.H + head) * kD);
+        const uint4* orow = reinterpret_cast<const uint4*>(p.o + ((long long)r * p.H + head) * kD) + cg * 2;
+        const uint4* grow = reinterpret_cast<const uint4*>(p.d_o + ((long long)r * p.H + head) * kD) + cg * 2;
 #pragma unroll
-        for (int q = 0; q < kD / 8; ++q) {
+        for (int q = 0; q < 2; ++q) {
           const uint4 ov = __ldg(orow + q), gv = __ldg(grow + q);
           const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
           const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 of = __bfloat1622float2(o2[e]), gf = __bfloat1622float2(g2[e]);
-            delta += of.x * gf.x + of.y * gf.y;
+            part += of.x * gf.x + of.y * gf.y;
           }
         }
-        const float l = p.lse[(long long)r * p.H + head];
-        lse2 = l * kL2e;
-        if (cg == 0) p.stat[(long long)r * p.H + head] = make_float2(l, delta);
+        lrow = p.lse[(long long)r * p.H + head];
+        lse2 = lrow * kL2e;
       }
+      s_part[cg * kTileM + row] = part;
     } else {
       // (lse, delta) of the band's queries: column j of the scores is query bmin + j
       for (int i = tid; i < kSpan; i += kThreads) {
@@ -471,6 +491,11 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       }
     }
     ok = __syncthreads_and(mbar_wait(bar_load, 0));
+    if constexpr (!kSrc) {
+#pragma unroll
+      for (int g = 0; g < kColGroups; ++g) delta += s_part[g * kTileM + row];   // the same order in all four threads
+      if (cg == 0 && r < p.n_own) p.stat[(long long)r * p.H + head] = make_float2(lrow, delta);
+    }
 
     const int jlo = deg > 0 ? lo - bmin : 1, jhi = deg > 0 ? lo - bmin + deg - 1 : 0;
     int wlo = deg > 0 ? jlo : INT_MAX, whi = deg > 0 ? jhi : -1;
@@ -518,12 +543,12 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const int col = col0 + j;
             if (col >= jlo && col <= jhi) {
               const float l2 = kSrc ? s_stat[col].x * kL2e : lse2, dl = kSrc ? s_stat[col].y : delta;
-              pa = exp2f(fmaf(sv[j], sl2, -l2));
+              pa = exp2_fast(fmaf(sv[j], sl2, -l2));
               da = pa * (dv[j] - dl) * p.scale;
             }
             if (col + 1 >= jlo && col + 1 <= jhi) {
               const float l2 = kSrc ? s_stat[col + 1].x * kL2e : lse2, dl = kSrc ? s_stat[col + 1].y : delta;
-              pb = exp2f(fmaf(sv[j + 1], sl2, -l2));
+              pb = exp2_fast(fmaf(sv[j + 1], sl2, -l2));
               db = pb * (dv[j + 1] - dl) * p.scale;
             }
             pk0[j / 2] = kSrc ? pack_bf16(pa, pb) : pack_bf16(da, db);
@@ -557,7 +582,9 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         }
         umma_commit(bar_g);
       }
-      ok = __syncthreads_and(ok && mbar_wait(bar_g, b & 1));
+      // the gradient products of this block are done, and the next block of the band has landed
+      ok = __syncthreads_and(ok && mbar_wait(bar_g, b & 1) &&
+                             (b + 1 >= kBlocks || mbar_wait(bar_more + 8 * b, 0)));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
 

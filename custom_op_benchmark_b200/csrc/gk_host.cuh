@@ -831,6 +831,109 @@ inline int attention_backward(const GS& gs_r, const GS& gs_c, bool has_eid_t, lo
   });
 }
 
+// ---------------------------------------------------------------------------------------
+// Attention with an edge term in the scores: s_k = scale * q[n] . (k[other[k]] + rel[k]), rel an (n_edges, D)
+// tensor indexed by row-CSR position and shared by the heads.  It is the reference's node_mul_edge
+// (graphop_kernel.cu:16-34, "designed for relative positional encoding") added to maskedmm's scores before
+// the softmax, computed in the fused pass instead of as two more (n_edges, H) tensors.
+// ---------------------------------------------------------------------------------------
+template <typename T, class GS>
+inline int attention_bias_forward(const GS& gs, long long C, const T* q, const T* k, const T* v, const T* rel,
+                                  double scale, T* o, void* lse, long long E, long long n_dst, long long n_src, int H,
+                                  int D, void* ws, size_t wsb, cudaStream_t st) {
+  using A = typename AccOf<T>::type;
+  GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
+  VecShape s;
+  if (!attention_shape_ok<T>(H, D, aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(rel), &s))
+    return GRAPHOP_ERR_UNSUPPORTED;
+  if (E == 0 || n_dst == 0)   // no edge: the edge term has nothing to add
+    return attention_forward<T>(gs, C, q, k, v, scale, o, lse, E, n_dst, n_src, H, D, ws, wsb, st);
+  if (!q || !k || !v || !rel || !o || !lse || !gs.valid(true)) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  GraphView g;
+  GK_TRY(gs(ar, st, &g));
+  const int HD = H * D, tile0 = pick_tile(E);
+  return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
+    constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+    const long long cstride = HD + 2 * s.S;
+    if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
+    else return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, [&](void* cout, void* cin) {
+      AttnFwdOp<T, V, R, true> op;
+      op.q = q; op.k = k; op.v = v; op.rel = rel; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout;
+      op.carry_in = (const A*)cin; op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+      op.cstride = cstride;
+      return op;
+    });
+  });
+}
+
+// Gradients of the above.  The transposed CSR must carry eid_t (for each of its positions the row-CSR position of
+// the same edge): the destination pass leaves (p, ds) of every edge in the workspace, the source pass aggregates
+// them into dk and dv, and d_rel[j] = sum_h ds[j, h] q[node(j), h] comes from the same pairs.
+template <typename T, class GS>
+inline int attention_bias_backward(const GS& gs_r, const GS& gs_c, bool has_eid_t, long long C, long long Ct,
+                                   const T* q, const T* k, const T* v, const T* rel, const T* o, const void* lse,
+                                   const T* dout, double scale, T* dq, T* dk, T* dv, T* d_rel, long long E,
+                                   long long n_dst, long long n_src, int H, int D, void* ws, size_t wsb,
+                                   cudaStream_t st) {
+  using A = typename AccOf<T>::type;
+  GK_TRY(check_sizes(C, E, n_dst, n_src, H, D));
+  if (Ct < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  VecShape s;
+  const bool al = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(dout) && aligned16(dq) &&
+                  aligned16(dk) && aligned16(dv) && aligned16(rel);
+  if (!attention_shape_ok<T>(H, D, al, &s)) return GRAPHOP_ERR_UNSUPPORTED;
+  if (E == 0)
+    return attention_backward<T>(gs_r, gs_c, has_eid_t, C, Ct, q, k, v, o, lse, dout, scale, dq, dk, dv, E, n_dst,
+                                 n_src, H, D, ws, wsb, st);
+  if (!has_eid_t || !gs_r.valid(true) || !gs_c.valid(true) || !q || !k || !v || !rel || !o || !lse || !dout || !dq ||
+      !dk || !dv || !d_rel)
+    return GRAPHOP_ERR_INVALID_ARGUMENT;
+  GK_TRY(check_ws(ws));
+  Arena ar(ws, wsb);
+  const int HD = H * D, tile0 = pick_tile(E), Hp = stat_heads(H, (int)sizeof(A));
+  StatPair<A>* stat = (StatPair<A>*)ar.take((size_t)n_dst * Hp * sizeof(StatPair<A>));
+  EdgePair<A>* pd = (EdgePair<A>*)ar.take((size_t)E * Hp * sizeof(EdgePair<A>));
+  const size_t mark = ar.used;
+  {
+    GraphView g;
+    GK_TRY(gs_r(ar, st, &g));
+    GK_TRY((dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
+      constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+      if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
+      else return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, [&](void* cout, void* cin) {
+        AttnBwdDstOp<T, V, R, true> op;
+        op.q = q; op.k = k; op.v = v; op.rel = rel; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.stat = stat;
+        op.pairs = pd; op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+        op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+        return op;
+      });
+    })));
+    const long long total = E * D;
+    const unsigned grid = (unsigned)((total + 255) / 256 < (1 << 16) ? (total + 255) / 256 : (1 << 16));
+    bias_grad_kernel<T><<<grid ? grid : 1, 256, 0, st>>>(g.erow, pd, q, d_rel, E, H, Hp, D);
+    GK_LAUNCHED("attention_bias_grad");
+  }
+  ar.used = mark;
+  GraphView g;
+  GK_TRY(gs_c(ar, st, &g));
+  return dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
+    constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
+    if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
+    else return dispatch_lph(D / V, [&](auto Lc) -> int {
+      constexpr int LPH = decltype(Lc)::value;
+      return run_row_levels(ar, g, tile0, n_src, sizeof(A), 2 * HD, st, [&](void* cout, void* cin) {
+        AttnBwdSrcPairsStaged<T, V, R, LPH> op;
+        op.q = q; op.k = k; op.v = v; op.dout = dout; op.stat = stat; op.pd = pd; op.dk = dk;
+        op.dv = dv; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
+        op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+        return op;
+      });
+    });
+  });
+}
+
 template <typename T>
 inline int attention_backward_planned(const graphop_plan_t* plan_r, const graphop_plan_t* plan_t, const T* q,
                                       const T* k, const T* v, const T* o, const void* lse, const T* dout, double scale,

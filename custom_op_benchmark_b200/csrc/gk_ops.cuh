@@ -263,10 +263,13 @@ edge_mix_heads_kernel(const int32_t* __restrict__ erow, const int32_t* __restric
 // Streaming softmax: running maximum m, running sum l and the running weighted sum are
 // rescaled whenever the maximum grows; partials of split nodes merge with the same rule.
 // ---------------------------------------------------------------------------------------
-template <typename T, int V, int R>
+// kBias: the score of an edge is scale * q . (k[other] + rel[edge]), rel an (n_edges, D) tensor shared by the
+// heads - the node_mul_edge term (graphop_kernel.cu:16-34, "relative positional encoding") folded into the scores.
+template <typename T, int V, int R, bool kBias = false>
 struct AttnFwdOp {
   using A = typename AccOf<T>::type;
-  static constexpr const char* kName = "attention_fwd";
+  static constexpr const char* kName = kBias ? "attention_bias_fwd" : "attention_fwd";
+  const T* __restrict__ rel = nullptr;   // (n_edges, D), kBias only
   static constexpr bool kRowOut = true;
   static constexpr int kUnroll = (R * V * (int)sizeof(A) <= 16) ? 4 : 2;
   const T* __restrict__ q;   // (n_dst, H, D)
@@ -295,12 +298,18 @@ struct AttnFwdOp {
       if (st.sm.ok[i]) load_acc<T, V>(st.q[i], q + (long long)node * HD + st.sm.feat[i]);
     }
   }
-  __device__ __forceinline__ void fetch(const State& st, Fetched& f, int c, int, int) const {
+  __device__ __forceinline__ void fetch(const State& st, Fetched& f, int c, int edge, int) const {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       if (st.sm.ok[i]) {
         load_acc<T, V>(f.k[i], k + (long long)c * HD + st.sm.feat[i]);
         load_acc<T, V>(f.v[i], v + (long long)c * HD + st.sm.feat[i]);
+        if constexpr (kBias) {
+          A b[V];
+          load_acc<T, V>(b, rel + (long long)edge * D + st.sm.efeat[i]);
+#pragma unroll
+          for (int e = 0; e < V; ++e) f.k[i][e] += b[e];
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < V; ++e) { f.k[i][e] = A(0); f.v[i][e] = A(0); }
@@ -427,10 +436,14 @@ template <typename A> struct alignas(2 * sizeof(A)) EdgePair { A p, ds; };
 __host__ __device__ constexpr int stat_heads(int H, int acc_bytes) { return acc_bytes >= 8 ? H : ((H + 1) & ~1); }
 
 // ---------------------------------------------------------------------------------------
-template <typename T, int V, int R>
+// kBias: scores with the edge term (see AttnFwdOp); dq then sums ds * (k + rel), and (p, ds) of every edge
+// are left in `pairs` for the source pass and for the gradient of rel.
+template <typename T, int V, int R, bool kBias = false>
 struct AttnBwdDstOp {
   using A = typename AccOf<T>::type;
-  static constexpr const char* kName = "attention_bwd_dst";
+  static constexpr const char* kName = kBias ? "attention_bias_bwd_dst" : "attention_bwd_dst";
+  const T* __restrict__ rel = nullptr;          // (n_edges, D), kBias only
+  EdgePair<A>* __restrict__ pairs = nullptr;    // (n_edges, Hp) out, kBias only
   static constexpr bool kRowOut = true;
   static constexpr int kUnroll = (R * V * (int)sizeof(A) <= 16) ? 4 : 2;
   const T* __restrict__ q;
@@ -447,7 +460,7 @@ struct AttnBwdDstOp {
   int H, Hp, D, HD, S, lph;
 
   struct State { SlotMap<R> sm; A q[R][V]; A g[R][V]; A acc[R][V]; A lse[R]; A delta[R]; };
-  struct Fetched { A k[R][V]; A v[R][V]; };
+  struct Fetched { A k[R][V]; A v[R][V]; int edge; };
   struct CarryIn { A x[R][V]; };
 
   __device__ __forceinline__ void setup(State& st, int lane) const { st.sm.init(lane, S, V, D, 0); }
@@ -482,12 +495,19 @@ struct AttnBwdDstOp {
       if (st.sm.ok[i] && st.sm.efeat[i] == 0) stat[(long long)node * Hp + st.sm.head[i]] = StatPair<A>{st.lse[i], dl[i]};
     }
   }
-  __device__ __forceinline__ void fetch(const State& st, Fetched& f, int c, int, int) const {
+  __device__ __forceinline__ void fetch(const State& st, Fetched& f, int c, int edge, int) const {
+    f.edge = edge;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       if (st.sm.ok[i]) {
         load_acc<T, V>(f.k[i], k + (long long)c * HD + st.sm.feat[i]);
         load_acc<T, V>(f.v[i], v + (long long)c * HD + st.sm.feat[i]);
+        if constexpr (kBias) {
+          A b[V];
+          load_acc<T, V>(b, rel + (long long)edge * D + st.sm.efeat[i]);
+#pragma unroll
+          for (int e = 0; e < V; ++e) f.k[i][e] += b[e];
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < V; ++e) { f.k[i][e] = A(0); f.v[i][e] = A(0); }
@@ -511,6 +531,9 @@ struct AttnBwdDstOp {
       const A ds = p * (dp[i] - st.delta[i]) * scale;
 #pragma unroll
       for (int e = 0; e < V; ++e) st.acc[i][e] += ds * f.k[i][e];
+      if constexpr (kBias) {
+        if (st.sm.ok[i] && st.sm.efeat[i] == 0) pairs[(long long)f.edge * Hp + st.sm.head[i]] = EdgePair<A>{p, ds};
+      }
     }
   }
   __device__ __forceinline__ void store_row(const State& st, int node, int) const {
@@ -703,5 +726,26 @@ struct AttnBwdSrcOp {
     }
   }
 };
+
+// Gradient of the edge term of the biased attention:  d_rel[j, :] = sum_h ds[j, h] * q[node(j), h, :]
+// (the dB half of node_mul_edge backward, graphop_kernel.cu:79-93, with the score gradients the destination
+// pass left in `pairs`).  One thread per (position, feature); positions no chunk covers get 0.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_grad_kernel(const int32_t* __restrict__ erow, const EdgePair<typename AccOf<T>::type>* __restrict__ pairs,
+                 const T* __restrict__ q, T* __restrict__ d_rel, long long E, int H, int Hp, int D) {
+  using A = typename AccOf<T>::type;
+  const long long stride = (long long)gridDim.x * blockDim.x, total = E * D;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long j = i / D;
+    const int d = (int)(i - j * D);
+    const int r = erow[j];
+    A sum = A(0);
+    if (r >= 0) {
+      for (int h = 0; h < H; ++h) sum += pairs[j * Hp + h].ds * to_acc<T>(q[((long long)r * H + h) * D + d]);
+    }
+    d_rel[i] = from_acc<T>(sum);
+  }
+}
 
 }  // namespace gk

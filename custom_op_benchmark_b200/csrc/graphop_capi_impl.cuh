@@ -1,5 +1,5 @@
 // Expands to the extern "C" entry points of one element type (see include/graphop_b200.h): the chunk-table
-// forms GRAPHOP_DEFINE_OPS / GRAPHOP_DEFINE_ATTENTION per index type, and the plan forms
+// forms GRAPHOP_DEFINE_OPS / GRAPHOP_DEFINE_ATTENTION / GRAPHOP_DEFINE_ATTENTION_BIAS per index type, and the plan forms
 // GRAPHOP_DEFINE_PLANNED_OPS / GRAPHOP_DEFINE_PLANNED_ATTENTION once per element type.
 #pragma once
 #include "gk_host.cuh"
@@ -93,6 +93,28 @@
                                      eid_t != nullptr, n_chunks, n_chunks_t, (const T*)q, (const T*)k, (const T*)v,  \
                                      (const T*)o, lse, (const T*)d_o, scale, (T*)dq, (T*)dk, (T*)dv, n_edges, n_dst, \
                                      n_src, H, D, ws, wsb, GK_ST);                                                   \
+  }
+
+#define GRAPHOP_DEFINE_ATTENTION_BIAS(SUF, CT, T, I)                                                                 \
+  extern "C" int graphop_attention_bias_forward_##SUF(                                                               \
+      const I* row, const I* indptr, const I* indices, int64_t n_chunks, const CT* q, const CT* k, const CT* v,      \
+      const CT* rel, double scale, CT* o, void* lse, int64_t n_edges, int64_t n_dst, int64_t n_src, int H, int D,    \
+      void* ws, size_t wsb, graphop_stream_t stream) {                                                               \
+    return gk::attention_bias_forward<T>(GK_CH(I, row, indptr, (const I*)nullptr, indices, n_chunks, n_edges),       \
+                                         n_chunks, (const T*)q, (const T*)k, (const T*)v, (const T*)rel, scale,      \
+                                         (T*)o, lse, n_edges, n_dst, n_src, H, D, ws, wsb, GK_ST);                   \
+  }                                                                                                                  \
+  extern "C" int graphop_attention_bias_backward_##SUF(                                                              \
+      const I* row, const I* indptr, const I* indices, int64_t n_chunks, const I* col, const I* indptr_t,            \
+      const I* eid_t, const I* indices_t, int64_t n_chunks_t, const CT* q, const CT* k, const CT* v, const CT* rel,  \
+      const CT* o, const void* lse, const CT* d_o, double scale, CT* dq, CT* dk, CT* dv, CT* d_rel,                  \
+      int64_t n_edges, int64_t n_dst, int64_t n_src, int H, int D, void* ws, size_t wsb, graphop_stream_t stream) {  \
+    return gk::attention_bias_backward<T>(GK_CH(I, row, indptr, (const I*)nullptr, indices, n_chunks, n_edges),      \
+                                          GK_CH(I, col, indptr_t, eid_t, indices_t, n_chunks_t, n_edges),            \
+                                          eid_t != nullptr, n_chunks, n_chunks_t, (const T*)q, (const T*)k,          \
+                                          (const T*)v, (const T*)rel, (const T*)o, lse, (const T*)d_o, scale,        \
+                                          (T*)dq, (T*)dk, (T*)dv, (T*)d_rel, n_edges, n_dst, n_src, H, D, ws, wsb,   \
+                                          GK_ST);                                                                    \
   }
 
 // The same operations on plans (graphop_plan_build_*): the owner table and the 32-bit index copies come from the
