@@ -34,6 +34,9 @@ SIGNATURES = {
     "attention_forward": [_P] * 3 + [_I64] + [_P] * 3 + [_DBL] + [_P] * 2 + [_I64] * 3 + [_INT] * 2 + _TAIL,
     "attention_backward": [_P] * 3 + [_I64] + [_P] * 4 + [_I64] + [_P] * 6 + [_DBL] + [_P] * 3 + [_I64] * 3
                           + [_INT] * 2 + _TAIL,
+    "attention_bias_forward": [_P] * 3 + [_I64] + [_P] * 4 + [_DBL] + [_P] * 2 + [_I64] * 3 + [_INT] * 2 + _TAIL,
+    "attention_bias_backward": [_P] * 3 + [_I64] + [_P] * 4 + [_I64] + [_P] * 7 + [_DBL] + [_P] * 4 + [_I64] * 3
+                               + [_INT] * 2 + _TAIL,
 }
 
 class Plan(ctypes.Structure):

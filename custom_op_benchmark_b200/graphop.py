@@ -319,6 +319,48 @@ def attention_backward(row, indptr, indices, col, indptr_t, indices_t, q, k, v, 
     return [dq, dk, dv]
 
 
+def attention_bias_forward(row, indptr, indices, q, k, v, rel, scale):
+    """attention_forward with an edge term in the scores: s = scale * q[n].(k[indices[j]] + rel[j]), rel an (e, d)
+    tensor indexed by row-CSR position and shared by the heads - the reference's node_mul_edge ("designed for
+    relative positional encoding", graphop_kernel.cu:16-34) added to maskedmm's scores inside the fused pass."""
+    _check_all(row=row, indptr=indptr, indices=indices, q=q, k=k, v=v, rel=rel)
+    elem, index = _elem(q, k, v, rel), _index(row, indptr, indices)
+    h, d = _heads(q, True)
+    e, c = indices.size(0), _chunks(row, indptr)
+    if rel.dim() != 2 or rel.size(0) != e or rel.size(1) != d:
+        raise RuntimeError("rel must be (e, d)")
+    o = th.empty_like(q)
+    lse = th.empty((q.size(0), h), dtype=_lse_dtype(q), device=q.device)
+    if e == 0:
+        return o.zero_(), lse.fill_(float("-inf"))
+    with th.cuda.device(q.device):
+        _call("attention_bias_forward", elem, index, _capi.OP_ATTENTION_FWD, e, max(q.size(0), k.size(0)), h, d,
+              q.device, [_p(row), _p(indptr), _p(indices), c, _p(q), _p(k), _p(v), _p(rel), float(scale), _p(o),
+                         _p(lse), e, q.size(0), k.size(0), h, d])
+    return o, lse
+
+
+def attention_bias_backward(row, indptr, indices, col, indptr_t, eid_t, indices_t, q, k, v, rel, o, lse, d_o, scale):
+    """[dq, dk, dv, d_rel] of attention_bias_forward.  eid_t: for every position of the transposed CSR the position
+    of the same edge in the row CSR (required: the row pass hands (p, ds) of every edge to the other passes)."""
+    d_o = d_o.contiguous()
+    _check_all(row=row, indptr=indptr, indices=indices, col=col, indptr_t=indptr_t, eid_t=eid_t, indices_t=indices_t,
+               q=q, k=k, v=v, rel=rel, o=o, lse=lse, d_o=d_o)
+    elem = _elem(q, k, v, rel, o, d_o)
+    index = _index(row, indptr, indices, col, indptr_t, indices_t, eid_t)
+    h, d = _heads(q, True)
+    e, c, ct = indices.size(0), _chunks(row, indptr), _chunks(col, indptr_t)
+    dq, dk, dv, d_rel = th.empty_like(q), th.empty_like(k), th.empty_like(v), th.empty_like(rel)
+    if e == 0:
+        return [dq.zero_(), dk.zero_(), dv.zero_(), d_rel]
+    with th.cuda.device(q.device):
+        _call("attention_bias_backward", elem, index, _capi.OP_ATTENTION_BWD_PAIRS, e, max(q.size(0), k.size(0)), h,
+              d, q.device, [_p(row), _p(indptr), _p(indices), c, _p(col), _p(indptr_t), _p(eid_t), _p(indices_t), ct,
+                            _p(q), _p(k), _p(v), _p(rel), _p(o), _p(lse), _p(d_o), float(scale), _p(dq), _p(dk),
+                            _p(dv), _p(d_rel), e, q.size(0), k.size(0), h, d])
+    return [dq, dk, dv, d_rel]
+
+
 def gather_rows(table, idx, out=None):
     """out[r] = table[idx[r]] (rows of a contiguous CUDA tensor, int32 or int64 row ids; 16-byte multiples go
     through the library's copy kernel, anything else through torch)."""

@@ -8,7 +8,7 @@ from torch.autograd import Function
 from . import graphop as _g
 from .part_csr import partition_csr  # noqa: F401  (the reference wrapper re-exports it, wrapper.py:4)
 
-__all__ = ["SparseSoftmax", "MaskedMMCSR", "NodeMulEdge", "VectorSPMM", "GraphAttention", "GraphAttentionPlanned",
+__all__ = ["SparseSoftmax", "MaskedMMCSR", "NodeMulEdge", "VectorSPMM", "GraphAttention", "GraphAttentionBias", "GraphAttentionPlanned",
            "graph_attention", "partition_csr", "chunk_size"]
 
 chunk_size = 32  # wrapper.py:6
@@ -99,6 +99,30 @@ class GraphAttention(Function):
         dq, dk, dv = _g.attention_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse, d_o,
                                            ctx.scale, eid_t=ctx.eid_t)
         return None, None, None, None, None, None, dq, dk, dv, None, None
+
+
+class GraphAttentionBias(Function):
+    """The attention layer with a relative-position term, fused:
+    O = VectorSPMM(SparseSoftmax(scale * (MaskedMMCSR(Q, K) + NodeMulEdge(Q, rel))), V), the chain the reference's
+    ops compose (wrapper.py:20-55) without the (e, h) score tensors.
+
+    ``apply(row, indptr, indices, col, indptr_t, eid_t, indices_t, Q, K, V, rel, scale)``; ``rel`` is (e, d), one row
+    per edge in row-CSR order, shared by the heads; ``eid_t`` gives for every position of the transposed CSR the
+    row-CSR position of the same edge."""
+
+    @staticmethod
+    def forward(ctx, row, indptr, indices, col, indptr_t, eid_t, indices_t, Q, K, V, rel, scale):
+        o, lse = _g.attention_bias_forward(row, indptr, indices, Q, K, V, rel, scale)
+        ctx.save_for_backward(row, indptr, indices, col, indptr_t, eid_t, indices_t, Q, K, V, rel, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        row, indptr, indices, col, indptr_t, eid_t, indices_t, Q, K, V, rel, o, lse = ctx.saved_tensors
+        dq, dk, dv, d_rel = _g.attention_bias_backward(row, indptr, indices, col, indptr_t, eid_t, indices_t, Q, K, V,
+                                                       rel, o, lse, d_o, ctx.scale)
+        return None, None, None, None, None, None, None, dq, dk, dv, d_rel, None
 
 
 class GraphAttentionPlanned(Function):

@@ -258,7 +258,27 @@ int graphop_plan_build_i64(const int64_t* row, const int64_t* indptr, const int6
                                        const T* q, const T* k, const T* v, const T* o, const void* lse,             \
                                        const T* d_o, double scale, T* dq, T* dk, T* dv, int64_t n_edges,            \
                                        int64_t n_dst, int64_t n_src, int H, int D, void* workspace,                 \
-                                       size_t workspace_bytes, graphop_stream_t stream);
+                                       size_t workspace_bytes, graphop_stream_t stream);                            \
+  /* The fused chain with an edge term in the scores: s_k = scale * q[n] . (k[indices[k]] + rel[k]), rel an         \
+   * (n_edges, D) tensor indexed by row-CSR position and shared by the heads.  This is the layer the reference      \
+   * builds from maskedmm + node_mul_edge ("designed for relative positional encoding", graphop_kernel.cu:16-34,     \
+   * 40-55) -> softmax -> vector_spmm, without the two (n_edges, H) score tensors.  Workspace:                      \
+   * GRAPHOP_OP_ATTENTION_FWD.  Same shape limits as graphop_attention_forward. */                                   \
+  int graphop_attention_bias_forward_##SUF(const I* row, const I* indptr, const I* indices, int64_t n_chunks,       \
+                                           const T* q, const T* k, const T* v, const T* rel, double scale, T* o,    \
+                                           void* lse, int64_t n_edges, int64_t n_dst, int64_t n_src, int H, int D,  \
+                                           void* workspace, size_t workspace_bytes, graphop_stream_t stream);       \
+  /* Its gradients: dq = sum ds (k + rel), dk, dv as in graphop_attention_backward, and                             \
+   * d_rel[k, :] = sum_h ds[k, h] q[n, h, :] (node_mul_edge's dB, graphop_kernel.cu:79-93).  eid_t is required      \
+   * here (for every position of the transposed CSR the row-CSR position of the same edge): the row pass leaves     \
+   * (p, ds) of every edge in the workspace for the other two.  Workspace: GRAPHOP_OP_ATTENTION_BWD_PAIRS. */       \
+  int graphop_attention_bias_backward_##SUF(const I* row, const I* indptr, const I* indices, int64_t n_chunks,      \
+                                            const I* col, const I* indptr_t, const I* eid_t, const I* indices_t,    \
+                                            int64_t n_chunks_t, const T* q, const T* k, const T* v, const T* rel,   \
+                                            const T* o, const void* lse, const T* d_o, double scale, T* dq, T* dk,  \
+                                            T* dv, T* d_rel, int64_t n_edges, int64_t n_dst, int64_t n_src, int H,  \
+                                            int D, void* workspace, size_t workspace_bytes,                         \
+                                            graphop_stream_t stream);
 
 /* Scratch-free variant of graphop_vector_spmm_forward_f32_i32 for callers that cannot allocate
  * device memory (a plugin living inside another program's memory plan, a loop that must not take

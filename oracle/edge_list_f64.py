@@ -26,14 +26,22 @@ def _chunks(n, chunk):
         yield lo, min(n, lo + chunk)
 
 
-def _scores(Q, K, d, s, scale):
-    return (Q.index_select(0, d).to(F64) * K.index_select(0, s).to(F64)).sum(-1) * scale
+def _edge_scores(Q, K, d, s, scale, rel=None):
+    k = K.index_select(0, s).to(F64)
+    if rel is not None:              # the node_mul_edge term (graphop_kernel.cu:23-31): one row per edge, all heads
+        k = k + rel.to(F64).unsqueeze(1)
+    return (Q.index_select(0, d).to(F64) * k).sum(-1) * scale
 
 
-def attention_f64(indptr, indices, Q, K, V, scale, dO=None, chunk=1 << 20):
+def attention_f64(indptr, indices, Q, K, V, scale, dO=None, chunk=1 << 20, rel=None):
     """softmax(scale * Q K^T on the edges) V per destination, and its gradients when dO is given.
-    Returns (o, lse) or (o, lse, dq, dk, dv), all float64 on Q's device."""
+    rel (E, D), optional: the scores become scale * Q . (K + rel[edge]) - maskedmm plus node_mul_edge.
+    Returns (o, lse) or (o, lse, dq, dk, dv) (+ d_rel when rel is given), all float64 on Q's device."""
     dev = Q.device
+
+    def _scores(Q, K, d, s, scale, lo=0, hi=0):   # with the edge term of this chunk, when there is one
+        return _edge_scores(Q, K, d, s, scale, None if rel is None else rel[lo:hi])
+
     n_dst, (h, dd) = Q.shape[0], Q.shape[1:]
     dst = dst_of_edges(indptr.to(dev))
     src = indices.to(dev, th.int64)
@@ -41,17 +49,17 @@ def attention_f64(indptr, indices, Q, K, V, scale, dO=None, chunk=1 << 20):
     m = th.full((n_dst, h), -float("inf"), dtype=F64, device=dev)
     for lo, hi in _chunks(e, chunk):
         d, s = dst[lo:hi], src[lo:hi]
-        m.scatter_reduce_(0, d.view(-1, 1).expand(-1, h), _scores(Q, K, d, s, scale), reduce="amax")
+        m.scatter_reduce_(0, d.view(-1, 1).expand(-1, h), _scores(Q, K, d, s, scale, lo, hi), reduce="amax")
     l = th.zeros(n_dst, h, dtype=F64, device=dev)
     for lo, hi in _chunks(e, chunk):
         d, s = dst[lo:hi], src[lo:hi]
-        l.index_add_(0, d, th.exp(_scores(Q, K, d, s, scale) - m.index_select(0, d)))
+        l.index_add_(0, d, th.exp(_scores(Q, K, d, s, scale, lo, hi) - m.index_select(0, d)))
     lse = m + th.log(l)          # nodes without edges: -inf + log 0 = -inf
     lse_safe = th.where(th.isfinite(lse), lse, th.zeros_like(lse))
     o = th.zeros(n_dst, h, dd, dtype=F64, device=dev)
     for lo, hi in _chunks(e, chunk):
         d, s = dst[lo:hi], src[lo:hi]
-        p = th.exp(_scores(Q, K, d, s, scale) - lse_safe.index_select(0, d))
+        p = th.exp(_scores(Q, K, d, s, scale, lo, hi) - lse_safe.index_select(0, d))
         o.index_add_(0, d, p.unsqueeze(-1) * V.index_select(0, s).to(F64))
     if dO is None:
         return o, lse
@@ -59,15 +67,23 @@ def attention_f64(indptr, indices, Q, K, V, scale, dO=None, chunk=1 << 20):
     dq = th.zeros_like(o)
     dk = th.zeros(K.shape, dtype=F64, device=dev)
     dv = th.zeros(V.shape, dtype=F64, device=dev)
+    d_rel = None if rel is None else th.zeros(rel.shape, dtype=F64, device=dev)
     for lo, hi in _chunks(e, chunk):
         d, s = dst[lo:hi], src[lo:hi]
-        p = th.exp(_scores(Q, K, d, s, scale) - lse_safe.index_select(0, d))
+        p = th.exp(_scores(Q, K, d, s, scale, lo, hi) - lse_safe.index_select(0, d))
         g = dO.index_select(0, d).to(F64)
         dp = (g * V.index_select(0, s).to(F64)).sum(-1)
         ds = p * (dp - delta.index_select(0, d)) * scale
-        dq.index_add_(0, d, ds.unsqueeze(-1) * K.index_select(0, s).to(F64))
-        dk.index_add_(0, s, ds.unsqueeze(-1) * Q.index_select(0, d).to(F64))
+        kk = K.index_select(0, s).to(F64)
+        qq = Q.index_select(0, d).to(F64)
+        if rel is not None:
+            kk = kk + rel[lo:hi].to(F64).unsqueeze(1)
+            d_rel[lo:hi] = (ds.unsqueeze(-1) * qq).sum(1)     # node_mul_edge's dB (graphop_kernel.cu:79-93)
+        dq.index_add_(0, d, ds.unsqueeze(-1) * kk)
+        dk.index_add_(0, s, ds.unsqueeze(-1) * qq)
         dv.index_add_(0, s, p.unsqueeze(-1) * g)
+    if rel is not None:
+        return o, lse, dq, dk, dv, d_rel
     return o, lse, dq, dk, dv
 
 
@@ -81,7 +97,7 @@ def sddmm_softmax_f64(indptr, indices, Q, K, dP=None, chunk=1 << 20):
     e = src.numel()
     s = th.empty(e, h, dtype=F64, device=dev)
     for lo, hi in _chunks(e, chunk):
-        s[lo:hi] = _scores(Q, K, dst[lo:hi], src[lo:hi], 1.0)
+        s[lo:hi] = _edge_scores(Q, K, dst[lo:hi], src[lo:hi], 1.0)
     m = th.full((n_dst, h), -float("inf"), dtype=F64, device=dev)
     m.scatter_reduce_(0, dst.view(-1, 1).expand(-1, h), s, reduce="amax")
     ex = th.exp(s - m.index_select(0, dst))
