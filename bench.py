@@ -44,7 +44,13 @@ WORKLOADS = {
     "er_small_attention": dict(kind="er", n=4096, k=15, heads=8, dim=64, dtype="f32", ops="attention"),
     "banded_attention": dict(kind="banded", batch=4, length=8192, window=128, heads=8, dim=64, dtype="bf16",
                              ops="attention"),
+    # the same banded layer as ONE graph cut by rows over the ranks, K / V halo rows exchanged every step (strong scaling)
+    "banded_halo_attention": dict(kind="banded", batch=4, length=8192, window=128, heads=8, dim=64, dtype="bf16",
+                                  ops="halo_attention"),
     "zipf_attention": dict(kind="zipf", n=1_000_000, total=50_000_000, heads=2, dim=64, dtype="f32", ops="attention"),
+    # the fused chain with the node_mul_edge term in the scores (relative-position attention), forward + backward
+    "rmat21_attention_bias": dict(kind="rmat", scale=21, edge_factor=16, heads=4, dim=32, dtype="f32",
+                                  ops="attention_bias"),
     # node_mul_edge + vector_spmm, forward + backward, softmax-normalised edge weights (GAT style)
     "rmat21_gat": dict(kind="rmat", scale=21, edge_factor=16, heads=4, dim=32, dtype="f32", ops="gat"),
     # maskedmm + sparse_softmax, forward + backward, inputs scaled by 3 (max-subtraction stress)
@@ -315,6 +321,68 @@ class AttentionWorkload(Workload):
             out = wrapper.GraphAttentionPlanned.apply(self.plan_r, self.plan_t, q, k, v, self.scale)
         else:
             out = wrapper.GraphAttention.apply(R[0], R[1], R[3], C[0], C[1], C[3], q, k, v, self.scale, C[2])
+        out.backward(stage[3])
+        return [out.detach(), q.grad, k.grad, v.grad]
+
+
+class AttentionBiasWorkload(AttentionWorkload):
+    name = "fused attention with an edge term in the scores, forward + backward"
+    resident = "graph structure and the (edges, dim) edge-term tensor rel; e2e copies Q, K, V, dO in and O, dQ, dK, " \
+               "dV out every step (d_rel stays on the device)"
+
+    def __init__(self, spec, rank, dev):
+        super().__init__(spec, rank, dev)
+        gen = th.Generator(device=dev).manual_seed(2000 + rank)
+        self.rel = (th.randn(self.e, self.d, generator=gen, device=dev) * 0.5).to(self.dtype)
+        z = self.sizes()
+        pairs = self.e * self.h * 8
+        self.alg = {
+            "attention_bias_fwd": self.alg["attention_fwd"] + z["Be"],
+            # as attention_bwd_dst, plus rel read and (p, ds) of every edge written
+            "attention_bias_bwd_dst": self.alg["attention_bwd_dst"] + z["Be"] + pairs,
+            # owner of every position and the pairs read, q read, d_rel written
+            "attention_bias_grad": z["P"] + pairs + z["F_dst"] + z["Be"],
+            # q, dO read, dk, dv written, transposed indices and edge ids, the pairs read
+            "attention_bwd_src_pairs": 2 * z["F_dst"] + 2 * z["F_src"] + z["I_t"] + z["P"] + pairs,
+        }
+        self.alg_step += 3 * z["Be"]        # rel read by both passes, d_rel written
+        self.planned = False                 # the edge-term entry points take chunk tables
+
+    def gather_streams(self):
+        return {"attention_bias_fwd": (self.R[3], self.K, self.V), "attention_bias_bwd_dst": (self.R[3], self.K, self.V)}
+
+    def forward(self):
+        from custom_op_benchmark_b200 import graphop
+        R = self.R
+        self.o, self.lse = graphop.attention_bias_forward(R[0], R[1], R[3], self.Q, self.K, self.V, self.rel,
+                                                          self.scale)
+
+    def backward(self):
+        from custom_op_benchmark_b200 import graphop
+        R, C = self.R, self.C
+        return graphop.attention_bias_backward(R[0], R[1], R[3], C[0], C[1], C[2], C[3], self.Q, self.K, self.V,
+                                               self.rel, self.o, self.lse, self.dO, self.scale)
+
+    def max_err(self):
+        from oracle import edge_list_f64 as ref
+        self.forward()
+        got = [self.o, self.lse] + list(self.backward())
+        want = ref.attention_f64(self.g.indptr, self.g.indices, self.Q, self.K, self.V, self.scale, self.dO,
+                                 rel=self.rel)
+        out = {}
+        for name, a, b in zip(("o", "lse", "dq", "dk", "dv", "d_rel"), got, want):
+            keep = th.isfinite(b)
+            out[name] = ref.max_err(a[keep], b[keep])[0]
+        return dict(out, max_err=max(out.values()),
+                    what="every element of O, lse, dQ, dK, dV, d_rel of one step against the float64 edge-list "
+                         "reference on the same inputs, |x - ref| / (1 + |ref|)")
+
+    def e2e_compute(self, stage):
+        from custom_op_benchmark_b200 import wrapper
+        R, C = self.R, self.C
+        q, k, v = (t.detach().requires_grad_(True) for t in stage[:3])
+        rel = self.rel.detach().requires_grad_(True)
+        out = wrapper.GraphAttentionBias.apply(R[0], R[1], R[3], C[0], C[1], C[2], C[3], q, k, v, rel, self.scale)
         out.backward(stage[3])
         return [out.detach(), q.grad, k.grad, v.grad]
 
@@ -608,8 +676,101 @@ class ShardedSpmmWorkload:
         return out
 
 
-WORKLOAD_CLASSES = {"attention": AttentionWorkload, "gat": GatWorkload, "sddmm_softmax": SddmmSoftmaxWorkload,
-                    "sharded_spmm": ShardedSpmmWorkload}
+class HaloAttentionWorkload:
+    """Fused attention forward + backward over ONE banded graph cut by rows over the ranks (halo.py): every step
+    exchanges the K / V halo rows forward and the dK / dV halo rows backward."""
+    name = "fused attention forward + backward, one banded graph cut by rows over the ranks, K / V halo exchanged"
+    resident = "graph shard and its plans; e2e copies this rank's Q, K, V, dO rows in and O, dQ, dK, dV rows out"
+    scaling = "strong"
+
+    def __init__(self, spec, rank, dev, world):
+        from custom_op_benchmark_b200 import halo
+        self.spec, self.dev, self.world, self.rank = spec, dev, world, rank
+        self.h, self.d, self.dtype = spec["heads"], spec["dim"], DTYPES[spec["dtype"]]
+        g = make_graph(spec, seed=0, device=dev)          # the same graph on every rank
+        self.g, self.e, self.n_dst, self.n_src = g, g.n_edges, g.n_dst, g.n_src
+        self.sh = sh = halo.shard_band(g.indptr, g.indices, rank, world)
+        self.plan_r, self.plan_t = halo._plans(sh)
+        self.scale = self.d ** -0.5
+        # inputs are functions of the global node id, so any rank can rebuild any row for checking
+        ids = th.arange(sh.lo, sh.hi, device=dev, dtype=th.int64)
+        hd = self.h * self.d
+        mk = lambda seed: hashed_normal(ids, hd, seed).view(-1, self.h, self.d).to(self.dtype)
+        self.Q, self.K, self.V, self.dO = mk(21), mk(22), mk(23), mk(24)
+        self.host = [_pinned(t.cpu()) for t in (self.Q, self.K, self.V, self.dO)]
+        self.outs = [_pinned(th.empty_like(t, device="cpu")) for t in (self.Q, self.Q, self.K, self.V)]
+        s = 2
+        F = lambda n: n * hd * s
+        rows, win = sh.rows, sh.window_rows
+        self.alg = {
+            "attention_fwd_banded": 2 * F(rows) + 2 * F(win) + 2 * rows * 4 + rows * self.h * 4,
+            "attention_bwd_dst_banded": 4 * F(rows) + 2 * F(win) + 2 * rows * 4 + 3 * rows * self.h * 4,
+            "attention_bwd_src_banded": 4 * F(win) + 2 * F(rows) + 2 * win * 4 + 2 * rows * self.h * 4,
+        }
+        self.alg_step = 6 * F(rows) + 6 * F(win)
+
+    def units(self):
+        return float(self.sh.indices.numel()) * self.h    # this rank's edges: the sum over ranks is E * H
+
+    def forward(self):
+        from custom_op_benchmark_b200 import halo
+        self.o, self.lse, self.saved = halo.band_attention_forward(self.sh, self.Q, self.K, self.V, self.scale)
+
+    def backward(self):
+        from custom_op_benchmark_b200 import halo
+        return halo.band_attention_backward(self.sh, self.Q, self.saved, self.o, self.lse, self.dO, self.scale)
+
+    def e2e_compute(self, stage):
+        from custom_op_benchmark_b200 import halo
+        q, k, v, g_o = stage
+        o, lse, saved = halo.band_attention_forward(self.sh, q, k, v, self.scale)
+        dq, dk, dv = halo.band_attention_backward(self.sh, q, saved, o, lse, g_o, self.scale)
+        return [o, dq, dk, dv]
+
+    def e2e_bytes(self):
+        return _nbytes(self.host), _nbytes(self.outs)
+
+    def max_err(self):
+        """This rank's rows of O, lse, dQ, dK, dV against the float64 reference of the WHOLE layer, its inputs
+        rebuilt from their generating function (so the exchanged halo rows and returned gradients are checked)."""
+        from oracle import edge_list_f64 as ref
+        self.forward()
+        got = [self.o, self.lse] + list(self.backward())
+        ids = th.arange(self.n_dst, device=self.dev, dtype=th.int64)
+        hd = self.h * self.d
+        mk = lambda seed: hashed_normal(ids, hd, seed).view(-1, self.h, self.d).to(self.dtype)
+        want = ref.attention_f64(self.g.indptr, self.g.indices, mk(21), mk(22), mk(23), self.scale, mk(24))
+        out = {}
+        for name, a, b in zip(("o", "lse", "dq", "dk", "dv"), got, want):
+            b = b[self.sh.lo:self.sh.hi]
+            keep = th.isfinite(b)
+            out[name] = ref.max_err(a[keep], b[keep])[0]
+        return dict(out, max_err=max(out.values()),
+                    what="every element of this rank's rows of O, lse, dQ, dK, dV against the float64 edge-list "
+                         "reference of the whole layer, |x - ref| / (1 + |ref|)")
+
+    def collectives(self, reps=5):
+        from custom_op_benchmark_b200 import halo
+        if self.world == 1:
+            return None
+        kv = th.cat([self.K, self.V], dim=-1)
+        halo.halo_gather(self.sh, kv)
+        th.cuda.synchronize()
+        a, b = th.cuda.Event(enable_timing=True), th.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            halo.halo_gather(self.sh, kv)
+        b.record()
+        th.cuda.synchronize()
+        row = 2 * self.h * self.d * 2
+        return {"kind": "all-to-all of the halo rows (K and V in one message per neighbour), forward; the same rows of "
+                        "dK and dV travel back in the backward",
+                "halo_gather_ms": a.elapsed_time(b) / reps, "halo_rows": sum(self.sh.recv_counts),
+                "bytes_received_per_step": 2 * sum(self.sh.recv_counts) * row}
+
+
+WORKLOAD_CLASSES = {"attention": AttentionWorkload, "attention_bias": AttentionBiasWorkload, "gat": GatWorkload, "sddmm_softmax": SddmmSoftmaxWorkload,
+                    "sharded_spmm": ShardedSpmmWorkload, "halo_attention": HaloAttentionWorkload}
 
 
 # --------------------------------------------------------------------------------------------
@@ -715,6 +876,8 @@ def build_workload(args, spec, rank, dev, world):
     if spec["ops"] == "sharded_spmm":
         spec["exchange"] = args.exchange
         return ShardedSpmmWorkload(spec, rank, dev, world)
+    if spec["ops"] == "halo_attention":
+        return HaloAttentionWorkload(spec, rank, dev, world)
     return WORKLOAD_CLASSES[spec["ops"]](spec, rank, dev)
 
 
@@ -959,7 +1122,7 @@ def run_gpu(args):
             "config": {"workload": args.workload, "ops": wl.name, "graph": describe(spec), "nodes": wl.n_dst,
                        "edges": wl.e, "heads": wl.h, "dim": wl.d,
                        "index": "int32 CSR, chunk tables of partition_csr(32)",
-                       "per_rank": "a row shard of one graph" if spec["ops"] == "sharded_spmm" else "own graph",
+                       "per_rank": "a row shard of one graph" if spec["ops"] in ("sharded_spmm", "halo_attention") else "own graph",
                        "l2": "inputs (%.2f GB) %s the 126 MB L2" % (
                            in_bytes / 1e9, "larger than" if in_bytes > 2 * 126e6 else "NOT larger than"),
                        "resident": wl.resident,
@@ -1009,7 +1172,7 @@ def run_gpu(args):
             # the checker's other job: the same step's results against the float64 edge-list reference
             out["max_err"] = wl.max_err()
     # -- the sharded configuration beside the headline one (strong scaling, communication in the data path)
-    if args.sharded != "off" and spec["ops"] != "sharded_spmm":
+    if args.sharded != "off" and spec["ops"] not in ("sharded_spmm", "halo_attention"):
         del wl
         th.cuda.empty_cache()
         extra = sharded_extra(args, rank, dev, world)
@@ -1042,7 +1205,7 @@ def cpu_baseline(spec, sample_scale):
     else:
         g = graphs.zipf_graph(spec["n"] // 25, spec["total"] // 25, cap=spec["total"] // 25, seed=0)
         sample = "the same degree law at 1/25 of the nodes and edges"
-    ops = "gat" if spec["ops"] == "gat" else ("sddmm_softmax" if spec["ops"] == "sddmm_softmax" else "attention")
+    ops = spec["ops"] if spec["ops"] in ("gat", "sddmm_softmax", "attention_bias") else "attention"
     sec = cb.time_workload(ops, g, h, d)
     return {"value": g.n_edges * h / sec, "unit": UNIT, "cores": th.get_num_threads(), "host_cpus": os.cpu_count(),
             "kind": "port", "seconds": sec,
@@ -1065,7 +1228,7 @@ def reference_cuda(spec, graph, steps=3):
         return {"unavailable": "oracle/_ref holds no build of the reference"}
     from custom_op_benchmark_b200.part_csr import partition_csr
     h, d, ops = spec["heads"], spec["dim"], spec["ops"]
-    if ops not in ("attention", "gat", "sddmm_softmax"):
+    if ops not in ("attention", "attention_bias", "gat", "sddmm_softmax"):
         return {"unavailable": "not run on this workload"}
     if spec["dtype"] != "f32":
         return {"unavailable": "the reference has no %s kernels (AT_DISPATCH_FLOATING_TYPES)" % spec["dtype"]}
@@ -1099,6 +1262,19 @@ def reference_cuda(spec, graph, steps=3):
             dp, _ = timed("spmm_bwd", lambda: ref.vector_spmm_backward(*R, *C, p, dO, V))
             ds = timed("softmax_bwd", lambda: ref.sparse_softmax_backward(*R[:3], p, dp))
             timed("maskedmm_bwd", lambda: ref.maskedmm_csr_backward(*R, *C, Q, K, ds * scale))
+    elif ops == "attention_bias":
+        Q, K, V, dO, scale = rn(n, h, d), rn(m, h, d), rn(m, h, d), rn(n, h, d), d ** -0.5
+        rel = rn(e, d) * 0.5
+
+        def step():     # the layer as the reference's ops compose it: two score tensors, then the chain
+            s = timed("maskedmm_fwd", lambda: ref.maskedmm_csr_forward(*R, Q, K))
+            b = timed("node_mul_edge_fwd", lambda: ref.node_mul_edge_forward(*R[:3], Q, rel))
+            p = timed("softmax_fwd", lambda: ref.sparse_softmax_forward(*R[:3], (s + b) * scale))
+            timed("spmm_fwd", lambda: ref.vector_spmm_forward(*R, p, V))
+            dp, _ = timed("spmm_bwd", lambda: ref.vector_spmm_backward(*R, *C, p, dO, V))
+            ds = timed("softmax_bwd", lambda: ref.sparse_softmax_backward(*R[:3], p, dp)) * scale
+            timed("maskedmm_bwd", lambda: ref.maskedmm_csr_backward(*R, *C, Q, K, ds))
+            timed("node_mul_edge_bwd", lambda: ref.node_mul_edge_backward(*R[:3], Q, rel, ds))
     elif ops == "gat":
         X, Be, w, dY1, dY2 = rn(n, h, d), rn(e, d), th.rand(e, h, generator=gen, device=dev), rn(e, h), rn(n, h, d)
 
@@ -1156,7 +1332,7 @@ def run_reference(args):
         return
     t0 = time.time()
     g = make_graph(spec, seed=0, device="cuda" if th.cuda.is_available() else "cpu").to(device="cpu")
-    ops = spec["ops"]
+    ops = "attention" if spec["ops"] == "halo_attention" else spec["ops"]   # the host cores see one whole graph
     secs = []
     budget_s = 150.0
     planned = max(1, args.steps)

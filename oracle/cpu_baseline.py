@@ -11,9 +11,10 @@ import time
 import torch as th
 
 
-def attention_chain_cpu(indptr, indices, Q, K, V, scale, dO, rows_per_block=1 << 15):
+def attention_chain_cpu(indptr, indices, Q, K, V, scale, dO, rows_per_block=1 << 15, rel=None):
     """Forward and backward of SDDMM(Q, K) * scale -> softmax per destination -> SpMM(V) on the
-    CPU.  Returns (O, dQ, dK, dV)."""
+    CPU.  Returns (O, dQ, dK, dV).  rel (edges, dim), optional: the node_mul_edge term added to the scores
+    (its gradient is computed and dropped)."""
     ip = indptr.to("cpu", th.int64)
     idx = indices.to("cpu", th.int64)
     n, h, d = Q.shape
@@ -21,6 +22,7 @@ def attention_chain_cpu(indptr, indices, Q, K, V, scale, dO, rows_per_block=1 <<
     k = K.detach().float().cpu().requires_grad_(True)
     v = V.detach().float().cpu().requires_grad_(True)
     g = dO.detach().float().cpu()
+    b = None if rel is None else rel.detach().float().cpu().requires_grad_(True)
     out = th.empty(n, h, d)
     for r0 in range(0, n, rows_per_block):
         r1 = min(n, r0 + rows_per_block)
@@ -32,7 +34,10 @@ def attention_chain_cpu(indptr, indices, Q, K, V, scale, dO, rows_per_block=1 <<
         dst = th.repeat_interleave(th.arange(r1 - r0), deg)
         src = idx[lo:hi]
         qb = q[r0:r1]
-        s = (qb.index_select(0, dst) * k.index_select(0, src)).sum(-1) * scale
+        ke = k.index_select(0, src)
+        if b is not None:
+            ke = ke + b[lo:hi].unsqueeze(1)
+        s = (qb.index_select(0, dst) * ke).sum(-1) * scale
         m = th.full((r1 - r0, h), -float("inf")).scatter_reduce(0, dst.view(-1, 1).expand(-1, h), s.detach(),
                                                                  reduce="amax")
         ex = th.exp(s - m.index_select(0, dst))
@@ -44,12 +49,12 @@ def attention_chain_cpu(indptr, indices, Q, K, V, scale, dO, rows_per_block=1 <<
     return out, q.grad, k.grad, v.grad
 
 
-def time_chain(indptr, indices, Q, K, V, scale, dO, repeats=1):
+def time_chain(indptr, indices, Q, K, V, scale, dO, repeats=1, rel=None):
     """Seconds of one forward+backward (best of `repeats`)."""
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
-        attention_chain_cpu(indptr, indices, Q, K, V, scale, dO)
+        attention_chain_cpu(indptr, indices, Q, K, V, scale, dO, rel=rel)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     return best
@@ -94,6 +99,9 @@ def time_workload(ops, g, h, d, seed=1):
     n, m, e = g.n_dst, g.n_src, g.n_edges
     if ops == "attention":
         return time_chain(g.indptr, g.indices, r(n, h, d), r(m, h, d), r(m, h, d), d ** -0.5, r(n, h, d))
+    if ops == "attention_bias":
+        return time_chain(g.indptr, g.indices, r(n, h, d), r(m, h, d), r(m, h, d), d ** -0.5, r(n, h, d),
+                          rel=r(e, d) * 0.5)
     t0 = time.perf_counter()
     if ops == "gat":
         gat_cpu(g.indptr, g.indices, r(n, h, d), r(e, d), th.rand(e, h, generator=gen), r(e, h), r(n, h, d))
