@@ -44,8 +44,8 @@ WORKLOADS = {
     "er_small_attention": dict(kind="er", n=4096, k=15, heads=8, dim=64, dtype="f32", ops="attention"),
     "banded_attention": dict(kind="banded", batch=4, length=8192, window=128, heads=8, dim=64, dtype="bf16",
                              ops="attention"),
-    # the same banded layer as ONE graph cut by rows over the ranks, K / V halo rows exchanged every step (strong scaling)
-    "banded_halo_attention": dict(kind="banded", batch=4, length=8192, window=128, heads=8, dim=64, dtype="bf16",
+    # the banded layer on ONE sequence of 32768 positions, its graph cut by rows over the ranks, K / V halo rows exchanged every step (strong scaling)
+    "banded_halo_attention": dict(kind="banded", batch=1, length=32768, window=128, heads=8, dim=64, dtype="bf16",
                                   ops="halo_attention"),
     "zipf_attention": dict(kind="zipf", n=1_000_000, total=50_000_000, heads=2, dim=64, dtype="f32", ops="attention"),
     # the fused chain with the node_mul_edge term in the scores (relative-position attention), forward + backward

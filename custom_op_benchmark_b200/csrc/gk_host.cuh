@@ -910,8 +910,7 @@ inline int attention_bias_backward(const GS& gs_r, const GS& gs_c, bool has_eid_
         return op;
       });
     })));
-    const long long total = E * D;
-    const unsigned grid = (unsigned)((total + 255) / 256 < (1 << 16) ? (total + 255) / 256 : (1 << 16));
+    const unsigned grid = (unsigned)((E + 7) / 8 < 148 * 64 ? (E + 7) / 8 : 148 * 64);   // 8 warps per block
     bias_grad_kernel<T><<<grid ? grid : 1, 256, 0, st>>>(g.erow, pd, q, d_rel, E, H, Hp, D);
     GK_LAUNCHED("attention_bias_grad");
   }
