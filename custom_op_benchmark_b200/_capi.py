@@ -44,10 +44,11 @@ class Plan(ctypes.Structure):
     _fields_ = [("n_chunks", ctypes.c_int64), ("n_edges", ctypes.c_int64), ("n_nodes", ctypes.c_int64),
                 ("header", ctypes.c_void_p), ("erow", ctypes.c_void_p), ("other", ctypes.c_void_p),
                 ("eid", ctypes.c_void_p), ("node_lo", ctypes.c_void_p), ("node_deg", ctypes.c_void_p),
-                ("flags", ctypes.c_int32), ("band_span", ctypes.c_int32)]
+                ("flags", ctypes.c_int32), ("band_span", ctypes.c_int32), ("tile_start", ctypes.c_void_p),
+                ("tile", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
-PLAN_DENSE_BAND = 1
+PLAN_DENSE_BAND, PLAN_ROW_TILES, PLAN_NO_CARRY = 1, 2, 4
 _PP = ctypes.POINTER(Plan)
 
 # argument lists of the plan forms (one per element type), in the order of include/graphop_b200.h

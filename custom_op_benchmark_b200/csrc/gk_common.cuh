@@ -281,15 +281,17 @@ template <class Op, bool kCarryLevel>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 walk_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ erow,
             const int32_t* __restrict__ other, const int32_t* __restrict__ eid, long long E, int tile,
-            long long n_rows, int32_t* __restrict__ rows_next) {
+            long long n_rows, int32_t* __restrict__ rows_next, const int32_t* __restrict__ tile_start) {
   constexpr int U = Op::kUnroll;
   constexpr bool kOut = Op::kRowOut;
   constexpr bool kFill = Op::kRowOut && !kCarryLevel;
   const int lane = threadIdx.x & 31;
   const long long t = (long long)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  const long long j0 = t * tile;
-  if (j0 >= E) return;
-  const long long j1 = j0 + tile < E ? j0 + tile : E;
+  // tile t covers positions [t * tile, (t + 1) * tile), or, with a plan's row-aligned boundaries,
+  // [tile_start[t], tile_start[t + 1]): the same number of tiles, each boundary moved up to the next row start
+  if (t * tile >= E) return;
+  const long long j0 = tile_start ? (long long)__ldg(tile_start + t) : t * tile;
+  const long long j1 = tile_start ? (long long)__ldg(tile_start + t + 1) : (j0 + tile < E ? j0 + tile : E);
 
   if constexpr (kFill) {
     if (t == 0 && hdr->cover_hi <= hdr->cover_lo) {  // no covered position at all

@@ -137,6 +137,12 @@ struct GraphView {
   const int32_t* other;  // may be null (ops without a second endpoint)
   const int32_t* eid;    // may be null: identity
   long long E;
+  // from a plan: boundaries of the level-0 tiles moved up to row starts (for tiles of `start_tile` positions), and
+  // whether no row crosses a boundary any more (then there is nothing for the carry levels to do)
+  const int32_t* tile_start = nullptr;
+  int start_tile = 0;
+  bool no_carry = false;
+  const int32_t* starts_for(int tile) const { return tile == start_tile ? tile_start : nullptr; }
 };
 
 template <typename I>
@@ -196,6 +202,11 @@ struct FromPlan {
     g->other = p->other;
     g->eid = p->eid;
     g->E = p->n_edges;
+    if ((p->flags & GRAPHOP_PLAN_ROW_TILES) && p->tile_start) {
+      g->tile_start = p->tile_start;
+      g->start_tile = p->tile;
+      g->no_carry = (p->flags & GRAPHOP_PLAN_NO_CARRY) != 0;
+    }
     return GRAPHOP_OK;
   }
 };
@@ -284,7 +295,7 @@ inline int launch_staged(const Op& op, const GraphView& g, int tile, long long n
   }
   const long long nt = (g.E + tile - 1) / tile;
   walk_staged_kernel<Op><<<grid_for_warps(nt, Op::kWarps), Op::kWarps * 32, staged_smem_bytes<Op>(), st>>>(
-      op, g.hdr, g.erow, g.other, g.eid, g.E, tile, n_rows, rows_next);
+      op, g.hdr, g.erow, g.other, g.eid, g.E, tile, n_rows, rows_next, g.starts_for(tile));
   GK_LAUNCHED(Op::kName);
   return GRAPHOP_OK;
 }
@@ -299,7 +310,8 @@ template <class Op> struct IsStaged<Op, std::void_t<decltype(Op::kEdgeBytes)>> :
 template <class MakeOp, class MakeOp0>
 inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_rows, size_t carry_elem_bytes,
                           long long carry_stride, cudaStream_t st, MakeOp&& make_op, MakeOp0&& make_op0) {
-  const Levels lv = make_levels(g.E, tile0);
+  Levels lv = make_levels(g.E, tile0);
+  if (g.no_carry && g.starts_for(tile0)) lv.n = 1;   // row-aligned tiles that no row crosses: level 0 stores every row
   void* carry[kMaxLevels];
   int32_t* rows[kMaxLevels + 1];
   rows[0] = nullptr;
@@ -317,7 +329,7 @@ inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_
       GK_TRY(launch_staged(op, g, lv.tile[0], n_rows, rows[1], st));
     } else {
       walk_kernel<Op, false><<<grid_for_warps(lv.ntiles[0], kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
-          op, g.hdr, g.erow, g.other, g.eid, g.E, lv.tile[0], n_rows, rows[1]);
+          op, g.hdr, g.erow, g.other, g.eid, g.E, lv.tile[0], n_rows, rows[1], g.starts_for(lv.tile[0]));
       GK_LAUNCHED(Op::kName);
     }
   }
@@ -325,7 +337,7 @@ inline int run_row_levels(Arena& ar, const GraphView& g, int tile0, long long n_
     auto op = make_op(carry[k], carry[k - 1]);
     using Op = decltype(op);
     walk_kernel<Op, true><<<grid_for_warps(lv.ntiles[k], kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
-        op, g.hdr, rows[k], nullptr, nullptr, lv.len[k], lv.tile[k], n_rows, rows[k + 1]);
+        op, g.hdr, rows[k], nullptr, nullptr, lv.len[k], lv.tile[k], n_rows, rows[k + 1], nullptr);
     GK_LAUNCHED("carry_level");
   }
   return GRAPHOP_OK;
@@ -398,7 +410,7 @@ inline int run_edge_dot(const GraphView& g, const T* a, const T* b, T* y, int H,
     EdgeDotAnyOp<T, kEdgeFeat> op;
     op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD;
     walk_kernel<decltype(op), false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E, tile0, 0,
-                                                                        nullptr);
+                                                                        nullptr, nullptr);
     GK_LAUNCHED("edge_dot_any");
     return GRAPHOP_OK;
   }
@@ -414,7 +426,7 @@ inline int run_edge_dot(const GraphView& g, const T* a, const T* b, T* y, int H,
       EdgeDotOp<T, V, R, kEdgeFeat> op;
       op.a = a; op.b = b; op.y = y; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = lph;
       walk_kernel<decltype(op), false><<<grid, kWarpsPerCta * 32, 0, st>>>(op, g.hdr, g.erow, g.other, g.eid, g.E,
-                                                                          tile0, 0, nullptr);
+                                                                          tile0, 0, nullptr, nullptr);
       GK_LAUNCHED("edge_dot");
       return (int)GRAPHOP_OK;
     }
@@ -479,7 +491,7 @@ inline int run_softmax_heads(Arena& ar, const GraphView& g, const T* in0, const 
     op.stats = stats; op.carry = (A*)carry[k]; op.carry_in = k ? (const A*)carry[k - 1] : carry0; op.H = H;
     op.n_nodes = n_nodes;
     walk_kernel<decltype(op), true><<<grid_for_warps(lv.ntiles[k], kWarpsPerCta), kWarpsPerCta * 32, 0, st>>>(
-        op, g.hdr, rows[k], nullptr, nullptr, lv.len[k], lv.tile[k], n_nodes, rows[k + 1]);
+        op, g.hdr, rows[k], nullptr, nullptr, lv.len[k], lv.tile[k], n_nodes, rows[k + 1], nullptr);
     GK_LAUNCHED("carry_level");
   }
   softmax_finish_kernel<T, H, kBackward><<<grid0, kSoftmaxWarps * 32, 0, st>>>(g.erow, g.eid, in0, in1, out, stats,
@@ -910,8 +922,17 @@ inline int attention_bias_backward(const GS& gs_r, const GS& gs_c, bool has_eid_
         return op;
       });
     })));
-    const unsigned grid = (unsigned)((E + 7) / 8 < 148 * 64 ? (E + 7) / 8 : 148 * 64);   // 8 warps per block
-    bias_grad_kernel<T><<<grid ? grid : 1, 256, 0, st>>>(g.erow, pd, q, d_rel, E, H, Hp, D);
+    {
+      constexpr int VM = VecMax<T>::value;
+      const bool vec = aligned16(d_rel) && D % VM == 0;   // q is 16-byte aligned (checked above)
+      const int slots = vec ? D / VM : D;
+      int shift = -1;
+      if (is_pow2(slots)) for (shift = 0; (1 << shift) < slots; ++shift) {}
+      const long long total = E * slots;
+      const unsigned grid = (unsigned)((total + 255) / 256 < (1 << 20) ? (total + 255) / 256 : (1 << 20));
+      if (vec) bias_grad_kernel<T, VM><<<grid ? grid : 1, 256, 0, st>>>(g.erow, pd, q, d_rel, E, H, Hp, D, shift);
+      else bias_grad_kernel<T, 1><<<grid ? grid : 1, 256, 0, st>>>(g.erow, pd, q, d_rel, E, H, Hp, D, shift);
+    }
     GK_LAUNCHED("attention_bias_grad");
   }
   ar.used = mark;

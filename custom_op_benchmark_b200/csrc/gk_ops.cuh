@@ -729,31 +729,35 @@ struct AttnBwdSrcOp {
 
 // Gradient of the edge term of the biased attention:  d_rel[j, :] = sum_h ds[j, h] * q[node(j), h, :]
 // (the dB half of node_mul_edge backward, graphop_kernel.cu:79-93, with the score gradients the destination
-// pass left in `pairs`).  One warp per position, lanes across the features (consecutive positions of a node
-// re-read its q row from L1 / L2); positions no chunk covers get 0.
-template <typename T>
+// pass left in `pairs`).  One thread per (position, slot of V features); consecutive threads cover a position's
+// features, consecutive positions of a node re-read its q row from L1 / L2; positions no chunk covers get 0.
+// shift = log2(D / V) when that is a power of two, else -1.
+template <typename T, int V>
 __global__ void __launch_bounds__(256)
 bias_grad_kernel(const int32_t* __restrict__ erow, const EdgePair<typename AccOf<T>::type>* __restrict__ pairs,
-                 const T* __restrict__ q, T* __restrict__ d_rel, long long E, int H, int Hp, int D) {
+                 const T* __restrict__ q, T* __restrict__ d_rel, long long E, int H, int Hp, int D, int shift) {
   using A = typename AccOf<T>::type;
-  const int lane = threadIdx.x & 31;
-  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long j = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); j < E; j += warps) {
+  const int slots = D / V;
+  const long long stride = (long long)gridDim.x * blockDim.x, total = E * slots;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long j = shift >= 0 ? (i >> shift) : i / slots;
+    const int d = (int)(i - j * slots) * V;
     const int r = __ldg(erow + j);
-    // the position's H score gradients: lane h holds ds[j, h] (heads beyond 32 are fetched in the loop)
-    const A mine = (r >= 0 && lane < H) ? pairs[j * Hp + lane].ds : A(0);
-    for (int d0 = 0; d0 < D; d0 += 32) {   // whole-warp trips: the shuffles below need every lane
-      const int d = d0 + lane;
-      A sum = A(0);
-      if (r >= 0) {
-        const T* qrow = q + (long long)r * H * D + (d < D ? d : 0);
-        for (int h = 0; h < H; ++h) {
-          const A ds = h < 32 ? __shfl_sync(kFull, mine, h) : pairs[j * Hp + h].ds;
-          sum += ds * to_acc<T>(qrow[(long long)h * D]);
-        }
+    A sum[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) sum[e] = A(0);
+    if (r >= 0) {
+      const T* qrow = q + (long long)r * H * D + d;
+      const EdgePair<A>* pr = pairs + j * Hp;
+      for (int h = 0; h < H; ++h) {
+        const A ds = pr[h].ds;
+        A qv[V];
+        load_acc<T, V>(qv, qrow + (long long)h * D);
+#pragma unroll
+        for (int e = 0; e < V; ++e) sum[e] += ds * qv[e];
       }
-      if (d < D) d_rel[j * D + d] = from_acc<T>(sum);
     }
+    store_acc<T, V>(d_rel + j * D + d, sum);
   }
 }
 

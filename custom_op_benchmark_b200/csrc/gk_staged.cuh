@@ -152,7 +152,7 @@ template <class Op>
 __global__ void __launch_bounds__(Op::kWarps * 32, Op::kMinCtas)
 walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ erow,
                    const int32_t* __restrict__ other, const int32_t* __restrict__ eid, long long E, int tile,
-                   long long n_rows, int32_t* __restrict__ rows_next) {
+                   long long n_rows, int32_t* __restrict__ rows_next, const int32_t* __restrict__ tile_start) {
   constexpr int U = Op::kBatch;
   constexpr int DEPTH = Op::kDepth;
   constexpr int EB = Op::kEdgeBytes;
@@ -164,10 +164,12 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
   const int lane = threadIdx.x & 31;
   const int w = threadIdx.x >> 5;
   const long long t = (long long)blockIdx.x * Op::kWarps + w;
-  const long long j0 = t * tile;
-  if (j0 >= E) return;
-  const int nt = (int)(j0 + tile < E ? tile : E - j0);
-  const long long j1 = j0 + nt;
+  // uniform tiles, or a plan's row-aligned ones (see walk_kernel): up to 2 * tile - 1 positions then, which the
+  // rolling metadata window does not mind
+  if (t * tile >= E) return;
+  const long long j0 = tile_start ? (long long)__ldg(tile_start + t) : t * tile;
+  const long long j1 = tile_start ? (long long)__ldg(tile_start + t + 1) : (j0 + tile < E ? j0 + tile : E);
+  const int nt = (int)(j1 - j0);
 
   if constexpr (kOut) {
     if (t == 0 && hdr->cover_hi <= hdr->cover_lo) {  // no covered position at all

@@ -448,6 +448,12 @@ class GraphPlan:
     def band_span(self):
         return int(self.c.band_span)
 
+    @property
+    def no_carry(self):
+        """No node's positions cross a (row-aligned) work-tile boundary: the planned row-reducing ops are one
+        launch each on this graph."""
+        return bool(self.c.flags & _capi.PLAN_NO_CARRY)
+
     def ref(self):
         import ctypes
         return ctypes.byref(self.c)

@@ -110,11 +110,24 @@ int graphop_check_graph_i64(const int64_t* row, const int64_t* indptr, const int
  * block-diagonal test graph of wrapper.py:79-112): graphop_attention_forward_planned_bf16 then runs such a graph on
  * the tensor cores.
  *
+ * The kernels cut the position stream into tiles of equal length, one warp each, and a node whose positions cross a
+ * tile boundary is finished by small follow-up launches (carry levels).  plan_build moves every boundary up to the
+ * next row start where there is one inside the tile; if no node crosses a boundary then (every node at most a tile
+ * long: the two flags GRAPHOP_PLAN_ROW_TILES | GRAPHOP_PLAN_NO_CARRY are set together), the planned row-reducing ops
+ * use those tiles and are one launch each.  The order in which a row's terms are added then differs from the
+ * chunk-table entry points' (whole rows instead of tile pieces): results agree to rounding, not to the bit; each
+ * stays reproducible from run to run.  On every other graph the planned ops use the same tiles as the chunk-table
+ * ones and give identical bits.
+ *
  * A plan refers to the caller's `indices` / `eid` arrays when they are 32-bit (they must outlive the plan) and to
  * plan memory otherwise.  graphop_plan_build_* enqueues its kernels on `stream` and waits for them once, to read
  * the shape flags back: it is a set-up call, not a per-step one.
  * --------------------------------------------------------------------------------------------------------- */
-enum { GRAPHOP_PLAN_DENSE_BAND = 1 };
+enum {
+  GRAPHOP_PLAN_DENSE_BAND = 1,
+  GRAPHOP_PLAN_ROW_TILES = 2, /* tile_start holds the work tiles' boundaries, moved up to row starts, ... */
+  GRAPHOP_PLAN_NO_CARRY = 4   /* ... and no node's positions cross one: row reductions finish in one launch */
+};
 #define GRAPHOP_BAND_MAX_SPAN 384
 
 typedef struct graphop_plan {
@@ -129,6 +142,9 @@ typedef struct graphop_plan {
   const int32_t* node_deg; /* device, n_nodes: number of positions every node owns */
   int32_t flags;           /* GRAPHOP_PLAN_* */
   int32_t band_span;       /* most different neighbours any 128 consecutive nodes reach (dense-band graphs) */
+  const int32_t* tile_start; /* device, n_tiles + 1: first position of every work tile (GRAPHOP_PLAN_ROW_TILES) */
+  int32_t tile;            /* nominal positions per work tile the boundaries were made for */
+  int32_t reserved;
 } graphop_plan_t;
 
 /* Bytes of device memory (256-byte aligned) a plan of these sizes needs. */

@@ -1,5 +1,6 @@
-"""Graph plans: the planned ops give the same bits as the chunk-table ops, the shape analysis finds dense bands,
-and a dense-band graph's bfloat16 attention forward (tensor-core kernel) matches the float64 reference."""
+"""Graph plans: the planned ops agree with the chunk-table ops (per-edge outputs and the softmax to the bit; row
+reductions to rounding, because a plan's work tiles end on row starts), the shape analysis finds dense bands, and a
+dense-band graph's bfloat16 attention (tensor-core kernels) matches the float64 reference."""
 import pytest
 import torch as th
 
@@ -27,31 +28,53 @@ def test_planned_ops_equal_chunk_table_ops(name, g, cs, idt):
     rn = lambda *s: th.randn(*s, generator=gen, device=DEV)
     A, B, dY = rn(g.n_dst, h, d), rn(g.n_src, h, d), rn(g.n_dst, h, d)
     w, ds, Be = th.rand(e, h, generator=gen, device=DEV), rn(e, h), rn(e, d)
+    def same_sums(a, b, what):   # the same terms, added row by row instead of tile piece by tile piece
+        assert_close(a, b, 2e-5, 2e-5 * max(1.0, float(b.abs().max())), what)
+
     assert th.equal(graphop.maskedmm_csr_forward_planned(pr, A, B), graphop.maskedmm_csr_forward(*rc, A, B))
     for a, b in zip(graphop.maskedmm_csr_backward_planned(pr, pt, A, B, ds),
                     graphop.maskedmm_csr_backward(*rc, *cc, A, B, ds)):
-        assert th.equal(a, b)
-    assert th.equal(graphop.vector_spmm_forward_planned(pr, w, B, num_dst=g.n_dst),
-                    graphop.vector_spmm_forward(*rc, w, B, num_dst=g.n_dst))
+        same_sums(a, b, "maskedmm backward")
+    same_sums(graphop.vector_spmm_forward_planned(pr, w, B, num_dst=g.n_dst),
+              graphop.vector_spmm_forward(*rc, w, B, num_dst=g.n_dst), "spmm forward")
     if g.n_dst == g.n_src:
-        for a, b in zip(graphop.vector_spmm_backward_planned(pr, pt, w, dY, B),
-                        graphop.vector_spmm_backward(*rc, *cc, w, dY, B)):
-            assert th.equal(a, b)
+        got = graphop.vector_spmm_backward_planned(pr, pt, w, dY, B)
+        want = graphop.vector_spmm_backward(*rc, *cc, w, dY, B)
+        assert th.equal(got[0], want[0])
+        same_sums(got[1], want[1], "spmm backward dx")
     p = graphop.sparse_softmax_forward_planned(pr, ds)
     assert th.equal(p, graphop.sparse_softmax_forward(*rc[:3], ds))
     assert th.equal(graphop.sparse_softmax_backward_planned(pr, p, w), graphop.sparse_softmax_backward(*rc[:3], p, w))
     assert th.equal(graphop.node_mul_edge_forward_planned(pr, A, Be), graphop.node_mul_edge_forward(*rc[:3], A, Be))
-    for a, b in zip(graphop.node_mul_edge_backward_planned(pr, A, Be, ds),
-                    graphop.node_mul_edge_backward(*rc[:3], A, Be, ds)):
-        assert th.equal(a, b)
+    got = graphop.node_mul_edge_backward_planned(pr, A, Be, ds)
+    want = graphop.node_mul_edge_backward(*rc[:3], A, Be, ds)
+    same_sums(got[0], want[0], "node_mul_edge backward dA")
+    assert th.equal(got[1], want[1])
     o, lse = graphop.attention_forward_planned(pr, A, B, B * 0.5, 0.2)
     o2, lse2 = graphop.attention_forward(rc[0], rc[1], rc[3], A, B, B * 0.5, 0.2)
-    assert th.equal(o, o2) and th.equal(lse, lse2)
-    got = graphop.attention_backward_planned(pr, pt, A, B, B * 0.5, o, lse, dY, 0.2)
-    want = graphop.attention_backward(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], A, B, B * 0.5, o, lse, dY, 0.2,
+    has = th.isfinite(lse2)
+    same_sums(o, o2, "attention o")
+    assert th.equal(th.isfinite(lse), has)
+    same_sums(lse[has], lse2[has], "attention lse")
+    got = graphop.attention_backward_planned(pr, pt, A, B, B * 0.5, o2, lse2, dY, 0.2)
+    want = graphop.attention_backward(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], A, B, B * 0.5, o2, lse2, dY, 0.2,
                                       eid_t=cc[2])
-    for a, b in zip(got, want):
+    for a, b, what in zip(got, want, ("dq", "dk", "dv")):
+        same_sums(a, b, "attention " + what)
+    # and twice the same answer
+    again = graphop.attention_backward_planned(pr, pt, A, B, B * 0.5, o2, lse2, dY, 0.2)
+    for a, b in zip(got, again):
         assert th.equal(a, b)
+
+
+def test_row_aligned_tiles_need_no_carry_levels():
+    """A graph whose rows are all shorter than a work tile: the plan says so, and the fused step is 3 launches."""
+    g = graphs.er_graph(4096, 15, seed=0)
+    rc, cc, pr, pt = _plans(g, 32, th.int32)
+    assert pr.no_carry and pt.no_carry
+    long_rows = ZOO[3][1]
+    _, _, pl, _ = _plans(long_rows, 32, th.int32)
+    assert not pl.no_carry
 
 
 def test_planned_autograd_function():
@@ -65,7 +88,7 @@ def test_planned_autograd_function():
     q2, k2, v2 = (t.clone().requires_grad_(True) for t in (Q, K, V))
     wrapper.GraphAttention.apply(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], q2, k2, v2, 0.3, cc[2]).backward(dO)
     for a, b in ((q, q2), (k, k2), (v, v2)):
-        assert th.equal(a.grad, b.grad)
+        assert_close(a.grad, b.grad, 2e-5, 2e-5 * max(1.0, float(b.grad.abs().max())), "grad")
 
 
 def test_shape_analysis_finds_dense_bands():
