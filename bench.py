@@ -551,7 +551,9 @@ class ShardedSpmmWorkload:
         self.e, self.n_dst, self.n_src = g.n_edges, g.n_dst, g.n_src
         self.sh = sh = sharding.shard_graph(g, rank, world, chunk_size=32)
         # world > 1: fetch only the node rows this shard's edges reference (built once per graph)
-        self.ex = sharding.plan_shard_exchange(sh) if (world > 1 and spec.get("exchange", "needed") == "needed") else None
+        mode = spec.get("exchange", "needed")
+        self.ex = sharding.plan_shard_exchange(sh) if (world > 1 and mode in ("needed", "peer")) else None
+        self.peer = world > 1 and mode == "peer"
         del g
         th.cuda.empty_cache()
         # every input is a pure function of its global id (edge id, source node, destination node), so that any
@@ -564,6 +566,15 @@ class ShardedSpmmWorkload:
         self.dy_local = hashed_normal(ar(int(sh.dst_bounds[rank]), sh.rows), self.d, 13)
         self.host = [_pinned(self.x_shard.cpu()), _pinned(self.dy_local.cpu())]
         self.outs = [_pinned(th.empty(sh.rows, self.d)), _pinned(th.empty(sh.cols, self.d))]
+        if self.peer:
+            # the two row-sharded inputs live in symmetric memory: every rank pulls the rows it references out of the
+            # owners' blocks with one kernel (plain peer loads over NVLink), no collective in the data path
+            self.px = sharding.PeerRows(rows_x, (self.d,), th.float32, dev)
+            self.pdy = sharding.PeerRows(sh.rows, (self.d,), th.float32, dev)
+            self.px.local.copy_(self.x_shard)
+            self.pdy.local.copy_(self.dy_local)
+            self.px.barrier()
+            self.pdy.barrier()
         s, i = 4, 4
         e_loc, e_t = sh.indices.numel(), sh.eid_t.numel()
         F = lambda n: n * self.h * self.d * s
@@ -579,14 +590,29 @@ class ShardedSpmmWorkload:
 
     def forward(self):
         from custom_op_benchmark_b200 import sharding
+        if self.peer:
+            self.px.barrier()       # every block is in place before anyone pulls (a training step writes x each time)
+            self.y, self.x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, self.px, exchange=self.ex)
+            return
         self.y, self.x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, self.x_shard, exchange=self.ex)
 
     def backward(self):
         from custom_op_benchmark_b200 import sharding
+        if self.peer:
+            self.pdy.barrier()
+            return sharding.sharded_spmm_backward(self.sh, self.w_local, self.pdy, self.x_all, exchange=self.ex)
         return sharding.sharded_spmm_backward(self.sh, self.w_local, self.dy_local, self.x_all, exchange=self.ex)
 
     def e2e_compute(self, stage):
         from custom_op_benchmark_b200 import sharding
+        if self.peer:
+            self.px.barrier()       # nobody is still pulling from the blocks about to be overwritten
+            self.px.local.copy_(stage[0])
+            self.pdy.local.copy_(stage[1])
+            self.px.barrier()
+            y, x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, self.px, exchange=self.ex)
+            _, dx = sharding.sharded_spmm_backward(self.sh, self.w_local, self.pdy, x_all, exchange=self.ex)
+            return [y, dx]
         y, x_all = sharding.sharded_spmm_forward(self.sh, self.w_local, stage[0], exchange=self.ex)
         _, dx = sharding.sharded_spmm_backward(self.sh, self.w_local, stage[1], x_all, exchange=self.ex)
         return [y, dx]
@@ -647,14 +673,17 @@ class ShardedSpmmWorkload:
         if self.world == 1:
             return None
         xb = sharding.even_bounds(self.n_src, self.world)
-        if self.ex is not None:
+        if self.peer:
+            legs = (("x", lambda: self.px.pull(self.ex.x)), ("dy", lambda: self.pdy.pull(self.ex.dy)))
+        elif self.ex is not None:
             from custom_op_benchmark_b200 import graphop
             legs = (("x", lambda: sharding.exchange_rows(self.x_shard, self.ex.x, gather=graphop.gather_rows)),
                     ("dy", lambda: sharding.exchange_rows(self.dy_local, self.ex.dy, gather=graphop.gather_rows)))
         else:
             legs = (("x", lambda: sharding.all_gather_rows(self.x_shard, xb)),
                     ("dy", lambda: sharding.all_gather_rows(self.dy_local, self.sh.dst_bounds)))
-        out = {"kind": "all-to-all of the referenced rows" if self.ex is not None else "all-gather of every row"}
+        out = {"kind": "referenced rows pulled from the peers' memory by one kernel per rank" if self.peer else
+               ("all-to-all of the referenced rows" if self.ex is not None else "all-gather of every row")}
         for name, leg in legs:
             leg()
             th.cuda.synchronize()
@@ -1095,6 +1124,16 @@ def run_gpu(args):
     # -- the collectives of a sharded step, timed alone (per-kernel events count them with the kernel after them)
     coll = wl.collectives() if hasattr(wl, "collectives") else None
 
+    # -- the timed step's results against the float64 edge-list reference, every rank its own (worst one reported);
+    #    a sharded workload's check runs its step, collectives included, so every rank takes part
+    err = None
+    if not args.no_cpu_baseline:
+        err = wl.max_err()
+        if world > 1:
+            worst = th.tensor([err["max_err"]], dtype=th.float64, device=dev)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            err = dict(err, max_err=worst.item(), over_ranks=world)
+
     # -- reduce over ranks ---------------------------------------------------------------------
     stats = th.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], dtype=th.float64, device=dev)
     work = th.tensor([wl.units()], dtype=th.float64, device=dev)
@@ -1169,8 +1208,8 @@ def run_gpu(args):
                                       for k, v in floors.items() if k in kernels}}
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(spec, args.cpu_sample_scale)
-            # the checker's other job: the same step's results against the float64 edge-list reference
-            out["max_err"] = wl.max_err()
+        if err is not None:
+            out["max_err"] = err
     # -- the sharded configuration beside the headline one (strong scaling, communication in the data path)
     if args.sharded != "off" and spec["ops"] not in ("sharded_spmm", "halo_attention"):
         del wl
@@ -1372,8 +1411,9 @@ def main():
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (smaller runs)")
     ap.add_argument("--cpu-sample-scale", type=int, default=19)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="needed", choices=["needed", "all"],
-                    help="sharded workload: fetch only the node rows a shard references, or all-gather every row")
+    ap.add_argument("--exchange", default="needed", choices=["needed", "all", "peer"],
+                    help="sharded workload: fetch only the node rows a shard references (all-to-all), all-gather every "
+                         "row, or pull the referenced rows out of the peers' memory with a kernel (symmetric memory)")
     ap.add_argument("--sharded", default="auto", choices=["auto", "off"],
                     help="also run the row-sharded R-MAT scale-24 SpMM at this GPU count and attach it as `sharded`")
     ap.add_argument("--sharded-scale", type=int, default=0, help="override the R-MAT scale of the sharded extra")

@@ -76,6 +76,7 @@ UNTYPED = {
     "graphop_static_scratch_bytes": ([], _SZ),
     "graphop_vector_spmm_forward_f32_i32_static": ([_P] * 7 + [_I64] * 4 + [_INT] * 2 + [_P], _INT),
     "graphop_gather_rows_i32": ([_P, _I64, _P, _I64, _P, _P], _INT),
+    "graphop_pull_rows_i32": ([_P, _P, _INT, _P, _I64, _P, _P], _INT),
     "graphop_check_graph_i32": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
     "graphop_check_graph_i64": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
 }

@@ -113,7 +113,73 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const int32_t* __restr
     }
   }
 }
+// out[r] = table_p[idx[r]] for the rows r of segment p (seg[p] <= r < seg[p + 1]): the tables are the blocks of a
+// row-sharded tensor on this and on other GPUs, mapped into this process (peer pointers), so the loads of a remote
+// segment cross NVLink - each needed row exactly once - and the stores are local.  Plain loads: no multicast, no
+// waits; the caller orders the kernel after the owners' writes.  Same shape as gather_rows_kernel.
+struct PullTables {
+  const uint4* table[GRAPHOP_MAX_PEERS];
+  long long seg[GRAPHOP_MAX_PEERS + 1];
+  int n;
+};
+__global__ void __launch_bounds__(256) pull_rows_kernel(const __grid_constant__ PullTables tabs,
+                                                       const int32_t* __restrict__ idx, long long n_rows,
+                                                       int row_vec, uint4* __restrict__ out) {
+  constexpr int kRows = 4;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * 8;
+  for (long long g = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); g * kRows < n_rows; g += warps) {
+    const long long r0 = g * kRows;
+    const uint4* src[kRows];
+#pragma unroll
+    for (int u = 0; u < kRows; ++u) {
+      src[u] = nullptr;
+      const long long r = r0 + u;
+      if (r < n_rows) {
+        int p = 0;
+        while (p + 1 < tabs.n && r >= tabs.seg[p + 1]) ++p;
+        src[u] = tabs.table[p] + (long long)__ldg(idx + r) * row_vec;
+      }
+    }
+    for (int j = lane; j < row_vec; j += 32) {
+      uint4 v[kRows];
+#pragma unroll
+      for (int u = 0; u < kRows; ++u)
+        if (src[u]) v[u] = src[u][j];
+#pragma unroll
+      for (int u = 0; u < kRows; ++u)
+        if (src[u]) out[(r0 + u) * row_vec + j] = v[u];
+    }
+  }
+}
 }  // namespace gk
+
+extern "C" int graphop_pull_rows_i32(const void* const* tables, const int64_t* seg, int n_tables, const int32_t* idx,
+                                     int64_t row_bytes, void* out, graphop_stream_t stream) {
+  using namespace gk;
+  if (n_tables < 1 || n_tables > GRAPHOP_MAX_PEERS || !tables || !seg || row_bytes <= 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  const long long n_rows = seg[n_tables];
+  if (seg[0] != 0 || n_rows < 0) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (n_rows == 0) return GRAPHOP_OK;
+  if (!idx || !out) return GRAPHOP_ERR_INVALID_ARGUMENT;
+  if (row_bytes % 16 || row_bytes / 16 > 0x7fffffff || ((uintptr_t)out & 15)) return GRAPHOP_ERR_UNSUPPORTED;
+  PullTables tabs{};
+  tabs.n = n_tables;
+  for (int p = 0; p < n_tables; ++p) {
+    if (seg[p + 1] < seg[p]) return GRAPHOP_ERR_INVALID_ARGUMENT;
+    if (seg[p + 1] > seg[p] && (!tables[p] || ((uintptr_t)tables[p] & 15))) return GRAPHOP_ERR_INVALID_ARGUMENT;
+    tabs.table[p] = (const uint4*)tables[p];
+    tabs.seg[p] = seg[p];
+  }
+  tabs.seg[n_tables] = n_rows;
+  const long long groups = (n_rows + 3) / 4;
+  const long long blocks = (groups + 7) / 8;
+  const unsigned grid = (unsigned)(blocks < 148 * 64 ? blocks : 148 * 64);
+  cudaStream_t st = (cudaStream_t)stream;
+  pull_rows_kernel<<<grid, 256, 0, st>>>(tabs, idx, n_rows, (int)(row_bytes / 16), (uint4*)out);
+  GK_LAUNCHED("pull_rows");
+  return GRAPHOP_OK;
+}
 
 extern "C" int graphop_gather_rows_i32(const int32_t* idx, int64_t n_rows, const void* table, int64_t row_bytes,
                                        void* out, graphop_stream_t stream) {

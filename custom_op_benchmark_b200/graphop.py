@@ -382,6 +382,27 @@ def gather_rows(table, idx, out=None):
     return out
 
 
+def pull_rows(tables, seg, idx, row_bytes, out):
+    """out[r] = table_p[idx[r]] for the rows r of segment p (seg[p] <= r < seg[p + 1]); `tables` are device addresses
+    (ints) of row blocks on this and on peer GPUs, mapped into this process.  One kernel of plain peer loads
+    (graphop_pull_rows_i32); the caller orders it after the owners' writes."""
+    import ctypes
+    n = len(tables)
+    if len(seg) != n + 1:
+        raise RuntimeError("seg must hold one more entry than tables")
+    _check_all(idx=idx, out=out)
+    if idx.dtype != th.int32:
+        raise RuntimeError("idx must be int32")
+    tabs = (ctypes.c_void_p * n)(*[ctypes.c_void_p(int(t)) for t in tables])
+    segs = (ctypes.c_int64 * (n + 1))(*[int(s) for s in seg])
+    with th.cuda.device(out.device):
+        rc = _capi.lib().graphop_pull_rows_i32(tabs, segs, n, _p(idx), int(row_bytes), _p(out),
+                                               th.cuda.current_stream(out.device).cuda_stream)
+    if rc != _capi.OK:
+        raise RuntimeError("graphop_pull_rows: %s" % _capi.error_message(rc))
+    return out
+
+
 def check_graph(row, indptr, eid, indices, n_nodes, n_other):
     """Debug aid: verifies on the device the graph contract the kernels rely on (monotone
     indptr and row, indices and edge ids in range) and returns the violation bit mask

@@ -33,7 +33,7 @@ import torch.distributed as dist
 from .part_csr import partition_csr
 
 __all__ = ["balanced_bounds", "even_bounds", "GraphShard", "shard_graph", "all_gather_rows",
-           "RowExchange", "ShardExchange", "plan_row_exchange", "plan_shard_exchange", "exchange_rows",
+           "RowExchange", "ShardExchange", "PeerRows", "plan_row_exchange", "plan_shard_exchange", "exchange_rows",
            "gather_edge_weights", "sharded_spmm_forward", "sharded_spmm_backward"]
 
 
@@ -150,6 +150,7 @@ class RowExchange:
     send_counts: list     # rows sent to each rank (0 for this rank)
     recv_counts: list     # rows received from each rank, in rank order (0 for this rank)
     own_idx: th.Tensor    # rows of this rank's own block that it references itself
+    pull_idx: th.Tensor = None   # (sum(recv_counts),) int32: the other ranks' rows as ids local to their owner
 
 
 @dataclass
@@ -184,8 +185,9 @@ def plan_row_exchange(indices, owner_bounds, rank, group=None):
     recv_counts = counts.tolist()
     recv_counts[rank] = 0
     own_idx = local_id[c0:c1].contiguous()
+    pull_idx = request.to(th.int32) if int(ob[-1]) < 2 ** 31 else None
     if parts == 1:
-        return RowExchange(needed, request, [0], [0], own_idx), compact
+        return RowExchange(needed, request, [0], [0], own_idx, pull_idx), compact
     send_counts_t = th.empty(parts, dtype=th.int64, device=dev)
     dist.all_to_all_single(send_counts_t, th.tensor(recv_counts, dtype=th.int64, device=dev), group=group)
     send_counts = send_counts_t.tolist()
@@ -194,7 +196,7 @@ def plan_row_exchange(indices, owner_bounds, rank, group=None):
                            input_split_sizes=recv_counts, group=group)
     if int(ob[-1]) < 2 ** 31:   # row ids of one block: the copy kernel takes them as int32
         send_idx, own_idx = send_idx.to(th.int32), own_idx.to(th.int32)
-    return RowExchange(needed, send_idx, send_counts, recv_counts, own_idx), compact
+    return RowExchange(needed, send_idx, send_counts, recv_counts, own_idx, pull_idx), compact
 
 
 def plan_shard_exchange(sh, group=None):
@@ -225,6 +227,51 @@ def exchange_rows(local, plan, group=None, async_op=False, gather=None):
     return (out, work if async_op else None) if async_op else out
 
 
+class PeerRows:
+    """A row-sharded tensor whose block on every rank lives in symmetric memory, so that every rank can read every
+    block with plain loads over NVLink.  Built once (collective): `local` is this rank's block to write into,
+    `pull(plan)` fetches the rows `plan.needed` with one kernel on this GPU (graphop_pull_rows_i32) instead of
+    pack + all-to-all + unpack, `barrier()` orders the ranks (all blocks written before anyone pulls; everyone done
+    pulling before a block is written again).  NVLink multicast is not used and is switched off for the mapping."""
+
+    def __init__(self, rows, row_shape, dtype, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        group = group or dist.group.WORLD
+        enable = getattr(symm, "enable_symm_mem_for_group", None)
+        if enable is not None:            # needed by older torch releases, a no-op on newer ones
+            try:
+                enable(group.group_name)
+            except Exception:
+                pass
+        world = dist.get_world_size(group)
+        counts = [th.zeros(1, dtype=th.int64, device=device) for _ in range(world)]
+        dist.all_gather(counts, th.tensor([rows], dtype=th.int64, device=device), group=group)
+        most = max(int(c) for c in counts)                 # symmetric allocations have one size on all ranks
+        self.buffer = symm.empty((max(most, 1),) + tuple(row_shape), dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.buffer, group)
+        self.local = self.buffer[:rows]
+        self.tables = [int(p) for p in self.handle.buffer_ptrs]
+        self.rank, self.world = dist.get_rank(group), world
+        self.row_bytes = self.local[0].numel() * self.local.element_size() if rows else 0
+
+    def barrier(self):
+        self.handle.barrier()
+
+    def pull(self, plan, ops=None):
+        ops = ops or _default_ops()
+        peers, own = sum(plan.recv_counts), plan.own_idx.numel()
+        out = th.empty((peers + own,) + tuple(self.local.shape[1:]), dtype=self.local.dtype, device=self.local.device)
+        seg = [0]
+        for c in plan.recv_counts:
+            seg.append(seg[-1] + c)
+        if peers:
+            ops.pull_rows(self.tables, seg, plan.pull_idx, self.row_bytes, out[:peers])
+        ops.gather_rows(self.local, plan.own_idx, out=out[peers:])
+        return out
+
+
 def _default_ops():
     from . import graphop
     return graphop
@@ -235,6 +282,10 @@ def sharded_spmm_forward(sh, edata_local, x_shard, ops=None, group=None, exchang
     order), `x_shard`: this rank's even share of the source features.  Returns (y_local, x_rows):
     x_rows is the gathered node tensor, or with `exchange` only the rows the shard references."""
     ops = ops or _default_ops()
+    if isinstance(x_shard, PeerRows):     # the block lives in symmetric memory: pull the referenced rows from the peers
+        x_rows = x_shard.pull(exchange.x, ops)
+        y = ops.vector_spmm_forward(sh.row, sh.indptr, sh.eid, exchange.indices, edata_local, x_rows, num_dst=sh.rows)
+        return y, x_rows
     if exchange is not None:
         x_rows = exchange_rows(x_shard, exchange.x, group, gather=getattr(ops, "gather_rows", None))
         y = ops.vector_spmm_forward(sh.row, sh.indptr, sh.eid, exchange.indices, edata_local, x_rows, num_dst=sh.rows)
@@ -262,7 +313,11 @@ def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all=None, ops=
     change)."""
     ops = ops or _default_ops()
     # the rows of dy are only needed by dx: their transfer is enqueued first and travels while dedata is computed
-    if exchange is not None:
+    if isinstance(dy_local, PeerRows):
+        dy_rows, pending = dy_local.pull(exchange.dy, ops), None
+        src_ids, dst_ids = exchange.indices, exchange.indices_t
+        dy_local = dy_local.local
+    elif exchange is not None:
         dy_rows, pending = exchange_rows(dy_local, exchange.dy, group, async_op=True,
                                          gather=getattr(ops, "gather_rows", None))
         src_ids, dst_ids = exchange.indices, exchange.indices_t

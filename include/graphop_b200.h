@@ -79,6 +79,16 @@ int graphop_last_cuda_error(void);
 int graphop_gather_rows_i32(const int32_t* idx, int64_t n_rows, const void* table, int64_t row_bytes, void* out,
                             graphop_stream_t stream);
 
+/* out[r, :] = tables[p][idx[r], :] for the rows r of segment p, seg[p] <= r < seg[p + 1] (`tables` and `seg` are host
+ * arrays of n_tables pointers and n_tables + 1 offsets, seg[0] = 0; n_tables <= GRAPHOP_MAX_PEERS).  The tables are
+ * the blocks of a row-sharded tensor on this and on peer GPUs, mapped into this process (CUDA IPC / symmetric memory):
+ * one kernel on the receiving GPU pulls every needed row across NVLink once, with plain peer loads, instead of the
+ * owners packing rows and a collective delivering them.  The caller orders the call after the owners' writes (and the
+ * owners' next writes after it).  Rows are row_bytes bytes, a multiple of 16; tables and out 16-byte aligned. */
+#define GRAPHOP_MAX_PEERS 16
+int graphop_pull_rows_i32(const void* const* tables, const int64_t* seg, int n_tables, const int32_t* idx,
+                          int64_t row_bytes, void* out, graphop_stream_t stream);
+
 /* Sufficient workspace for one call of `op`.  n_nodes: the largest node count among the
  * call's node tensors (for the softmax ops: an upper bound on node id + 1).  elem_bytes: 2, 4
  * or 8; index_bytes: 4 or 8. */

@@ -397,3 +397,21 @@ def test_gather_probe_status_codes():
     assert probe(None, 1000, table.data_ptr(), None, 512, sink.data_ptr(), st) == _capi.ERR_INVALID_ARGUMENT
     th.cuda.synchronize()
     assert int(sink.item()) == 0
+
+
+def test_pull_rows_reads_each_segment_from_its_own_table():
+    """graphop_pull_rows_i32 with both tables on this GPU (on several GPUs the tables are peer mappings): rows of
+    segment p come from table p, empty segments and segments of odd sizes included."""
+    gen = th.Generator(device=DEV).manual_seed(77)
+    tabs = [th.randn(n, 128, generator=gen, device=DEV) for n in (50, 1, 300)]
+    counts = [37, 0, 1001]
+    idx = [th.randint(0, t.size(0), (c,), generator=gen, device=DEV, dtype=th.int32) for t, c in zip(tabs, counts)]
+    seg = [0, 37, 37, 1038]
+    out = th.full((1038, 128), float("nan"), device=DEV)
+    graphop.pull_rows([t.data_ptr() for t in tabs], seg, th.cat(idx), 512, out)
+    want = th.cat([t[i.long()] for t, i in zip(tabs, idx)])
+    assert th.equal(out, want)
+    with pytest.raises(RuntimeError, match="seg"):
+        graphop.pull_rows([tabs[0].data_ptr()], seg, th.cat(idx), 512, out)
+    with pytest.raises(RuntimeError, match="unsupported|invalid"):
+        graphop.pull_rows([t.data_ptr() for t in tabs], seg, th.cat(idx), 500, out)      # rows must be 16-byte multiples

@@ -31,7 +31,8 @@ def _inputs():
 
 
 def _worker(rank, world, port, out_dir):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     th.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=th.device("cuda", rank))
     dev = "cuda:%d" % rank
@@ -49,6 +50,18 @@ def _worker(rank, world, port, out_dir):
     assert th.equal(x_rows.cpu(), x[ex.x.needed.cpu()])
     dw2, dx2 = sharding.sharded_spmm_backward(sh, w[lo:hi].to(dev), dy[r0:r1].to(dev), x_rows, exchange=ex)
     assert th.equal(y2, y) and th.equal(dw2, dw) and th.equal(dx2, dx)   # same rows, same order of summation
+    # the same rows pulled straight out of the peers' memory by one kernel per rank (no collective in the data path)
+    px = sharding.PeerRows(int(xb[rank + 1] - xb[rank]), (128,), th.float32, dev)
+    pdy = sharding.PeerRows(r1 - r0, (128,), th.float32, dev)
+    px.local.copy_(x[int(xb[rank]):int(xb[rank + 1])])
+    pdy.local.copy_(dy[r0:r1])
+    px.barrier()
+    pdy.barrier()
+    y3, x_rows3 = sharding.sharded_spmm_forward(sh, w[lo:hi].to(dev), px, exchange=ex)
+    dw3, dx3 = sharding.sharded_spmm_backward(sh, w[lo:hi].to(dev), pdy, x_rows3, exchange=ex)
+    th.cuda.synchronize()
+    dist.barrier()      # every rank is done reading its peers' blocks; only then may a rank fail and leave
+    assert th.equal(x_rows3, x_rows) and th.equal(y3, y) and th.equal(dw3, dw) and th.equal(dx3, dx)
     th.save({"y": y.cpu(), "dw": dw.cpu(), "dx": dx.cpu(), "rows": (r0, r1), "edges": (lo, hi),
              "cols": (int(sh.src_bounds[rank]), int(sh.src_bounds[rank + 1]))}, os.path.join(out_dir, "r%d.pt" % rank))
     dist.barrier()
