@@ -870,12 +870,15 @@ inline int attention_bias_forward(const GS& gs, long long C, const T* q, const T
     constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
     const long long cstride = HD + 2 * s.S;
     if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
-    else return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, [&](void* cout, void* cin) {
-      AttnFwdOp<T, V, R, true> op;
-      op.q = q; op.k = k; op.v = v; op.rel = rel; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout;
-      op.carry_in = (const A*)cin; op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
-      op.cstride = cstride;
-      return op;
+    else return dispatch_lph(D / V, [&](auto Lc) -> int {
+      constexpr int LPH = decltype(Lc)::value;
+      return run_row_levels(ar, g, tile0, n_dst, sizeof(A), cstride, st, [&](void* cout, void* cin) {
+        AttnFwdStaged<T, V, R, LPH, true> op;
+        op.q = q; op.k = k; op.v = v; op.rel = rel; op.o = o; op.lse = (A*)lse; op.carry = (A*)cout;
+        op.carry_in = (const A*)cin; op.scale = (A)scale; op.H = H; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+        op.cstride = cstride;
+        return op;
+      });
     });
   });
 }
@@ -914,12 +917,15 @@ inline int attention_bias_backward(const GS& gs_r, const GS& gs_c, bool has_eid_
     GK_TRY((dispatch_shape<T>(s, [&](auto Vc, auto Rc) -> int {
       constexpr int V = decltype(Vc)::value, R = decltype(Rc)::value;
       if constexpr (V == 1) return (int)GRAPHOP_ERR_UNSUPPORTED;
-      else return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, [&](void* cout, void* cin) {
-        AttnBwdDstOp<T, V, R, true> op;
-        op.q = q; op.k = k; op.v = v; op.rel = rel; op.o = o; op.dout = dout; op.lse = (const A*)lse; op.stat = stat;
-        op.pairs = pd; op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin; op.scale = (A)scale;
-        op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
-        return op;
+      else return dispatch_lph(D / V, [&](auto Lc) -> int {
+        constexpr int LPH = decltype(Lc)::value;
+        return run_row_levels(ar, g, tile0, n_dst, sizeof(A), HD, st, [&](void* cout, void* cin) {
+          AttnBwdDstStaged<T, V, R, LPH, true> op;
+          op.q = q; op.k = k; op.v = v; op.rel = rel; op.o = o; op.dout = dout; op.lse = (const A*)lse;
+          op.stat = stat; op.pd = pd; op.dq = dq; op.carry = (A*)cout; op.carry_in = (const A*)cin;
+          op.scale = (A)scale; op.H = H; op.Hp = Hp; op.D = D; op.HD = HD; op.S = s.S; op.lph = D / V;
+          return op;
+        });
       });
     })));
     {

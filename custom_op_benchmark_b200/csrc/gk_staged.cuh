@@ -648,23 +648,26 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
 // scale * log2(e) when a node starts, so a probability is one ex2 of a difference.
 // ring entry = [k row][v row]
 // ---------------------------------------------------------------------------------------
-template <typename T, int V, int R, int LPH>
-struct AttnFwdStaged : AttnFwdOp<T, V, R> {
-  using Base = AttnFwdOp<T, V, R>;
+// kBias: a third row per entry, the edge's row of `rel` laid out slot by slot like the key row (every head's lanes
+// copy the same D elements: they come out of L1 / L2), added to the key as it is read back.
+template <typename T, int V, int R, int LPH, bool kBias = false>
+struct AttnFwdStaged : AttnFwdOp<T, V, R, kBias> {
+  using Base = AttnFwdOp<T, V, R, kBias>;
   using A = typename Base::A;
   struct State : Base::State {
-    A qn[R][V]; int next_node; const unsigned char* kb[R]; const unsigned char* vb[R]; unsigned char* scratch;
+    A qn[R][V]; int next_node; const unsigned char* kb[R]; const unsigned char* vb[R]; const unsigned char* rb[R];
+    unsigned char* scratch;
   };
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
   using CarryIn = typename Base::CarryIn;
   static constexpr bool kFast = FastShape<R, LPH>::value;
-  using Ring = RingShape<T, R, 2, false, GK_CTAS_NARROW, kFastScratch, 0, kFast ? kFastBatch : 0>;
+  using Ring = RingShape<T, R, kBias ? 3 : 2, kBias, GK_CTAS_NARROW, kFastScratch, 0, kFast ? kFastBatch : 0>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr int kScratchBytes = kFast ? kFastScratch : 0;
-  static constexpr bool kUsesEid = false;
+  static constexpr bool kUsesEid = kBias;   // the edge term is indexed by edge id (the position, without an eid array)
 
   __device__ __forceinline__ void setup(State& st, int lane) const {
     Base::setup(st, lane);
@@ -673,6 +676,17 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
     for (int i = 0; i < R; ++i) {
       st.kb[i] = reinterpret_cast<const unsigned char*>(this->k + st.sm.feat[i]);
       st.vb[i] = reinterpret_cast<const unsigned char*>(this->v + st.sm.feat[i]);
+      st.rb[i] = kBias ? reinterpret_cast<const unsigned char*>(this->rel + st.sm.efeat[i]) : nullptr;
+    }
+  }
+  // the key slot of a ring entry, with the edge term added when there is one
+  __device__ __forceinline__ void load_key(A (&kv)[V], const unsigned char* entry, int slot) const {
+    lds_acc<T, V>(kv, entry + slot * 16);
+    if constexpr (kBias) {
+      A rv[V];
+      lds_acc<T, V>(rv, entry + 2 * Ring::kRowBytes + slot * 16);
+#pragma unroll
+      for (int e = 0; e < V; ++e) kv[e] += rv[e];
     }
   }
   __device__ __forceinline__ void prefetch_node(State& st, int node, int) const {
@@ -700,12 +714,15 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
 #pragma unroll
       for (int e = 0; e < V; ++e) st.q[i][e] *= c;
   }
-  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int edge, int lane) const {
     const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.kb[i], c, rowb));
       cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.vb[i], c, rowb));
+      if constexpr (kBias)
+        cp_async16(entry + 2 * Ring::kRowBytes + (lane + 32 * i) * 16,
+                   row_ptr(st.rb[i], edge, (unsigned)this->D * (unsigned)sizeof(T)));
     }
   }
   // Batch of U = 2 or 4 with one 16-byte slot per lane: the U partial dot products of a lane are reduced
@@ -720,7 +737,7 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
       s[u] = A(0);
       if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
         A kv[V];
-        lds_acc<T, V>(kv, GK_RING_SLOT(u) + lane * 16);
+        load_key(kv, GK_RING_SLOT(u), lane);
         s[u] = st.q[0][0] * kv[0];
 #pragma unroll
         for (int e = 1; e < V; ++e) s[u] += st.q[0][e] * kv[e];
@@ -769,7 +786,7 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         A kv[V];
-        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
+        load_key(kv, entry, lane + 32 * i);
         s[u][i] = A(0);
 #pragma unroll
         for (int e = 0; e < V; ++e) s[u][i] += st.q[i][e] * kv[e];
@@ -834,13 +851,13 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R> {
 // ---------------------------------------------------------------------------------------
 // Fused attention backward, destination side, staged.  ring entry = [k row][v row]
 // ---------------------------------------------------------------------------------------
-template <typename T, int V, int R, int LPH>
-struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
-  using Base = AttnBwdDstOp<T, V, R>;
+template <typename T, int V, int R, int LPH, bool kBias = false>
+struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R, kBias> {
+  using Base = AttnBwdDstOp<T, V, R, kBias>;
   using A = typename Base::A;
   struct State : Base::State {
     A qn[R][V]; A gn[R][V]; A on[R][V]; A lsen[R]; int next_node; int tile_base; int batch_pos;
-    const unsigned char* kb[R]; const unsigned char* vb[R];
+    const unsigned char* kb[R]; const unsigned char* vb[R]; const unsigned char* rb[R];
     unsigned char* pdw[R];  // where this lane writes its head's (p, ds) of edge 0, or null: not a writer
     unsigned char* scratch;
   };
@@ -850,12 +867,23 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
   static constexpr bool kFast = FastShape<R, LPH>::value;
-  using Ring = RingShape<T, R, 2, false, GK_CTAS_DST, kFastScratch, 0, kFast ? kFastBatch : 0>;
+  using Ring = RingShape<T, R, kBias ? 3 : 2, kBias, GK_CTAS_DST, kFastScratch, 0, kFast ? kFastBatch : 0>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr int kScratchBytes = kFast ? kFastScratch : 0;
-  static constexpr bool kUsesEid = false;
+  static constexpr bool kUsesEid = kBias;   // the edge term (see AttnFwdStaged) is indexed by edge id
   static constexpr bool kNodeRows = true;
+
+  // the key slot of a ring entry, with the edge term added when there is one (dq sums ds * (k + rel))
+  __device__ __forceinline__ void load_key(A (&kv)[V], const unsigned char* entry, int slot) const {
+    lds_acc<T, V>(kv, entry + slot * 16);
+    if constexpr (kBias) {
+      A rv[V];
+      lds_acc<T, V>(rv, entry + 2 * Ring::kRowBytes + slot * 16);
+#pragma unroll
+      for (int e = 0; e < V; ++e) kv[e] += rv[e];
+    }
+  }
 
   __device__ __forceinline__ void prefetch_rows_l2(int node) const {
     const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
@@ -872,6 +900,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
     for (int i = 0; i < R; ++i) {
       st.kb[i] = reinterpret_cast<const unsigned char*>(this->k + st.sm.feat[i]);
       st.vb[i] = reinterpret_cast<const unsigned char*>(this->v + st.sm.feat[i]);
+      st.rb[i] = kBias ? reinterpret_cast<const unsigned char*>(this->rel + st.sm.efeat[i]) : nullptr;
       // the slow path writes a head's pair from the lane that holds the head's first slot; the fast path from
       // the first U lanes of the head's group, lane j writing edge j of the batch
       const bool writer = kFast ? (lane & (LPH - 1)) < kFastBatch : st.sm.efeat[i] == 0;
@@ -896,7 +925,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
       if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
         const unsigned char* entry = GK_RING_SLOT(u);
         A kv[V], vv[V];
-        lds_acc<T, V>(kv, entry + lane * 16);
+        load_key(kv, entry, lane);
         lds_acc<T, V>(vv, entry + Ring::kRowBytes + lane * 16);
         s[u] = st.q[0][0] * kv[0];
         dp[u] = st.g[0][0] * vv[0];
@@ -924,7 +953,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
     for (int u = 0; u < U; ++u) {
       if (kFullBatch || u < cnt) {
         A kv[V];
-        lds_acc<T, V>(kv, GK_RING_SLOT(u) + lane * 16);
+        load_key(kv, GK_RING_SLOT(u), lane);
 #pragma unroll
         for (int e = 0; e < V; ++e) st.acc[0][e] += dsv[u] * kv[e];
       }
@@ -980,12 +1009,15 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
       for (int e = 0; e < V; ++e) st.q[i][e] *= c;
     }
   }
-  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int, int lane) const {
+  __device__ __forceinline__ void stage(const State& st, unsigned char* entry, int c, int edge, int lane) const {
     const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.kb[i], c, rowb));
       cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.vb[i], c, rowb));
+      if constexpr (kBias)
+        cp_async16(entry + 2 * Ring::kRowBytes + (lane + 32 * i) * 16,
+                   row_ptr(st.rb[i], edge, (unsigned)this->D * (unsigned)sizeof(T)));
     }
   }
   template <bool kFullBatch>
@@ -1003,7 +1035,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         A kv[V], vv[V];
-        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
+        load_key(kv, entry, lane + 32 * i);
         lds_acc<T, V>(vv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
         s[u][i] = A(0);
         dp[u][i] = A(0);
@@ -1023,7 +1055,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R> {
           *reinterpret_cast<EdgePair<A>*>(st.pdw[i] + (unsigned long long)(unsigned)(st.tile_base + st.batch_pos + u) * pairb) =
               EdgePair<A>{p, ds};
         A kv[V];
-        lds_acc<T, V>(kv, entry + (lane + 32 * i) * 16);
+        load_key(kv, entry, lane + 32 * i);
 #pragma unroll
         for (int e = 0; e < V; ++e) st.acc[i][e] += ds * kv[e];
       }

@@ -413,5 +413,5 @@ def test_pull_rows_reads_each_segment_from_its_own_table():
     assert th.equal(out, want)
     with pytest.raises(RuntimeError, match="seg"):
         graphop.pull_rows([tabs[0].data_ptr()], seg, th.cat(idx), 512, out)
-    with pytest.raises(RuntimeError, match="unsupported|invalid"):
+    with pytest.raises(RuntimeError, match="not supported"):
         graphop.pull_rows([t.data_ptr() for t in tabs], seg, th.cat(idx), 500, out)      # rows must be 16-byte multiples
