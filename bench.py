@@ -566,15 +566,24 @@ class ShardedSpmmWorkload:
         self.dy_local = hashed_normal(ar(int(sh.dst_bounds[rank]), sh.rows), self.d, 13)
         self.host = [_pinned(self.x_shard.cpu()), _pinned(self.dy_local.cpu())]
         self.outs = [_pinned(th.empty(sh.rows, self.d)), _pinned(th.empty(sh.cols, self.d))]
+        self.peer_note = None
         if self.peer:
             # the two row-sharded inputs live in symmetric memory: every rank pulls the rows it references out of the
             # owners' blocks with one kernel (plain peer loads over NVLink), no collective in the data path
-            self.px = sharding.PeerRows(rows_x, (self.d,), th.float32, dev)
-            self.pdy = sharding.PeerRows(sh.rows, (self.d,), th.float32, dev)
-            self.px.local.copy_(self.x_shard)
-            self.pdy.local.copy_(self.dy_local)
-            self.px.barrier()
-            self.pdy.barrier()
+            try:
+                self.px = sharding.PeerRows(rows_x, (self.d,), th.float32, dev)
+                self.pdy = sharding.PeerRows(sh.rows, (self.d,), th.float32, dev)
+                ok = th.ones(1, device=dev)
+            except Exception as exc:       # no peer mapping on this machine: the all-to-all of packed rows instead
+                self.peer_note = "symmetric memory unavailable (%s): all-to-all used" % str(exc)[:100]
+                ok = th.zeros(1, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)      # the ranks agree on one path
+            self.peer = bool(ok.item() > 0)
+            if self.peer:
+                self.px.local.copy_(self.x_shard)
+                self.pdy.local.copy_(self.dy_local)
+                self.px.barrier()
+                self.pdy.barrier()
         s, i = 4, 4
         e_loc, e_t = sh.indices.numel(), sh.eid_t.numel()
         F = lambda n: n * self.h * self.d * s
@@ -684,6 +693,8 @@ class ShardedSpmmWorkload:
                     ("dy", lambda: sharding.all_gather_rows(self.dy_local, self.sh.dst_bounds)))
         out = {"kind": "referenced rows pulled from the peers' memory by one kernel per rank" if self.peer else
                ("all-to-all of the referenced rows" if self.ex is not None else "all-gather of every row")}
+        if self.peer_note:
+            out["note_peer"] = self.peer_note
         for name, leg in legs:
             leg()
             th.cuda.synchronize()
@@ -1411,7 +1422,7 @@ def main():
     ap.add_argument("--scale", type=int, default=0, help="override the R-MAT scale (smaller runs)")
     ap.add_argument("--cpu-sample-scale", type=int, default=19)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="needed", choices=["needed", "all", "peer"],
+    ap.add_argument("--exchange", default="peer", choices=["needed", "all", "peer"],
                     help="sharded workload: fetch only the node rows a shard references (all-to-all), all-gather every "
                          "row, or pull the referenced rows out of the peers' memory with a kernel (symmetric memory)")
     ap.add_argument("--sharded", default="auto", choices=["auto", "off"],

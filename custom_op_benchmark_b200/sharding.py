@@ -239,12 +239,6 @@ class PeerRows:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         group = group or dist.group.WORLD
-        enable = getattr(symm, "enable_symm_mem_for_group", None)
-        if enable is not None:            # needed by older torch releases, a no-op on newer ones
-            try:
-                enable(group.group_name)
-            except Exception:
-                pass
         world = dist.get_world_size(group)
         counts = [th.zeros(1, dtype=th.int64, device=device) for _ in range(world)]
         dist.all_gather(counts, th.tensor([rows], dtype=th.int64, device=device), group=group)
