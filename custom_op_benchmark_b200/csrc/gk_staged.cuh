@@ -577,7 +577,9 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
-  using Ring = RingShape<T, R, 1, true>;
+  // batches of 2 for one-slot rows: measured against 4 (the most the ring would hold) and 1 on R-MAT 21 and Zipf 50M,
+  // 5.15 / 6.13 / 5.70 ms and 3.66 / 4.03 / 3.96 ms per step's two launches
+  using Ring = RingShape<T, R, 1, true, GK_CTAS_NARROW, 0, 0, R == 1 ? 2 : 0>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
   static constexpr bool kUsesEid = true;
