@@ -62,6 +62,18 @@ def test_config2_banded_bf16_fused_chain_full_size():
     assert_rows(dq, wq, deg, "dq", rtol=2e-2, atol=5e-2)
     assert_rows(dk, wk, deg_t, "dk", rtol=2e-2, atol=5e-2)
     assert_rows(dv, wv, deg_t, "dv", rtol=2e-2, atol=5e-2)
+    # the same step through graph plans: a dense band in bfloat16 with 64 features runs on the tensor-core kernels
+    plan_r = graphop.GraphPlan(*R, g.n_dst)
+    plan_t = graphop.GraphPlan(*C, g.n_src)
+    assert plan_r.dense_band and plan_t.dense_band and plan_r.band_span == 128 + 2 * 128
+    o2, lse2 = graphop.attention_forward_planned(plan_r, Q, K, V, scale)
+    dq2, dk2, dv2 = graphop.attention_backward_planned(plan_r, plan_t, Q, K, V, o2, lse2, dO, scale)
+    assert_rows(o2, wo, deg, "o (tensor cores)", rtol=2e-2, atol=2e-2)
+    assert_rows(lse2, wl, deg, "lse (tensor cores)", rtol=1e-5, atol=2e-3)
+    assert_rows(dq2, wq, deg, "dq (tensor cores)", rtol=2e-2, atol=5e-2)
+    assert_rows(dk2, wk, deg_t, "dk (tensor cores)", rtol=2e-2, atol=5e-2)
+    assert_rows(dv2, wv, deg_t, "dv (tensor cores)", rtol=2e-2, atol=5e-2)
+    assert not bool(th.isnan(o2).any() | th.isnan(dq2).any() | th.isnan(dk2).any() | th.isnan(dv2).any())
 
 
 @pytest.fixture(scope="module")
