@@ -13,6 +13,7 @@ Differences from the reference, all supersets: index tensors may be int32 as wel
 and float64; ``dy`` is made contiguous instead of being read unchecked
 (graphop.cpp:120-130, 148-153); the source and destination node counts may differ.
 """
+import collections
 import weakref
 
 import torch as th
@@ -478,6 +479,30 @@ class GraphPlan:
     def ref(self):
         import ctypes
         return ctypes.byref(self.c)
+
+
+plan_cache_size = 8      # plans kept by cached_plan(); 0 switches the cache off
+_PLAN_CACHE = collections.OrderedDict()
+
+
+def cached_plan(row, indptr, eid, indices, n_nodes):
+    """The GraphPlan of these index tensors, built on first use and kept while the same tensor objects come back
+    unmodified (identity and torch's version counter; the most recent ``plan_cache_size`` plans are kept).  This is
+    what lets the entry points that take (row, indptr, eid, indices) per call - the reference's calling convention -
+    run at the speed of the planned ones: a training loop passes the same graph tensors every step."""
+    tensors = (row, indptr, eid, indices)
+    if plan_cache_size <= 0:
+        return GraphPlan(row, indptr, eid, indices, n_nodes)
+    key = tuple((id(t), t._version) if t is not None else None for t in tensors) + (int(n_nodes),)
+    hit = _PLAN_CACHE.get(key)
+    if hit is not None and all(a is b for a, b in zip(hit._keep, tensors)):
+        _PLAN_CACHE.move_to_end(key)
+        return hit
+    plan = GraphPlan(row, indptr, eid, indices, n_nodes)
+    _PLAN_CACHE[key] = plan
+    while len(_PLAN_CACHE) > plan_cache_size:
+        _PLAN_CACHE.popitem(last=False)
+    return plan
 
 
 def _call_planned(name, elem, op_id, plans, n_nodes, h, d, device, args):

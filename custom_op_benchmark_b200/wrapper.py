@@ -87,7 +87,15 @@ class GraphAttention(Function):
 
     @staticmethod
     def forward(ctx, row, indptr, indices, col, indptr_t, indices_t, Q, K, V, scale, eid_t=None):
-        o, lse = _g.attention_forward(row, indptr, indices, Q, K, V, scale)
+        cached = getattr(_g, "cached_plan", None)
+        if cached is not None and getattr(_g, "plan_cache_size", 0) > 0 and indices.numel() > 0:
+            # the same graph tensors come back every step: their plans are built once and looked up here, so this
+            # per-call signature runs the planned kernels (and, on a dense band in bfloat16, the tensor-core ones)
+            ctx.plans = (cached(row, indptr, None, indices, Q.size(0)), cached(col, indptr_t, eid_t, indices_t, K.size(0)))
+            o, lse = _g.attention_forward_planned(ctx.plans[0], Q, K, V, scale)
+        else:
+            ctx.plans = None
+            o, lse = _g.attention_forward(row, indptr, indices, Q, K, V, scale)
         ctx.save_for_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse)
         ctx.scale = scale
         ctx.eid_t = eid_t
@@ -96,8 +104,11 @@ class GraphAttention(Function):
     @staticmethod
     def backward(ctx, d_o):
         row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse = ctx.saved_tensors
-        dq, dk, dv = _g.attention_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse, d_o,
-                                           ctx.scale, eid_t=ctx.eid_t)
+        if ctx.plans is not None:
+            dq, dk, dv = _g.attention_backward_planned(ctx.plans[0], ctx.plans[1], Q, K, V, o, lse, d_o, ctx.scale)
+        else:
+            dq, dk, dv = _g.attention_backward(row, indptr, indices, col, indptr_t, indices_t, Q, K, V, o, lse, d_o,
+                                               ctx.scale, eid_t=ctx.eid_t)
         return None, None, None, None, None, None, dq, dk, dv, None, None
 
 

@@ -149,3 +149,36 @@ def test_dense_band_attention_forward_on_tensor_cores(make, h):
     _, _, wq, wk, wv = ref.attention_f64(g.indptr.to(DEV), g.indices.to(DEV), Q, K, V, scale, dO)
     for got, want, what in ((dq, wq, "dq"), (dk, wk, "dk"), (dv, wv, "dv")):
         assert_close(got, want, 2e-2, 5e-2 * max(1.0, float(want.abs().max())), what)
+
+
+def test_per_call_signature_runs_on_cached_plans():
+    """wrapper.GraphAttention takes the graph tensors per call (the reference's convention); their plans are built
+    once and found again, so a dense band in bfloat16 reaches the tensor-core kernels through that signature too."""
+    g = graphs.banded_graph(1, 640, 64)
+    rc, cc, pr, pt = _plans(g, 32, th.int32)
+    gen = th.Generator(device=DEV).manual_seed(14)
+    Q, K, V, dO = (th.randn(g.n_dst, 4, 64, generator=gen, device=DEV).to(th.bfloat16) for _ in range(4))
+    graphop._PLAN_CACHE.clear()
+    outs = []
+    for _ in range(2):
+        q, k, v = (t.clone().requires_grad_(True) for t in (Q, K, V))
+        o = wrapper.GraphAttention.apply(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], q, k, v, 0.125, cc[2])
+        o.backward(dO)
+        outs.append((o.detach(), q.grad, k.grad, v.grad))
+    assert len(graphop._PLAN_CACHE) == 2                       # one plan per orientation, built once
+    assert all(p.dense_band for p in graphop._PLAN_CACHE.values())
+    q, k, v = (t.clone().requires_grad_(True) for t in (Q, K, V))
+    wrapper.GraphAttentionPlanned.apply(pr, pt, q, k, v, 0.125).backward(dO)
+    for a, b, c in zip(outs[0][1:], outs[1][1:], (q.grad, k.grad, v.grad)):
+        assert th.equal(a, b) and th.equal(a, c)
+    # a graph tensor modified in place gets a new plan
+    rc[3].add_(0)
+    assert graphop.cached_plan(rc[0], rc[1], None, rc[3], g.n_dst) not in list(graphop._PLAN_CACHE.values())[:2]
+    # and the cache can be switched off
+    old, graphop.plan_cache_size = graphop.plan_cache_size, 0
+    try:
+        q2 = Q.clone().requires_grad_(True)
+        o2 = wrapper.GraphAttention.apply(rc[0], rc[1], rc[3], cc[0], cc[1], cc[3], q2, K, V, 0.125, cc[2])
+        assert_close(o2, outs[0][0].double(), 2e-2, 2e-2, "walker against tensor cores")
+    finally:
+        graphop.plan_cache_size = old
