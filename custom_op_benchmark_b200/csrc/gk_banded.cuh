@@ -13,7 +13,8 @@
 //   * each of the 128 threads owns one query row: it reads the row from tensor memory (tcgen05.ld), masks the columns
 //     outside its node's range, takes max and sum, and writes the probabilities as bf16 into shared memory;
 //   * a second tcgen05.mma chain multiplies them with V; the thread scales its output row by 1 / sum and stores it.
-// Everything a tile needs lives on chip: 208 KB of shared memory and 448 of the 512 tensor-memory columns.
+// Everything a tile needs lives on chip: 208 KB of shared memory and 448 of the 512 tensor-memory columns; one block
+// per SM walks its share of the tiles and loads the next tile's operands while the current tile's softmax runs.
 // Every wait on an mbarrier is bounded; a tile whose wait runs out writes NaN to its rows of O instead of hanging.
 #pragma once
 #include <cuda.h>
@@ -159,6 +160,9 @@ struct Params {
   float scale;
 };
 
+// One block per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (t = tile of 128 nodes * H + head).  While
+// a tile's softmax runs, the next tile's Q and K are already on their way into the shared memory the score products
+// have released, and its V follows once the second product chain is done: a tile does not start with an idle load.
 __global__ void __launch_bounds__(kThreads, 1)
 attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -175,20 +179,8 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int quarter = warp & 3, cg = warp >> 2;                // tensor-memory lane quarter, column group
   const int row = quarter * 32 + lane;                         // row of the tile = tensor-memory lane
-  const int head = blockIdx.y;
-  const long long r0 = (long long)blockIdx.x * kTileM;
-  const long long r = r0 + row;
+  const long long n_tiles = (p.n_dst + kTileM - 1) / kTileM * p.H;
 
-  // this thread's node: first neighbour and count
-  int lo = INT_MAX, deg = 0;
-  if (r < p.n_dst) {
-    deg = p.node_deg[r];
-    if (deg > 0) lo = p.node_lo[r];
-  }
-  int wmin = lo;
-#pragma unroll
-  for (int o = 16; o; o >>= 1) wmin = min(wmin, __shfl_xor_sync(kFull, wmin, o));
-  if (lane == 0 && cg == 0) s_red[quarter] = wmin;
   if (tid == 0) {
     mbar_init(bar_load, 1);
     mbar_init(bar_s, 1);
@@ -202,138 +194,217 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+
+  // a tile's node range and first key: every thread its own row, the minimum over the tile through shared memory
+  auto tile_rows = [&](long long t, int& lo, int& deg) {
+    lo = INT_MAX;
+    deg = 0;
+    const long long r = t / p.H * kTileM + row;
+    if (t < n_tiles && r < p.n_dst) {
+      deg = p.node_deg[r];
+      if (deg > 0) lo = p.node_lo[r];
+    }
+    int wmin = lo;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) wmin = min(wmin, __shfl_xor_sync(kFull, wmin, o));
+    if (lane == 0 && cg == 0) s_red[quarter] = wmin;
+  };
+  auto issue_qk = [&](long long t, int kmin) {   // one thread
+    mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * (1 + kSpan / kKeyBlock)));
+    tma_load_3d(s_base + kOffQ, &map_q, bar_load, 0, (int)(t % p.H), (int)(t / p.H * kTileM));
+#pragma unroll
+    for (int b = 0; b < kSpan / kKeyBlock; ++b)
+      tma_load_3d(s_base + kOffK + b * kBlockBytes, &map_k, bar_load, 0, (int)(t % p.H), kmin + b * kKeyBlock);
+  };
+  auto issue_v = [&](long long t, int kmin) {    // one thread
+    mbar_expect_tx(bar_v, (uint32_t)(kBlockBytes * (kSpan / kKeyBlock)));
+#pragma unroll
+    for (int b = 0; b < kSpan / kKeyBlock; ++b)
+      tma_load_3d(s_base + kOffV + b * kBlockBytes, &map_v, bar_v, 0, (int)(t % p.H), kmin + b * kKeyBlock);
+  };
+
+  long long t = blockIdx.x;
+  int lo, deg;
+  tile_rows(t, lo, deg);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  const int kmin = min(min(s_red[0], s_red[1]), min(s_red[2], s_red[3]));
+  int kmin = min(min(s_red[0], s_red[1]), min(s_red[2], s_red[3]));
+  __syncthreads();   // s_red is rewritten for the next tile below
+  if (tid == 0 && t < n_tiles && kmin != INT_MAX) {
+    issue_qk(t, kmin);
+    issue_v(t, kmin);
+  }
   bool ok = true;
+  uint32_t phase = 0;          // tiles this block has loaded so far, mod 2: the parity of all four barriers
+  bool pending_qk = false, pending_v = false;   // loads issued for the next tile (what to wait for if this one fails)
+  const uint32_t row_taddr = tmem + ((uint32_t)(quarter * 32) << 16);
+  const float sl2 = p.scale * 1.4426950408889634f;
 
-  if (kmin != INT_MAX) {  // some node of the tile has neighbours
-    if (tid == 0) {
-      // queries and keys first: the scores start as soon as they are in; the values land during the softmax
-      mbar_expect_tx(bar_load, (uint32_t)(kBlockBytes * (1 + kSpan / kKeyBlock)));
-      tma_load_3d(s_base + kOffQ, &map_q, bar_load, 0, head, (int)r0);
+  for (; t < n_tiles; t += gridDim.x) {
+    const int head = (int)(t % p.H);
+    const long long r = t / p.H * kTileM + row;
+    const long long t_next = t + gridDim.x;
+    int lo_n, deg_n;
+    tile_rows(t_next, lo_n, deg_n);      // s_red: the next tile's minima, read after the next block-wide barrier
+    pending_qk = pending_v = false;
+
+    if (kmin != INT_MAX) {  // some node of the tile has neighbours: its Q, K (and V) are on their way
+      ok = __syncthreads_and(mbar_wait(bar_load, phase));   // the same verdict in every thread
+      const int kmin_n = min(min(s_red[0], s_red[1]), min(s_red[2], s_red[3]));
+      if (ok && tid == 0) {
+        // scores: for each block of 128 keys, 4 steps of 16 features
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        constexpr uint32_t idesc = umma_idesc(kTileM, kKeyBlock, false);
 #pragma unroll
-      for (int b = 0; b < kSpan / kKeyBlock; ++b)
-        tma_load_3d(s_base + kOffK + b * kBlockBytes, &map_k, bar_load, 0, head, kmin + b * kKeyBlock);
-      mbar_expect_tx(bar_v, (uint32_t)(kBlockBytes * (kSpan / kKeyBlock)));
+        for (int b = 0; b < kSpan / kKeyBlock; ++b) {
 #pragma unroll
-      for (int b = 0; b < kSpan / kKeyBlock; ++b)
-        tma_load_3d(s_base + kOffV + b * kBlockBytes, &map_v, bar_v, 0, head, kmin + b * kKeyBlock);
-    }
-    ok = __syncthreads_and(mbar_wait(bar_load, 0));   // the same verdict in every thread
-    if (ok && tid == 0) {
-      // scores: for each block of 128 keys, 4 steps of 16 features
+          for (int kk = 0; kk < kD / 16; ++kk) {
+            const uint64_t a = umma_desc(s_base + kOffQ + kk * 32, 16, 1024);
+            const uint64_t bd = umma_desc(s_base + kOffK + b * kBlockBytes + kk * 32, 16, 1024);
+            umma_f16(tmem + b * kKeyBlock, a, bd, idesc, kk > 0);
+          }
+        }
+        umma_commit(bar_s);
+      }
+      ok = __syncthreads_and(ok && mbar_wait(bar_s, phase));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      constexpr uint32_t idesc = umma_idesc(kTileM, kKeyBlock, false);
+      // the score products are done with Q and K: the next tile's may land there while this tile's softmax runs
+      const bool more = ok && t_next < n_tiles && kmin_n != INT_MAX;
+      if (more && tid == 0) issue_qk(t_next, kmin_n);
+      pending_qk = more;
+
+      // this thread's row: columns [jlo, jhi] are its node's neighbours; it handles chunks cg, cg + 4, cg + 8
+      const int jlo = deg > 0 ? lo - kmin : 1, jhi = deg > 0 ? lo - kmin + deg - 1 : 0;
+      int wlo = deg > 0 ? jlo : INT_MAX, whi = deg > 0 ? jhi : -1;
 #pragma unroll
-      for (int b = 0; b < kSpan / kKeyBlock; ++b) {
+      for (int o = 16; o; o >>= 1) {
+        wlo = min(wlo, __shfl_xor_sync(kFull, wlo, o));
+        whi = max(whi, __shfl_xor_sync(kFull, whi, o));
+      }
+      const int c_first = wlo == INT_MAX ? 0 : wlo / 32, c_last = whi < 0 ? -1 : whi / 32;   // warp-uniform chunk range
+      float m = -INFINITY;
+      for (int c = cg; c < kSpan / 32; c += kColGroups) {
+        if (ok && c >= c_first && c <= c_last) {
+          float v[32];
+          tmem_ld32(row_taddr + c * 32, v);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint64_t a = umma_desc(s_base + kOffQ + kk * 32, 16, 1024);
-          const uint64_t bd = umma_desc(s_base + kOffK + b * kBlockBytes + kk * 32, 16, 1024);
-          umma_f16(tmem + b * kKeyBlock, a, bd, idesc, kk > 0);
+          for (int j = 0; j < 32; ++j) {
+            const int col = c * 32 + j;
+            if (col >= jlo && col <= jhi) m = fmaxf(m, v[j]);
+          }
         }
       }
-      umma_commit(bar_s);
-    }
-    ok = __syncthreads_and(ok && mbar_wait(bar_s, 0));
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-    // this thread's row: columns [jlo, jhi] are its node's neighbours; it handles chunks cg, cg + 4, cg + 8
-    const int jlo = deg > 0 ? lo - kmin : 1, jhi = deg > 0 ? lo - kmin + deg - 1 : 0;
-    int wlo = deg > 0 ? jlo : INT_MAX, whi = deg > 0 ? jhi : -1;
+      s_max[cg * kTileM + row] = m;
+      __syncthreads();
 #pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      wlo = min(wlo, __shfl_xor_sync(kFull, wlo, o));
-      whi = max(whi, __shfl_xor_sync(kFull, whi, o));
-    }
-    const int c_first = wlo == INT_MAX ? 0 : wlo / 32, c_last = whi < 0 ? -1 : whi / 32;   // warp-uniform chunk range
-    const uint32_t row_taddr = tmem + ((uint32_t)(quarter * 32) << 16);
-    const float sl2 = p.scale * 1.4426950408889634f;
-    float m = -INFINITY;
-    for (int c = cg; c < kSpan / 32; c += kColGroups) {
-      if (ok && c >= c_first && c <= c_last) {
+      for (int g = 0; g < kColGroups; ++g) m = fmaxf(m, s_max[g * kTileM + row]);
+      const float msl2 = deg > 0 ? m * sl2 : 0.f;
+      float l = 0.f;
+      unsigned char* prow = smem + kOffP + row * kRowBytes;   // this row inside each 64-key panel
+      for (int c = cg; c < kSpan / 32; c += kColGroups) {
         float v[32];
-        tmem_ld32(row_taddr + c * 32, v);
+        const bool live = ok && c >= c_first && c <= c_last;
+        if (live) tmem_ld32(row_taddr + c * 32, v);
+        uint32_t packed[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = c * 32 + j;
-          if (col >= jlo && col <= jhi) m = fmaxf(m, v[j]);
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = 0.f, p1 = 0.f;
+          if (live) {
+            const int col = c * 32 + j;
+            if (col >= jlo && col <= jhi) p0 = exp2_fast(fmaf(v[j], sl2, -msl2));
+            if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2_fast(fmaf(v[j + 1], sl2, -msl2));
+          }
+          l += p0 + p1;
+          packed[j / 2] = pack_bf16(p0, p1);
+        }
+        // 32 keys = 4 chunks of 16 bytes in panel c / 2, at chunk index (c & 1) * 4 + q, swizzled by the row
+        unsigned char* panel = prow + (c >> 1) * kBlockBytes;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
+          *reinterpret_cast<uint4*>(panel + chunk * 16) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
         }
       }
-    }
-    s_max[cg * kTileM + row] = m;
-    __syncthreads();
+      s_sum[cg * kTileM + row] = l;
+      // the probabilities were written through the generic proxy; the tensor core reads through the async proxy
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      ok = __syncthreads_and(ok && mbar_wait(bar_v, phase));   // probabilities written by all, values landed
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      l = 0.f;
 #pragma unroll
-    for (int g = 0; g < kColGroups; ++g) m = fmaxf(m, s_max[g * kTileM + row]);
-    const float msl2 = deg > 0 ? m * sl2 : 0.f;
-    float l = 0.f;
-    unsigned char* prow = smem + kOffP + row * kRowBytes;   // this row inside each 64-key panel
-    for (int c = cg; c < kSpan / 32; c += kColGroups) {
-      float v[32];
-      const bool live = ok && c >= c_first && c <= c_last;
-      if (live) tmem_ld32(row_taddr + c * 32, v);
-      uint32_t packed[16];
+      for (int g = 0; g < kColGroups; ++g) l += s_sum[g * kTileM + row];
+      if (ok && tid == 0) {
+        constexpr uint32_t idesc = umma_idesc(kTileM, kD, true);
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        float p0 = 0.f, p1 = 0.f;
-        if (live) {
-          const int col = c * 32 + j;
-          if (col >= jlo && col <= jhi) p0 = exp2_fast(fmaf(v[j], sl2, -msl2));
-          if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2_fast(fmaf(v[j + 1], sl2, -msl2));
+        for (int ks = 0; ks < kSpan / 16; ++ks) {
+          const uint64_t a = umma_desc(s_base + kOffP + (ks >> 2) * kBlockBytes + (ks & 3) * 32, 16, 1024);
+          const uint64_t bd = umma_desc(s_base + kOffV + ks * 16 * kRowBytes, 16, 1024);
+          umma_f16(tmem + kColO, a, bd, idesc, ks > 0);
         }
-        l += p0 + p1;
-        packed[j / 2] = pack_bf16(p0, p1);
+        umma_commit(bar_o);
       }
-      // 32 keys = 4 chunks of 16 bytes in panel c / 2, at chunk index (c & 1) * 4 + q, swizzled by the row
-      unsigned char* panel = prow + (c >> 1) * kBlockBytes;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
-        *reinterpret_cast<uint4*>(panel + chunk * 16) =
-            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      }
-    }
-    s_sum[cg * kTileM + row] = l;
-    // the probabilities were written through the generic proxy; the tensor core reads through the async proxy
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    ok = __syncthreads_and(ok && mbar_wait(bar_v, 0));   // probabilities written by all, values landed
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    l = 0.f;
-#pragma unroll
-    for (int g = 0; g < kColGroups; ++g) l += s_sum[g * kTileM + row];
-    if (ok && tid == 0) {
-      constexpr uint32_t idesc = umma_idesc(kTileM, kD, true);
-#pragma unroll
-      for (int ks = 0; ks < kSpan / 16; ++ks) {
-        const uint64_t a = umma_desc(s_base + kOffP + (ks >> 2) * kBlockBytes + (ks & 3) * 32, 16, 1024);
-        const uint64_t bd = umma_desc(s_base + kOffV + ks * 16 * kRowBytes, 16, 1024);
-        umma_f16(tmem + kColO, a, bd, idesc, ks > 0);
-      }
-      umma_commit(bar_o);
-    }
-    ok = __syncthreads_and(ok && mbar_wait(bar_o, 0));
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      ok = __syncthreads_and(ok && mbar_wait(bar_o, phase));
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // the second product chain is done with V: the next tile's may land
+      if (ok && pending_qk && tid == 0) issue_v(t_next, kmin_n);
+      pending_v = ok && pending_qk;
 
-    // this thread's 16 of the row's 64 output features
-    float v[16];
-    if (ok) tmem_ld16(row_taddr + kColO + cg * 16, v);   // warp-wide, whether or not the lane's row exists
-    if (r < p.n_dst) {
-      if (ok && deg == 0) {
+      // this thread's 16 of the row's 64 output features
+      float v[16];
+      if (ok) tmem_ld16(row_taddr + kColO + cg * 16, v);   // warp-wide, whether or not the lane's row exists
+      if (r < p.n_dst) {
+        if (ok && deg == 0) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+        store_out16(p.o + ((long long)r * p.H + head) * kD + cg * 16, v, deg > 0 ? 1.f / l : 0.f, ok);
+        if (cg == 0) p.lse[(long long)r * p.H + head] = !ok ? NAN : (deg > 0 ? m * p.scale + logf(l) : -INFINITY);
       }
-      store_out16(p.o + ((long long)r * p.H + head) * kD + cg * 16, v, deg > 0 ? 1.f / l : 0.f, ok);
-      if (cg == 0) p.lse[(long long)r * p.H + head] = !ok ? NAN : (deg > 0 ? m * p.scale + logf(l) : -INFINITY);
-    }
-  } else if (r < p.n_dst && cg == 0) {  // no node of the tile has a neighbour
-    __nv_bfloat16* orow = p.o + ((long long)r * p.H + head) * kD;
+      phase ^= 1u;
+      kmin = kmin_n;
+      // tensor memory is read (scores, output) before the next tile's products overwrite it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      if (!ok) break;
+    } else {
+      // no node of the tile has a neighbour: nothing was loaded; zeros, and the next tile's loads start here
+      __syncthreads();
+      const int kmin_n = min(min(s_red[0], s_red[1]), min(s_red[2], s_red[3]));
+      if (r < p.n_dst && cg == 0) {
+        __nv_bfloat16* orow = p.o + ((long long)r * p.H + head) * kD;
 #pragma unroll
-    for (int q = 0; q < kD / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
-    p.lse[(long long)r * p.H + head] = -INFINITY;
+        for (int q = 0; q < kD / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(0, 0, 0, 0);
+        p.lse[(long long)r * p.H + head] = -INFINITY;
+      }
+      if (tid == 0 && t_next < n_tiles && kmin_n != INT_MAX) {
+        issue_qk(t_next, kmin_n);
+        issue_v(t_next, kmin_n);
+      }
+      kmin = kmin_n;
+    }
+    lo = lo_n;
+    deg = deg_n;
+    __syncthreads();   // s_red and the reduction rows are free for the next tile
+  }
+
+  if (!ok) {
+    // a wait ran out: this tile's rows hold NaN already; so do the rows of the tiles this block will not reach.
+    // Loads issued for the next tile are given (bounded) time to land before the shared memory is handed back.
+    if (pending_qk) mbar_wait(bar_load, phase);
+    if (pending_v) mbar_wait(bar_v, phase);
+    for (long long u = t + gridDim.x; u < n_tiles; u += gridDim.x) {
+      const long long r = u / p.H * kTileM + row;
+      if (r < p.n_dst && cg == 0) {
+        __nv_bfloat16* orow = p.o + ((long long)r * p.H + (int)(u % p.H)) * kD;
+        const uint32_t nan2 = pack_bf16(NAN, NAN);
+#pragma unroll
+        for (int q = 0; q < kD / 8; ++q) *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(nan2, nan2, nan2, nan2);
+        p.lse[(long long)r * p.H + (int)(u % p.H)] = NAN;
+      }
+    }
   }
 
   // every thread is done with tensor memory: hand it back
@@ -674,7 +745,12 @@ inline int banded_attention_forward<__nv_bfloat16>(const graphop_plan_t* plan, c
   Params p;
   p.o = o; p.lse = (float*)lse; p.node_lo = plan->node_lo; p.node_deg = plan->node_deg; p.n_dst = n_dst; p.H = H;
   p.scale = (float)scale;
-  const dim3 grid((unsigned)((n_dst + kTileM - 1) / kTileM), (unsigned)H);
+  // one block per SM (the kernel's shared memory and tensor memory allow no second one), each walking its share of
+  // the (tile, head) pairs
+  int sms = 0;
+  GK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const long long n_tiles = (n_dst + kTileM - 1) / kTileM * H;
+  const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);
   attention_forward_kernel<<<grid, kThreads, kSmemBytes, st>>>(mq, mk, mv, p);
   GK_LAUNCHED("attention_fwd_banded");
   return GRAPHOP_OK;
