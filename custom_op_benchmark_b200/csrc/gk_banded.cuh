@@ -114,6 +114,44 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Two 32-column loads (two regions of the same lane) in flight together, one wait for both.  The wait names every
+// destination register as an operand, so that no use of the values can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld32_pair(uint32_t taddr_a, uint32_t taddr_b, float (&a)[32], float (&b)[32]) {
+  uint32_t r[32], q[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr_a));
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]), "=r"(q[8]),
+        "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15]), "=r"(q[16]),
+        "=r"(q[17]), "=r"(q[18]), "=r"(q[19]), "=r"(q[20]), "=r"(q[21]), "=r"(q[22]), "=r"(q[23]), "=r"(q[24]),
+        "=r"(q[25]), "=r"(q[26]), "=r"(q[27]), "=r"(q[28]), "=r"(q[29]), "=r"(q[30]), "=r"(q[31])
+      : "r"(taddr_b));
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+        "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+        "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+        "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]), "+r"(q[0]),
+        "+r"(q[1]), "+r"(q[2]), "+r"(q[3]), "+r"(q[4]), "+r"(q[5]), "+r"(q[6]), "+r"(q[7]), "+r"(q[8]), "+r"(q[9]),
+        "+r"(q[10]), "+r"(q[11]), "+r"(q[12]), "+r"(q[13]), "+r"(q[14]), "+r"(q[15]), "+r"(q[16]), "+r"(q[17]),
+        "+r"(q[18]), "+r"(q[19]), "+r"(q[20]), "+r"(q[21]), "+r"(q[22]), "+r"(q[23]), "+r"(q[24]), "+r"(q[25]),
+        "+r"(q[26]), "+r"(q[27]), "+r"(q[28]), "+r"(q[29]), "+r"(q[30]), "+r"(q[31])
+      :
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { a[i] = __uint_as_float(r[i]); b[i] = __uint_as_float(q[i]); }
+}
+
 // 16 consecutive fp32 columns of this thread's tensor-memory lane
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   uint32_t r[16];
@@ -580,22 +618,29 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     unsigned char* stage0 = smem + kBOffS0 + row * kRowBytes;
     unsigned char* stage1 = smem + kBOffS1 + row * kRowBytes;
 
-    for (int b = 0; b < kBlocks; ++b) {
-      if (ok && tid == 0) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        constexpr uint32_t idesc = umma_idesc(kTileM, kKeyBlock, false);
+    // scores and dP of one block of the band: owned operands x the band's block (issued by one thread)
+    auto issue_scores = [&](int b) {
+      constexpr uint32_t idesc = umma_idesc(kTileM, kKeyBlock, false);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {   // scores: owned first operand x band first operand
-          umma_f16(tmem + kColS, umma_desc(s_base + kBOffA + kk * 32, 16, 1024),
-                   umma_desc(s_base + kBOffC + b * kBlockBytes + kk * 32, 16, 1024), idesc, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {   // dP: owned second operand x band second operand
-          umma_f16(tmem + kColP, umma_desc(s_base + kBOffB + kk * 32, 16, 1024),
-                   umma_desc(s_base + kBOffD + b * kBlockBytes + kk * 32, 16, 1024), idesc, kk > 0);
-        }
-        umma_commit(bar_s);
+      for (int kk = 0; kk < kD / 16; ++kk) {   // scores: owned first operand x band first operand
+        umma_f16(tmem + kColS, umma_desc(s_base + kBOffA + kk * 32, 16, 1024),
+                 umma_desc(s_base + kBOffC + b * kBlockBytes + kk * 32, 16, 1024), idesc, kk > 0);
       }
+#pragma unroll
+      for (int kk = 0; kk < kD / 16; ++kk) {   // dP: owned second operand x band second operand
+        umma_f16(tmem + kColP, umma_desc(s_base + kBOffB + kk * 32, 16, 1024),
+                 umma_desc(s_base + kBOffD + b * kBlockBytes + kk * 32, 16, 1024), idesc, kk > 0);
+      }
+    };
+    if (ok && tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      issue_scores(0);
+      umma_commit(bar_s);
+    }
+    // Per block one wait: the gradient products of block b and the score products of block b + 1 are issued back to
+    // back behind one commit (every thread has read block b's scores by then, and the tensor core runs them in
+    // order), so when block b + 1's scores are there the staging tiles are free as well.
+    for (int b = 0; b < kBlocks; ++b) {
       ok = __syncthreads_and(ok && mbar_wait(bar_s, b & 1));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
@@ -606,8 +651,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         uint32_t pk0[16], pk1[16];
         if (live) {
           float sv[32], dv[32];
-          tmem_ld32(row_taddr + kColS + c * 32, sv);
-          tmem_ld32(row_taddr + kColP + c * 32, dv);
+          tmem_ld32_pair(row_taddr + kColS + c * 32, row_taddr + kColP + c * 32, sv, dv);
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             float pa = 0.f, pb = 0.f, da = 0.f, db = 0.f;
@@ -634,7 +678,8 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();
+      // the staging tiles are written by all, and the next block of the band has landed
+      ok = __syncthreads_and(ok && (b + 1 >= kBlocks || mbar_wait(bar_more + 8 * b, 0)));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (ok && tid == 0) {
         constexpr uint32_t idesc = umma_idesc(kTileM, kD, true);
@@ -651,13 +696,16 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                      umma_desc(s_base + kBOffC + b * kBlockBytes + ks * 16 * kRowBytes, 16, 1024), idesc, (b | ks) != 0);
           }
         }
-        umma_commit(bar_g);
+        if (b + 1 < kBlocks) {
+          issue_scores(b + 1);
+          umma_commit(bar_s);
+        } else {
+          umma_commit(bar_g);
+        }
       }
-      // the gradient products of this block are done, and the next block of the band has landed
-      ok = __syncthreads_and(ok && mbar_wait(bar_g, b & 1) &&
-                             (b + 1 >= kBlocks || mbar_wait(bar_more + 8 * b, 0)));
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
+    ok = __syncthreads_and(ok && mbar_wait(bar_g, 0));   // the last block's gradient products
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
     // gradients of the owned rows: this thread's 16 of the 64 features
     {
