@@ -81,3 +81,25 @@ def test_without_edges_and_bad_arguments():
     Q = th.randn(g.n_dst, h, d, device=DEV)
     with pytest.raises(RuntimeError, match="rel must be"):
         graphop.attention_bias_forward(r[0], r[1], r[3], Q, Q, Q, th.zeros(g.n_edges, d + 1, device=DEV), 1.0)
+
+
+def test_backward_needs_the_transposed_edge_ids():
+    from custom_op_benchmark_b200 import _capi
+    lib = _capi.lib()
+    g = ZOO[0][1]
+    r = [t.to(DEV) for t in chunked(g, 32, dtype=th.int32)]
+    c = [t.to(DEV) for t in chunked(g, 32, transposed=True, dtype=th.int32)]
+    h, d = 2, 16
+    Q, K, V, rel, dO = _inputs(g, h, d, th.float32, 43)
+    o, lse = graphop.attention_bias_forward(r[0], r[1], r[3], Q, K, V, rel, 0.25)
+    outs = [th.empty_like(t) for t in (Q, K, V, rel)]
+    n = lib.graphop_workspace_bytes(_capi.OP_ATTENTION_BWD_PAIRS, g.n_edges, g.n_dst, h, d, 4, 4)
+    ws = th.empty(n + 256, dtype=th.uint8, device=DEV)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    p = lambda t: t.data_ptr()
+    rc = lib.graphop_attention_bias_backward_f32_i32(
+        p(r[0]), p(r[1]), p(r[3]), r[0].numel(), p(c[0]), p(c[1]), None, p(c[3]), c[0].numel(), p(Q), p(K), p(V), p(rel),
+        p(o), p(lse), p(dO), 0.25, p(outs[0]), p(outs[1]), p(outs[2]), p(outs[3]), g.n_edges, g.n_dst, g.n_src, h, d, base,
+        n, th.cuda.current_stream().cuda_stream)
+    assert rc == _capi.ERR_INVALID_ARGUMENT
+    th.cuda.synchronize()

@@ -107,3 +107,58 @@ def test_what_the_descriptors_say_is_checked_before_any_launch():
         with pytest.raises(RuntimeError, match="invalid argument"):
             dl.maskedmm_csr_forward(a["row"], a["indptr"], a["eid"], a["indices"], a["A"], a["B"], a["y"], a["ws"])
     th.cuda.synchronize()
+
+
+class _HandMadeProducer:
+    """A DLPack producer that is not an array library: it fills a DLManagedTensor by hand (ctypes) over device memory
+    it was given, the way a C program would, and hands out the capsule."""
+
+    class _Managed(__import__("ctypes").Structure):
+        pass
+
+    def __init__(self, tensor, code, bits):
+        import ctypes
+        self._owner = tensor                      # keeps the device memory alive
+        self._shape = (ctypes.c_int64 * tensor.dim())(*tensor.shape)
+        m = self._Managed
+        if not hasattr(m, "_fields_"):
+            m._fields_ = [("dl_tensor", dl.DLTensor), ("manager_ctx", ctypes.c_void_p), ("deleter", ctypes.c_void_p)]
+        self._managed = m()
+        t = self._managed.dl_tensor
+        t.data = tensor.data_ptr()
+        t.device.device_type, t.device.device_id = 2, tensor.device.index or 0
+        t.ndim = tensor.dim()
+        t.dtype.code, t.dtype.bits, t.dtype.lanes = code, bits, 1
+        t.shape = ctypes.cast(self._shape, ctypes.POINTER(ctypes.c_int64))
+        t.strides = None
+        t.byte_offset = 0
+        self._managed.deleter = None
+
+    def __dlpack_device__(self):
+        return (2, self._owner.device.index or 0)
+
+    def __dlpack__(self, stream=None):
+        import ctypes
+        new = ctypes.pythonapi.PyCapsule_New
+        new.restype, new.argtypes = ctypes.py_object, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p]
+        return new(ctypes.addressof(self._managed), b"dltensor", None)
+
+
+def test_a_producer_that_is_not_an_array_library():
+    g = ZOO[1][1]
+    r = [t.to(DEV) for t in chunked(g, 32, dtype=th.int32)]
+    h, d = 4, 32
+    gen = th.Generator(device=DEV).manual_seed(33)
+    w = th.rand(g.n_edges, h, generator=gen, device=DEV)
+    x = th.randn(g.n_src, h, d, generator=gen, device=DEV)
+    out = th.full((g.n_dst, h, d), float("nan"), device=DEV)
+    ws = _ws(_capi.OP_SPMM_FWD, g, h, d, th.float32, th.int32)
+    wrap = lambda t, code, bits: _HandMadeProducer(t, code, bits)
+    idx = [wrap(t, 0, 32) for t in r]
+    dl.vector_spmm_forward(idx[0], idx[1], idx[2], idx[3], wrap(w, 2, 32), wrap(x, 2, 32), wrap(out, 2, 32),
+                           wrap(ws, 1, 8))
+    assert th.equal(out, graphop.vector_spmm_forward(*r, w, x, num_dst=g.n_dst))
+    # what the descriptor says is what counts: the same memory declared as float64 is refused
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        dl.vector_spmm_forward(idx[0], idx[1], idx[2], idx[3], wrap(w, 2, 64), wrap(x, 2, 32), wrap(out, 2, 32),
+                               wrap(ws, 1, 8))

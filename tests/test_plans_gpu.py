@@ -182,3 +182,30 @@ def test_per_call_signature_runs_on_cached_plans():
         assert_close(o2, outs[0][0].double(), 2e-2, 2e-2, "walker against tensor cores")
     finally:
         graphop.plan_cache_size = old
+
+
+def test_plan_entry_points_report_bad_arguments():
+    import ctypes
+    from custom_op_benchmark_b200 import _capi
+    lib = _capi.lib()
+    g = ZOO[0][1]
+    r = [t.to(DEV) for t in chunked(g, 32, dtype=th.int32)]
+    need = lib.graphop_plan_bytes(r[0].numel(), g.n_edges, g.n_dst, 4)
+    mem = th.empty(need + 256, dtype=th.uint8, device=DEV)
+    base = (mem.data_ptr() + 255) // 256 * 256
+    plan = _capi.Plan()
+    args = [r[0].data_ptr(), r[1].data_ptr(), r[2].data_ptr(), r[3].data_ptr(), r[0].numel(), g.n_edges, g.n_dst]
+    stream = th.cuda.current_stream().cuda_stream
+    assert lib.graphop_plan_build_i32(*args, base, 64, ctypes.byref(plan), stream) == _capi.ERR_WORKSPACE
+    assert lib.graphop_plan_build_i32(*args, base + 4, need, ctypes.byref(plan), stream) == _capi.ERR_WORKSPACE
+    assert lib.graphop_plan_build_i32(*args, base, need, None, stream) == _capi.ERR_INVALID_ARGUMENT
+    assert lib.graphop_plan_build_i32(*args[:4], -1, g.n_edges, g.n_dst, base, need, ctypes.byref(plan),
+                                      stream) == _capi.ERR_INVALID_ARGUMENT
+    assert lib.graphop_plan_build_i32(*args, base, need, ctypes.byref(plan), stream) == _capi.OK
+    x = th.randn(g.n_edges, 2, device=DEV)
+    y = th.empty_like(x)
+    ws = th.empty(1 << 20, dtype=th.uint8, device=DEV)
+    # a planned op without a plan
+    assert lib.graphop_sparse_softmax_forward_planned_f32(None, x.data_ptr(), y.data_ptr(), 2, ws.data_ptr(), ws.numel(),
+                                                          stream) == _capi.ERR_INVALID_ARGUMENT
+    th.cuda.synchronize()
