@@ -1,4 +1,4 @@
-// Fused attention forward for dense-band graphs on the sm_100a tensor cores.
+// Fused attention, forward and backward, for dense-band graphs on the sm_100a tensor cores.
 //
 // The reference expresses batched dense attention as a graph (512 fully connected blocks, wrapper.py:79-112) and
 // runs it through the same one-thread-per-edge kernels as any other graph (graphop_kernel.cu:40-55, 170-202,
@@ -10,9 +10,12 @@
 //   * TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) brings the tile's 128 q rows and the up to 384 k and v
 //     rows its band reaches into shared memory;
 //   * tcgen05.mma (kind::f16, bf16 in, fp32 out) forms the 128 x 384 scores in tensor memory;
-//   * each of the 128 threads owns one query row: it reads the row from tensor memory (tcgen05.ld), masks the columns
-//     outside its node's range, takes max and sum, and writes the probabilities as bf16 into shared memory;
-//   * a second tcgen05.mma chain multiplies them with V; the thread scales its output row by 1 / sum and stores it.
+//   * four threads share a query row (512 threads per tile: enough warps to hide the latency of this stage): each
+//     reads every fourth 32-column chunk of the row from tensor memory (tcgen05.ld), masks the columns outside its
+//     node's range, takes max and sum (combined over the four through shared memory), and writes the probabilities
+//     as bf16 into shared memory;
+//   * a second tcgen05.mma chain multiplies them with V; each thread scales 16 of the row's 64 outputs by 1 / sum
+//     and stores them.
 // Everything a tile needs lives on chip: 208 KB of shared memory and 448 of the 512 tensor-memory columns; one block
 // per SM walks its share of the tiles and loads the next tile's operands while the current tile's softmax runs.
 // Every wait on an mbarrier is bounded; a tile whose wait runs out writes NaN to its rows of O instead of hanging.
