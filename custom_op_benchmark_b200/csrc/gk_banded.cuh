@@ -24,6 +24,8 @@
 #include <cudaTypedefs.h>
 #include <limits.h>
 
+#include <type_traits>
+
 #include "gk_host.cuh"
 
 namespace gk {
@@ -330,10 +332,15 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (ok && c >= c_first && c <= c_last) {
           float v[32];
           tmem_ld32(row_taddr + c * 32, v);
+          if (c * 32 >= jlo && c * 32 + 31 <= jhi) {   // the whole chunk belongs to the row: no column tests
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = c * 32 + j;
-            if (col >= jlo && col <= jhi) m = fmaxf(m, v[j]);
+            for (int j = 0; j < 32; ++j) m = fmaxf(m, v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = c * 32 + j;
+              if (col >= jlo && col <= jhi) m = fmaxf(m, v[j]);
+            }
           }
         }
       }
@@ -349,16 +356,25 @@ attention_forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const bool live = ok && c >= c_first && c <= c_last;
         if (live) tmem_ld32(row_taddr + c * 32, v);
         uint32_t packed[16];
+        if (live && c * 32 >= jlo && c * 32 + 31 <= jhi) {   // the whole chunk belongs to the row
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p0 = 0.f, p1 = 0.f;
-          if (live) {
-            const int col = c * 32 + j;
-            if (col >= jlo && col <= jhi) p0 = exp2_fast(fmaf(v[j], sl2, -msl2));
-            if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2_fast(fmaf(v[j + 1], sl2, -msl2));
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = exp2_fast(fmaf(v[j], sl2, -msl2)), p1 = exp2_fast(fmaf(v[j + 1], sl2, -msl2));
+            l += p0 + p1;
+            packed[j / 2] = pack_bf16(p0, p1);
           }
-          l += p0 + p1;
-          packed[j / 2] = pack_bf16(p0, p1);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float p0 = 0.f, p1 = 0.f;
+            if (live) {
+              const int col = c * 32 + j;
+              if (col >= jlo && col <= jhi) p0 = exp2_fast(fmaf(v[j], sl2, -msl2));
+              if (col + 1 >= jlo && col + 1 <= jhi) p1 = exp2_fast(fmaf(v[j + 1], sl2, -msl2));
+            }
+            l += p0 + p1;
+            packed[j / 2] = pack_bf16(p0, p1);
+          }
         }
         // 32 keys = 4 chunks of 16 bytes in panel c / 2, at chunk index (c & 1) * 4 + q, swizzled by the row
         unsigned char* panel = prow + (c >> 1) * kBlockBytes;
@@ -655,23 +671,29 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         if (live) {
           float sv[32], dv[32];
           tmem_ld32_pair(row_taddr + kColS + c * 32, row_taddr + kColP + c * 32, sv, dv);
+          // kTest = false: the whole chunk belongs to the row, no column tests
+          auto elements = [&](auto tested) {
+            constexpr bool kTest = decltype(tested)::value;
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float pa = 0.f, pb = 0.f, da = 0.f, db = 0.f;
-            const int col = col0 + j;
-            if (col >= jlo && col <= jhi) {
-              const float l2 = kSrc ? s_stat[col].x * kL2e : lse2, dl = kSrc ? s_stat[col].y : delta;
-              pa = exp2_fast(fmaf(sv[j], sl2, -l2));
-              da = pa * (dv[j] - dl) * p.scale;
+            for (int j = 0; j < 32; j += 2) {
+              float pa = 0.f, pb = 0.f, da = 0.f, db = 0.f;
+              const int col = col0 + j;
+              if (!kTest || (col >= jlo && col <= jhi)) {
+                const float l2 = kSrc ? s_stat[col].x * kL2e : lse2, dl = kSrc ? s_stat[col].y : delta;
+                pa = exp2_fast(fmaf(sv[j], sl2, -l2));
+                da = pa * (dv[j] - dl) * p.scale;
+              }
+              if (!kTest || (col + 1 >= jlo && col + 1 <= jhi)) {
+                const float l2 = kSrc ? s_stat[col + 1].x * kL2e : lse2, dl = kSrc ? s_stat[col + 1].y : delta;
+                pb = exp2_fast(fmaf(sv[j + 1], sl2, -l2));
+                db = pb * (dv[j + 1] - dl) * p.scale;
+              }
+              pk0[j / 2] = kSrc ? pack_bf16(pa, pb) : pack_bf16(da, db);
+              pk1[j / 2] = pack_bf16(da, db);
             }
-            if (col + 1 >= jlo && col + 1 <= jhi) {
-              const float l2 = kSrc ? s_stat[col + 1].x * kL2e : lse2, dl = kSrc ? s_stat[col + 1].y : delta;
-              pb = exp2_fast(fmaf(sv[j + 1], sl2, -l2));
-              db = pb * (dv[j + 1] - dl) * p.scale;
-            }
-            pk0[j / 2] = kSrc ? pack_bf16(pa, pb) : pack_bf16(da, db);
-            pk1[j / 2] = pack_bf16(da, db);
-          }
+          };
+          if (col0 >= jlo && col0 + 31 <= jhi) elements(std::false_type{});
+          else elements(std::true_type{});
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) { pk0[j] = 0u; pk1[j] = 0u; }
