@@ -174,9 +174,7 @@ extern "C" int graphop_pull_rows_i32(const void* const* tables, const int64_t* s
   tabs.seg[n_tables] = n_rows;
   const long long groups = (n_rows + 3) / 4;
   const long long blocks = (groups + 7) / 8;
-  // Four blocks per SM keep enough loads in flight for the links (a warp holds 4 rows = 2 KB; the links'
-  // bandwidth-latency product is a few MB) and leave half of every SM to a kernel running beside the pull.
-  const unsigned grid = (unsigned)(blocks < 148 * 4 ? blocks : 148 * 4);
+  const unsigned grid = (unsigned)(blocks < 148 * 64 ? blocks : 148 * 64);
   cudaStream_t st = (cudaStream_t)stream;
   pull_rows_kernel<<<grid, 256, 0, st>>>(tabs, idx, n_rows, (int)(row_bytes / 16), (uint4*)out);
   GK_LAUNCHED("pull_rows");

@@ -289,36 +289,14 @@ def sharded_spmm_forward(sh, edata_local, x_shard, ops=None, group=None, exchang
     return y, x_all
 
 
-def gather_edge_weights(sh, edata_local, group=None, exchange=None, async_op=False):
+def gather_edge_weights(sh, edata_local, group=None, exchange=None):
     """Weights of the transposed shard's edges.  With `exchange`: (weights of exactly those edges, fetched from
     the ranks that own them, indexed by exchange.eid_t).  Without: (every rank's weights all-gathered, indexed by
-    global edge id, i.e. by sh.eid_t).  Returns (weights, edge ids to read them with), and with async_op=True a third
-    item: the pending transfer to wait for (or None)."""
+    global edge id, i.e. by sh.eid_t).  Returns (weights, edge ids to read them with)."""
     if exchange is not None:
-        got = exchange_rows(edata_local.reshape(edata_local.shape[0], -1), exchange.w, group, async_op=async_op)
-        rows, work = got if async_op else (got, None)
-        out = (rows.reshape((rows.shape[0],) + tuple(edata_local.shape[1:])), exchange.eid_t)
-    else:
-        got = all_gather_rows(edata_local, sh.edge_bounds, group, async_op=async_op)
-        rows, work = got if async_op else (got, None)
-        out = (rows, sh.eid_t)
-    return out + (work,) if async_op else out
-
-
-class _SideStream:
-    """Work enqueued on a second CUDA stream of the current device; wait() makes the current stream wait for it."""
-    _streams = {}
-
-    def __init__(self, device):
-        key = (device.type, device.index)
-        if key not in _SideStream._streams:
-            _SideStream._streams[key] = th.cuda.Stream(device=device)
-        self.stream = _SideStream._streams[key]
-        self.stream.wait_stream(th.cuda.current_stream(device))
-        self.device = device
-
-    def wait(self):
-        th.cuda.current_stream(self.device).wait_stream(self.stream)
+        rows = exchange_rows(edata_local.reshape(edata_local.shape[0], -1), exchange.w, group)
+        return rows.reshape((rows.shape[0],) + tuple(edata_local.shape[1:])), exchange.eid_t
+    return all_gather_rows(edata_local, sh.edge_bounds, group), sh.eid_t
 
 
 def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all=None, ops=None, group=None, exchange=None):
@@ -330,11 +308,7 @@ def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all=None, ops=
     ops = ops or _default_ops()
     # the rows of dy are only needed by dx: their transfer is enqueued first and travels while dedata is computed
     if isinstance(dy_local, PeerRows):
-        # the pull runs on a second stream beside the dedata kernel, which does not need its rows
-        pending = _SideStream(dy_local.local.device)
-        with th.cuda.stream(pending.stream):
-            dy_rows = dy_local.pull(exchange.dy, ops)
-        dy_rows.record_stream(th.cuda.current_stream(dy_rows.device))
+        dy_rows, pending = dy_local.pull(exchange.dy, ops), None
         src_ids, dst_ids = exchange.indices, exchange.indices_t
         dy_local = dy_local.local
     elif exchange is not None:
@@ -344,11 +318,8 @@ def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all=None, ops=
     else:
         dy_rows, pending = all_gather_rows(dy_local, sh.dst_bounds, group, async_op=True)
         src_ids, dst_ids = sh.indices, sh.indices_t
-    w_pending = None
     if edata_all is not None:
         w_t, eid_t = edata_all, sh.eid_t
-    elif sh.parts > 1 and edata_local.is_cuda:
-        w_t, eid_t, w_pending = gather_edge_weights(sh, edata_local, group, exchange, async_op=True)   # needed by dx only
     else:
         w_t, eid_t = gather_edge_weights(sh, edata_local, group, exchange)
     # dedata: sampled dot products of the owned rows of dy against the source rows; no exchange.
@@ -356,8 +327,6 @@ def sharded_spmm_backward(sh, edata_local, dy_local, x_all, edata_all=None, ops=
     dedata = ops.maskedmm_csr_forward(sh.row, sh.indptr, sh.eid, src_ids, dy_local, x_all)
     if pending is not None:
         pending.wait()
-    if w_pending is not None:
-        w_pending.wait()
     # dx: row-owned aggregation over the transposed shard
     dx = ops.vector_spmm_forward(sh.col, sh.indptr_t, eid_t, dst_ids, w_t, dy_rows, num_dst=sh.cols)
     return dedata, dx
