@@ -56,7 +56,10 @@ def _worker(rank, world, port, out_dir, kind, per):
     lo, hi = sh.lo, sh.hi
     # the window is the own rows plus what the band reaches on either side
     cols = g.indices[int(g.indptr[lo]):int(g.indptr[hi])]
-    assert sh.win_lo == min(int(cols.min()), lo) and sh.win_hi == max(int(cols.max()) + 1, hi)
+    if cols.numel():
+        assert sh.win_lo == min(int(cols.min()), lo) and sh.win_hi == max(int(cols.max()) + 1, hi)
+    else:
+        assert (sh.win_lo, sh.win_hi, sh.rows) == (lo, hi, 0)     # a rank without rows: an empty window
     assert sh.send_counts[rank] == 0 and sh.recv_counts[rank] == 0
     assert sum(sh.recv_counts) == sh.window_rows - sh.rows           # every halo row comes from exactly one owner
     # the transposed local CSR lists every local edge once, under its window column
@@ -76,7 +79,8 @@ def _worker(rank, world, port, out_dir, kind, per):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,kind,per", [(2, "band", 192), (3, "band", 128), (4, "wide", 64), (2, "blocks", 135)])
+@pytest.mark.parametrize("world,kind,per", [(2, "band", 192), (3, "band", 128), (4, "wide", 64), (2, "blocks", 135),
+                                            (3, "wide", 128)])    # the last rank of three owns no row at all
 def test_halo_sharded_attention_matches_unsharded(tmp_path, world, kind, per):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), kind, per), nprocs=world, join=True)
     g = _graph(kind)
@@ -95,8 +99,10 @@ def test_halo_sharded_attention_matches_unsharded(tmp_path, world, kind, per):
         assert halos == [0, 0]          # the cut falls between the two sequences: nothing to exchange
     if kind == "band" and world == 3:
         assert halos == [20, 40, 20]     # half-width 20 on every open side
-    if kind == "wide":
+    if kind == "wide" and world == 4:
         assert halos == [100, 164, 164, 100]   # half-width 100 over shards of 64: rows travel two ranks far
+    if kind == "wide" and world == 3:
+        assert halos == [100, 100, 0]           # two shards of 128 rows and a rank that owns nothing
 
 
 def test_single_rank_needs_no_process_group():
