@@ -248,7 +248,7 @@ class PeerRows:
         self.local = self.buffer[:rows]
         self.tables = [int(p) for p in self.handle.buffer_ptrs]
         self.rank, self.world = dist.get_rank(group), world
-        self.row_bytes = self.local[0].numel() * self.local.element_size() if rows else 0
+        self.row_bytes = self.buffer[0].numel() * self.buffer.element_size()   # also for a rank that owns no row
 
     def barrier(self):
         self.handle.barrier()
