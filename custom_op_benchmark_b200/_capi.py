@@ -77,6 +77,14 @@ UNTYPED = {
     "graphop_vector_spmm_forward_f32_i32_static": ([_P] * 7 + [_I64] * 4 + [_INT] * 2 + [_P], _INT),
     "graphop_gather_rows_i32": ([_P, _I64, _P, _I64, _P, _P], _INT),
     "graphop_pull_rows_i32": ([_P, _P, _INT, _P, _I64, _P, _P], _INT),
+    "graphop_partition_csr_workspace_bytes": ([_I64], _SZ),
+    "graphop_partition_csr_count_i32": ([_P, _I64, _I64, _P, _SZ, _P, _P], _INT),
+    "graphop_partition_csr_count_i64": ([_P, _I64, _I64, _P, _SZ, _P, _P], _INT),
+    "graphop_partition_csr_fill_i32": ([_P, _I64, _I64, _P, _I64, _P, _P, _P], _INT),
+    "graphop_partition_csr_fill_i64": ([_P, _I64, _I64, _P, _I64, _P, _P, _P], _INT),
+    "graphop_transpose_csr_workspace_bytes": ([_I64, _INT], _SZ),
+    "graphop_transpose_csr_i32": ([_P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _SZ, _P], _INT),
+    "graphop_transpose_csr_i64": ([_P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _SZ, _P], _INT),
     "graphop_check_graph_i32": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
     "graphop_check_graph_i64": ([_P] * 4 + [_I64] * 4 + [_P, _P], _INT),
 }

@@ -19,7 +19,7 @@ BENCH_LIB = os.path.join(HERE, "libgraphop_b200_bench.so")
 OBJ_DIR = os.path.join(HERE, "build")
 UNITS = ["graphop_capi_f32.cu", "graphop_capi_f64.cu", "graphop_capi_bf16.cu", "graphop_capi_attn_f32.cu",
          "graphop_capi_attn_f64.cu", "graphop_capi_attn_bf16.cu", "graphop_capi_misc.cu", "graphop_capi_static.cu",
-         "graphop_capi_dlpack.cu"]
+         "graphop_capi_dlpack.cu", "graphop_capi_prep.cu"]
 # the instrumented twin: what bench.py's workloads call, plus the hooks themselves
 BENCH_UNITS = ["graphop_capi_f32.cu", "graphop_capi_attn_f32.cu", "graphop_capi_attn_bf16.cu", "graphop_capi_misc.cu",
                os.path.join("bench", "graphop_bench.cu")]

@@ -404,6 +404,62 @@ def pull_rows(tables, seg, idx, row_bytes, out):
     return out
 
 
+def partition_csr(indptr, chunk_size=32):
+    """partition_csr of the reference (part_csr.py:13-27) for an int32 / int64 indptr on a CUDA device, by the
+    library's kernels (graphop_partition_csr_count / _fill): (row, indptr_) as int64 tensors on that device."""
+    import ctypes
+    if chunk_size <= 0:
+        raise ValueError("chunk_size must be positive")
+    if not indptr.is_cuda or indptr.dtype not in (th.int32, th.int64) or indptr.dim() != 1:
+        raise RuntimeError("indptr must be a one-dimensional int32 or int64 CUDA tensor")
+    if indptr.numel() < 1:
+        raise IndexError("indptr must hold at least one element")
+    ip = indptr.contiguous()
+    n = ip.numel() - 1
+    suffix = "i32" if ip.dtype == th.int32 else "i64"
+    lib = _capi.lib()
+    with th.cuda.device(ip.device):
+        stream = th.cuda.current_stream(ip.device).cuda_stream
+        ws = th.empty(lib.graphop_partition_csr_workspace_bytes(n), dtype=th.uint8, device=ip.device)
+        count = ctypes.c_int64(0)
+        rc = getattr(lib, "graphop_partition_csr_count_" + suffix)(
+            _p(ip), n, int(chunk_size), _p(ws), ws.numel(), ctypes.byref(count), stream)
+        if rc != _capi.OK:
+            raise RuntimeError("graphop_partition_csr_count: %s" % _capi.error_message(rc))
+        row = th.empty(count.value, dtype=th.int64, device=ip.device)
+        ptr = th.empty(count.value + 1, dtype=th.int64, device=ip.device)
+        rc = getattr(lib, "graphop_partition_csr_fill_" + suffix)(
+            _p(ip), n, int(chunk_size), _p(ws), count.value, _p(row), _p(ptr), stream)
+        if rc != _capi.OK:
+            raise RuntimeError("graphop_partition_csr_fill: %s" % _capi.error_message(rc))
+    return row, ptr
+
+
+def transpose_csr(indptr, indices, n_src):
+    """(indptr_t, indices_t, eid_t) of a row CSR on a CUDA device whose edge ids are its positions, in the inputs'
+    integer type (int32 or int64, the same for both): edges regrouped by source, ties in row-CSR order.  The
+    library's kernels (graphop_transpose_csr): a stable radix sort of the positions by source and one fill pass."""
+    if not (indptr.is_cuda and indices.is_cuda) or indptr.dtype != indices.dtype or \
+            indptr.dtype not in (th.int32, th.int64) or indptr.dim() != 1 or indices.dim() != 1:
+        raise RuntimeError("indptr and indices must be one-dimensional CUDA tensors of the same type, int32 or int64")
+    if indptr.numel() < 1:
+        raise IndexError("indptr must hold at least one element")
+    ip, idx = indptr.contiguous(), indices.contiguous()
+    n_dst, e, n_src = ip.numel() - 1, idx.numel(), int(n_src)
+    suffix, width = ("i32", 4) if ip.dtype == th.int32 else ("i64", 8)
+    lib = _capi.lib()
+    with th.cuda.device(ip.device):
+        ws = th.empty(lib.graphop_transpose_csr_workspace_bytes(e, width), dtype=th.uint8, device=ip.device)
+        ptr_t = th.empty(n_src + 1, dtype=ip.dtype, device=ip.device)
+        idx_t, eid_t = th.empty_like(idx), th.empty_like(idx)
+        rc = getattr(lib, "graphop_transpose_csr_" + suffix)(
+            _p(ip), _p(idx), n_dst, n_src, e, _p(ptr_t), _p(idx_t), _p(eid_t), _p(ws), ws.numel(),
+            th.cuda.current_stream(ip.device).cuda_stream)
+    if rc != _capi.OK:
+        raise RuntimeError("graphop_transpose_csr: %s" % _capi.error_message(rc))
+    return ptr_t, idx_t, eid_t
+
+
 def check_graph(row, indptr, eid, indices, n_nodes, n_other):
     """Debug aid: verifies on the device the graph contract the kernels rely on (monotone
     indptr and row, indices and edge ids in range) and returns the violation bit mask

@@ -23,7 +23,7 @@ import numpy as np
 import torch as th
 
 __all__ = [
-    "Graph", "coo_to_graph", "transpose_csr", "block_diagonal_graph", "er_graph",
+    "Graph", "coo_to_graph", "transpose_csr", "transpose_csr_tensor_ops", "block_diagonal_graph", "er_graph",
     "banded_graph", "rmat_graph", "zipf_graph",
 ]
 
@@ -70,6 +70,15 @@ def transpose_csr(indptr, indices, n_src):
     ties kept in row-CSR order (a stable sort), so within one source the
     destinations ascend.
     """
+    if indptr.is_cuda and indices.is_cuda and indptr.dtype == indices.dtype and \
+            indptr.dtype in (th.int32, th.int64) and indices.numel() < 2 ** 31 - 1:
+        from . import graphop   # the CUDA library's kernels; raises if it has not been built
+        return tuple(t.to(th.int64) for t in graphop.transpose_csr(indptr, indices, n_src))
+    return transpose_csr_tensor_ops(indptr, indices, n_src)
+
+
+def transpose_csr_tensor_ops(indptr, indices, n_src):
+    """The same by tensor ops on the inputs' device (the host path, and the checker of the kernels)."""
     ip = indptr.to(th.int64)
     src = indices.to(th.int64)
     n_dst = ip.numel() - 1

@@ -9,20 +9,32 @@ chunk.  Both outputs are int64 on the input's device, whatever the input
 integer dtype.
 
 The reference walks the rows in a Python double loop after copying the array
-to the host (part_csr.py:15-21), which is O(N + C) interpreter steps.  This
-version is a handful of tensor ops on the input's own device and is bit-exact
-with the loop.  One deliberate deviation: for a graph with no edges at all the
+to the host (part_csr.py:15-21), which is O(N + C) interpreter steps.  Here an
+int32 / int64 indptr on a CUDA device goes through the library's own kernels
+(csrc/graphop_capi_prep.cu: chunk counts, a prefix sum, one thread per chunk);
+anything else (host tensors, other integer types) through a handful of tensor
+ops.  Both are bit-exact with the loop.  One deliberate deviation: for a graph with no edges at all the
 reference returns ``row`` as an empty *float32* tensor (an artefact of
 ``th.tensor([])``, part_csr.py:24); here ``row`` is an empty int64 tensor.
 """
 import torch as th
 
-__all__ = ["partition_csr", "unchunked_rows"]
+__all__ = ["partition_csr", "partition_csr_tensor_ops", "unchunked_rows"]
 
 
 def partition_csr(indptr, chunk_size=32):
     if chunk_size <= 0:
         # range(a, b, 0) raises ValueError in the reference loop (part_csr.py:19)
+        raise ValueError("chunk_size must be positive")
+    if indptr.is_cuda and indptr.dtype in (th.int32, th.int64) and indptr.dim() == 1 and indptr.numel() >= 1:
+        from . import graphop   # the CUDA library; raises if it has not been built
+        return graphop.partition_csr(indptr, chunk_size)
+    return partition_csr_tensor_ops(indptr, chunk_size)
+
+
+def partition_csr_tensor_ops(indptr, chunk_size=32):
+    """The same table by tensor ops on the input's device (the host path, and the checker of the kernels)."""
+    if chunk_size <= 0:
         raise ValueError("chunk_size must be positive")
     device = indptr.device
     ip = indptr.to(th.int64)

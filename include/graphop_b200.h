@@ -89,6 +89,36 @@ int graphop_gather_rows_i32(const int32_t* idx, int64_t n_rows, const void* tabl
 int graphop_pull_rows_i32(const void* const* tables, const int64_t* seg, int n_tables, const int32_t* idx,
                           int64_t row_bytes, void* out, graphop_stream_t stream);
 
+/* partition_csr on the device (reference: part_csr.py:13-27, a host double loop): every CSR row
+ * [indptr[r], indptr[r+1]) cut into chunks of at most chunk_size positions; row[c] = the row of chunk c,
+ * indptr_out[c] = its first position, indptr_out[n_chunks] = indptr[n_rows].  Outputs are int64 for either index
+ * type.  Two calls, because the caller allocates the outputs: _count writes the number of chunks to the HOST
+ * integer *n_chunks (synchronises `stream`) and leaves every row's first chunk in `ws`; _fill, given the same `ws`
+ * untouched, writes row (n_chunks entries) and indptr_out (n_chunks + 1 entries).  n_rows < 2^31 - 1. */
+size_t graphop_partition_csr_workspace_bytes(int64_t n_rows);
+int graphop_partition_csr_count_i32(const int32_t* indptr, int64_t n_rows, int64_t chunk_size, void* ws,
+                                    size_t ws_bytes, int64_t* n_chunks, graphop_stream_t stream);
+int graphop_partition_csr_count_i64(const int64_t* indptr, int64_t n_rows, int64_t chunk_size, void* ws,
+                                    size_t ws_bytes, int64_t* n_chunks, graphop_stream_t stream);
+int graphop_partition_csr_fill_i32(const int32_t* indptr, int64_t n_rows, int64_t chunk_size, const void* ws,
+                                   int64_t n_chunks, int64_t* row, int64_t* indptr_out, graphop_stream_t stream);
+int graphop_partition_csr_fill_i64(const int64_t* indptr, int64_t n_rows, int64_t chunk_size, const void* ws,
+                                   int64_t n_chunks, int64_t* row, int64_t* indptr_out, graphop_stream_t stream);
+
+/* The transposed CSR the backward passes take (the reference's scripts build it with scipy on the host,
+ * wrapper.py:96-112): edges regrouped by source with ties in row-CSR order, so within one source the destinations
+ * ascend.  indptr (n_dst + 1) and indices (n_edges, source ids in [0, n_src)) are the row CSR whose edge ids are its
+ * positions; outputs, in the same integer type: indptr_t (n_src + 1), indices_t (n_edges: the destination of every
+ * transposed position), eid_t (n_edges: its position in the row CSR).  Deterministic; does not synchronise.
+ * n_edges < 2^31 - 1. */
+size_t graphop_transpose_csr_workspace_bytes(int64_t n_edges, int index_bytes);
+int graphop_transpose_csr_i32(const int32_t* indptr, const int32_t* indices, int64_t n_dst, int64_t n_src,
+                              int64_t n_edges, int32_t* indptr_t, int32_t* indices_t, int32_t* eid_t,
+                              void* ws, size_t ws_bytes, graphop_stream_t stream);
+int graphop_transpose_csr_i64(const int64_t* indptr, const int64_t* indices, int64_t n_dst, int64_t n_src,
+                              int64_t n_edges, int64_t* indptr_t, int64_t* indices_t, int64_t* eid_t,
+                              void* ws, size_t ws_bytes, graphop_stream_t stream);
+
 /* Sufficient workspace for one call of `op`.  n_nodes: the largest node count among the
  * call's node tensors (for the softmax ops: an upper bound on node id + 1).  elem_bytes: 2, 4
  * or 8; index_bytes: 4 or 8. */
