@@ -82,9 +82,10 @@ __device__ __forceinline__ void lds_acc(typename AccOf<T>::type (&dst)[V], const
 //   void consume_batch(State&, const unsigned char* first, int cnt, const int* eids, int lane)
 //        fold cnt positions whose ring entries are first, first + kEdgeBytes, ...;
 //        kFullBatch: cnt == kBatch, known at compile time
-// Lanes whose slot does not exist (slot >= S) are not masked in stage / consume_batch: their slot map
-// points at slot 0, so their copies and arithmetic are harmless duplicates, their node-resident
-// operand is zero, and only stores test `ok`.
+// Lanes whose slot does not exist (slot >= S) copy nothing in stage (32 lanes fetching slot 0 again cost a
+// narrow row - one head of 32 floats - more than the row itself: the kernels ran 2.5x slower on it than on a
+// 512-byte row); the walker zeroes every ring once per tile, so what those lanes read in consume_batch is zero,
+// their node-resident operand is zero as well, and only stores test `ok`.
 
 // Ops that hand a batch's per-edge scalars from their owner lanes to all lanes of a head through shared memory
 // declare `kScratchBytes` (a multiple of 16): that many bytes per warp follow the ring.
@@ -185,6 +186,8 @@ walk_staged_kernel(Op op, const PlanHeader* __restrict__ hdr, const int32_t* __r
   int* w_eid = w_oth + kWin;  // present only when Op::kUsesEid
   unsigned char* w_rem = reinterpret_cast<unsigned char*>(w_oth + (Op::kUsesEid ? 2 : 1) * kWin);
   unsigned char* ring = mine + staged_meta_bytes<Op>();
+  // ring bytes of slots that do not exist (rows narrower than the lanes) are never copied to: they read as zero
+  for (int off = lane * 16; off < DEPTH * EB; off += 32 * 16) *reinterpret_cast<uint4*>(ring + off) = uint4{0, 0, 0, 0};
 
   // Metadata window.  Block b (positions 32 b .. 32 b + 31 of the tile) occupies window entries
   // (b & 1) * 32 + lane.  w_rem = number of consecutive positions from this one on that have the same node,
@@ -510,7 +513,7 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
     const unsigned rowb = (unsigned)(kEdgeFeat ? this->D : this->HD) * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.xb[i], kEdgeFeat ? e : c, rowb));
+      if (st.sm.ok[i]) cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.xb[i], kEdgeFeat ? e : c, rowb));
       const int j = lane + 32 * i;
       if (mode() == kWeightsPieces) {
         if (j * 16 < wbytes) cp_async16(entry + Ring::kRowBytes + j * 16, wrow + j * 16);
@@ -612,7 +615,7 @@ struct EdgeDotStaged : EdgeDotOp<T, V, R, kEdgeFeat> {
     const unsigned rowb = (unsigned)(kEdgeFeat ? this->D : this->HD) * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.bb[i], kEdgeFeat ? e : c, rowb));
+      if (st.sm.ok[i]) cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.bb[i], kEdgeFeat ? e : c, rowb));
     }
   }
   template <bool kFullBatch>
@@ -720,6 +723,7 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R, kBias> {
     const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
+      if (!st.sm.ok[i]) continue;
       cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.kb[i], c, rowb));
       cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.vb[i], c, rowb));
       if constexpr (kBias)
@@ -1015,6 +1019,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R, kBias> {
     const unsigned rowb = (unsigned)this->HD * (unsigned)sizeof(T);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
+      if (!st.sm.ok[i]) continue;
       cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.kb[i], c, rowb));
       cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.vb[i], c, rowb));
       if constexpr (kBias)
@@ -1129,8 +1134,11 @@ struct AttnBwdSrcStaged : AttnBwdSrcOp<T, V, R> {
     for (int i = 0; i < R; ++i) {
       // plain index arithmetic here: the per-lane base pointers of the other two kernels would cost this
       // one, which is at its register limit, more than they save
-      cp_async16(entry + (lane + 32 * i) * 16, this->q + (long long)c * this->HD + st.sm.feat[i]);
-      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, this->dout + (long long)c * this->HD + st.sm.feat[i]);
+      if (st.sm.ok[i]) {
+        cp_async16(entry + (lane + 32 * i) * 16, this->q + (long long)c * this->HD + st.sm.feat[i]);
+        cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16,
+                   this->dout + (long long)c * this->HD + st.sm.feat[i]);
+      }
       const int piece = lane + 32 * i;
       if (piece < pieces) cp_async16(entry + 2 * Ring::kRowBytes + piece * 16, pairs + piece * 16);
     }
@@ -1218,8 +1226,10 @@ struct AttnBwdSrcPairsStaged : AttnBwdSrcOp<T, V, R> {
     const int pieces = (int)(pairb / 16);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.qb[i], c, rowb));
-      cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.gb[i], c, rowb));
+      if (st.sm.ok[i]) {
+        cp_async16(entry + (lane + 32 * i) * 16, row_ptr(st.qb[i], c, rowb));
+        cp_async16(entry + Ring::kRowBytes + (lane + 32 * i) * 16, row_ptr(st.gb[i], c, rowb));
+      }
       const int piece = lane + 32 * i;
       if (piece < pieces) cp_async16(entry + 2 * Ring::kRowBytes + piece * 16, pairs + piece * 16);
     }
