@@ -259,11 +259,13 @@ inline int dispatch_shape(const VecShape& s, F&& f) {
 }
 
 // Calls f(integral_constant<int, LPH>) with the compile-time lanes-per-head the staged dot-product
-// ops are specialised for (8, 16, 32), or 0 for "read it at run time".
+// ops are specialised for (2 to 32), or 0 for "read it at run time".
 template <class F>
 inline int dispatch_lph(int lph, F&& f) {
   using std::integral_constant;
   switch (lph) {
+    case 2: return f(integral_constant<int, 2>{});
+    case 4: return f(integral_constant<int, 4>{});
     case 8: return f(integral_constant<int, 8>{});
     case 16: return f(integral_constant<int, 16>{});
     case 32: return f(integral_constant<int, 32>{});

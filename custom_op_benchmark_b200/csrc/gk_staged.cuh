@@ -429,12 +429,13 @@ __device__ __forceinline__ A reduce_transposed(const A (&s)[U], int lane) {
   return keep;
 }
 // Batch size, scratch and lane roles of the ops that reduce with reduce_transposed: rows of one 16-byte slot
-// per lane, 8 / 16 / 32 lanes per head.  Lane l of a head's group owns edge l & (U - 1) of the batch; the first U
+// per lane, 2 to 32 lanes per head.  Lane l of a head's group owns edge l & (U - 1) of the batch; the first U
 // lanes of each group publish their edge's scalar in the warp's scratch, U consecutive values per head.
 constexpr int kFastBatch = GK_FAST_BATCH;
-constexpr int kFastScratch = 128;  // 4 values of 8 bytes for each of at most 4 heads
-template <int R, int LPH> struct FastShape {
-  static constexpr bool value = R == 1 && (LPH == 8 || LPH == 16 || LPH == 32);
+constexpr int kFastScratch = 128;  // U values of kAccBytes for each of the 32 / LPH heads of a 32-slot row
+template <int R, int LPH, int kAccBytes = 4> struct FastShape {
+  static constexpr bool value = R == 1 && LPH >= kFastBatch && (LPH == 2 || LPH == 4 || LPH == 8 || LPH == 16 || LPH == 32) &&
+                                (32 / (LPH ? LPH : 1)) * kFastBatch * kAccBytes <= kFastScratch;
 };
 template <int U, typename A>
 __device__ __forceinline__ void lds_batch(A (&d)[U], const A* p) {
@@ -667,7 +668,7 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R, kBias> {
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
   using CarryIn = typename Base::CarryIn;
-  static constexpr bool kFast = FastShape<R, LPH>::value;
+  static constexpr bool kFast = FastShape<R, LPH, (int)sizeof(A)>::value;
   using Ring = RingShape<T, R, kBias ? 3 : 2, kBias, GK_CTAS_NARROW, kFastScratch, 0, kFast ? kFastBatch : 0>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
@@ -872,7 +873,7 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R, kBias> {
   // the next node\'s resident rows are fetched ahead only while they fit 16 bytes per lane: wider rows need
   // the registers for the node being processed
   static constexpr bool kPrefetch = R * V * (int)sizeof(A) <= 16;
-  static constexpr bool kFast = FastShape<R, LPH>::value;
+  static constexpr bool kFast = FastShape<R, LPH, (int)sizeof(A)>::value;
   using Ring = RingShape<T, R, kBias ? 3 : 2, kBias, GK_CTAS_DST, kFastScratch, 0, kFast ? kFastBatch : 0>;
   static constexpr int kEdgeBytes = Ring::kEdgeBytes, kDepth = Ring::kDepth, kBatch = Ring::kBatch,
                        kMinCtas = Ring::kMinCtas, kWarps = kWarpsPerCta;
