@@ -476,7 +476,8 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   // How an edge's H weights reach the ring entry (set by the host):
   //   kWeightsPerLane  every lane copies the word of its own head (any H, any element size);
   //   kWeightsWords    lane j < H copies weight j, lanes read the weight of their head (4- and 8-byte
-  //                    elements, H <= 32 * R);
+  //                    elements, H <= 32 * R; 2-byte elements with an even H on a 4-byte aligned tensor: lane j
+  //                    copies the word that holds weights 2 j and 2 j + 1);
   //   kWeightsPieces   the H weights travel as 16-byte pieces copied by the first lanes (the weight
   //                    row is a whole number of aligned 16-byte pieces).
   // One scattered copy per edge instead of one per lane is what the packed modes buy.
@@ -499,7 +500,9 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
     const bool whole = feat0 == 0 && HD <= block_elems && H <= 32 * R;  // one feature block sees every head
     if (!whole) return kWeightsPerLane;
     if ((H * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) return kWeightsPieces;
-    return sizeof(T) >= 4 ? kWeightsWords : kWeightsPerLane;
+    if (sizeof(T) >= 4) return kWeightsWords;
+    // 2-byte elements: an even number of heads on a 4-byte aligned tensor is a row of whole aligned words
+    return (H % 2 == 0 && (reinterpret_cast<uintptr_t>(w) & 3) == 0) ? kWeightsWords : kWeightsPerLane;
   }
 
   __device__ __forceinline__ void setup(State& st, int lane) const {
@@ -522,6 +525,8 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
         if constexpr (sizeof(T) >= 4) {
           if (j < this->H)
             cp_async_small<sizeof(T)>(entry + Ring::kRowBytes + j * sizeof(T), wrow + j * sizeof(T));
+        } else {
+          if (j * 4 < wbytes) cp_async_small<4>(entry + Ring::kRowBytes + j * 4, wrow + j * 4);  // two weights per word
         }
       } else {
         const T* wsrc = this->w + (long long)e * this->H + st.sm.head[i];

@@ -72,6 +72,8 @@ SHAPES = [(1, 16), (4, 32), (8, 64), (2, 64), (1, 128), (3, 5), (1, 1), (2, 12),
     (8, 64, th.bfloat16, th.int32), (1, 1024, th.float32, th.int32), (8, 160, th.float64, th.int64),
     # weight rows that are not a whole number of 16-byte pieces (12, 8 and 6 bytes), vectorised features
     (3, 8, th.float32, th.int32), (2, 16, th.float32, th.int64), (3, 16, th.bfloat16, th.int32),
+    # 2-byte weights that travel as 4-byte words (an even number of heads: 4, 8 and 12 bytes per edge)
+    (2, 16, th.bfloat16, th.int32), (4, 32, th.bfloat16, th.int64), (6, 8, th.bfloat16, th.int32),
 ])
 def test_vector_spmm(name, g, cs, h, d, dtype, idt):
     if g.n_dst > g.n_src:
@@ -138,7 +140,7 @@ def test_maskedmm(name, g, cs, h, d, dtype, idt):
 @pytest.mark.parametrize("h,d,dtype,idt", [
     (8, 64, th.float32, th.int64), (4, 32, th.float32, th.int32), (4, 32, th.float64, th.int32),
     (1, 16, th.float32, th.int32), (3, 5, th.float64, th.int64), (8, 64, th.bfloat16, th.int32),
-    (2, 12, th.float32, th.int32),
+    (2, 12, th.float32, th.int32), (4, 32, th.bfloat16, th.int32), (2, 64, th.bfloat16, th.int64),
 ])
 def test_node_mul_edge(name, g, cs, h, d, dtype, idt):
     r = chunked(g, cs, dtype=idt)[:3]
