@@ -385,11 +385,15 @@ inline int run_aggregate(Arena& ar, const GraphView& g, const T* w, const T* x, 
         });
       };
       if constexpr (IsStaged<OpT>::value) {
-        // the two packed modes get their own instantiations; the per-lane mode keeps the run-time test
+        // the packed modes get their own instantiations; the per-lane mode keeps the run-time test
         using Pieces = AggregateStaged<T, V, R, kEdgeFeat, OpT::kWeightsPieces>;
         using Words = AggregateStaged<T, V, R, kEdgeFeat, OpT::kWeightsWords>;
         if (wm == OpT::kWeightsPieces) return run(TypeTag<Pieces>{});
         if (wm == OpT::kWeightsWords) return run(TypeTag<Words>{});
+        if constexpr (sizeof(T) == 2) {
+          using Half = AggregateStaged<T, V, R, kEdgeFeat, OpT::kWeightsHalfWords>;
+          if (wm == OpT::kWeightsHalfWords) return run(TypeTag<Half>{});
+        }
       }
       return run(TypeTag<OpT>{});
     })));

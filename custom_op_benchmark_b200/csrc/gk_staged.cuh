@@ -481,9 +481,13 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
   //   kWeightsPieces   the H weights travel as 16-byte pieces copied by the first lanes (the weight
   //                    row is a whole number of aligned 16-byte pieces).
   // One scattered copy per edge instead of one per lane is what the packed modes buy.
-  enum { kWeightsPerLane = 0, kWeightsWords = 1, kWeightsPieces = 2 };
+  //   kWeightsHalfWords  2-byte elements otherwise (odd H, or a tensor that is only 2-byte aligned): the first lanes
+  //                    copy the aligned 4-byte words that cover the edge's H weights (H / 2 + 1 at most); the row
+  //                    starts in the lower or the upper half of the first word, which the readers work out from
+  //                    the edge id.
+  enum { kWeightsPerLane = 0, kWeightsWords = 1, kWeightsPieces = 2, kWeightsHalfWords = 3 };
   int wmode = kWeightsPerLane;
-  // 2-byte elements, per-lane mode: the two elements whose aligned 4-byte word would reach outside the tensor
+  // 2-byte elements, per-lane and half-word modes: the two elements whose aligned 4-byte word would reach outside the tensor
   // (the first one when the tensor starts in the upper half of a word, the last one when it ends in the lower
   // half); they are copied alone.  Null when the tensor's ends are word-aligned.
   const T* w_first_alone = nullptr;
@@ -502,7 +506,7 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
     if ((H * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) return kWeightsPieces;
     if (sizeof(T) >= 4) return kWeightsWords;
     // 2-byte elements: an even number of heads on a 4-byte aligned tensor is a row of whole aligned words
-    return (H % 2 == 0 && (reinterpret_cast<uintptr_t>(w) & 3) == 0) ? kWeightsWords : kWeightsPerLane;
+    return (H % 2 == 0 && (reinterpret_cast<uintptr_t>(w) & 3) == 0) ? kWeightsWords : kWeightsHalfWords;
   }
 
   __device__ __forceinline__ void setup(State& st, int lane) const {
@@ -527,6 +531,19 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
             cp_async_small<sizeof(T)>(entry + Ring::kRowBytes + j * sizeof(T), wrow + j * sizeof(T));
         } else {
           if (j * 4 < wbytes) cp_async_small<4>(entry + Ring::kRowBytes + j * 4, wrow + j * 4);  // two weights per word
+        }
+      } else if (sizeof(T) == 2 && mode() == kWeightsHalfWords) {
+        const uintptr_t first = reinterpret_cast<uintptr_t>(wrow);               // the row's first weight
+        const uintptr_t a = (first & ~uintptr_t(3)) + 4 * (uintptr_t)j;          // lane j's word
+        if (a < first + (uintptr_t)wbytes) {
+          WWord* wdst = reinterpret_cast<WWord*>(entry + Ring::kRowBytes) + j;
+          // the two words that reach outside the tensor: only their inner half is read
+          if (a + 2 == reinterpret_cast<uintptr_t>(w_first_alone))
+            reinterpret_cast<uint16_t*>(wdst)[1] = __ldg(reinterpret_cast<const uint16_t*>(a + 2));
+          else if (a == reinterpret_cast<uintptr_t>(w_last_alone))
+            reinterpret_cast<uint16_t*>(wdst)[0] = __ldg(reinterpret_cast<const uint16_t*>(a));
+          else
+            cp_async_small<4>(wdst, reinterpret_cast<const void*>(a));
         }
       } else {
         const T* wsrc = this->w + (long long)e * this->H + st.sm.head[i];
@@ -555,7 +572,11 @@ struct AggregateStaged : AggregateOp<T, V, R, kEdgeFeat> {
         A xv[V];
         lds_acc<T, V>(xv, entry + (lane + 32 * i) * 16);
         A wv;
-        if (mode() != kWeightsPerLane) {
+        if (sizeof(T) == 2 && mode() == kWeightsHalfWords) {
+          // the row starts in the upper half of its first word when its first weight's address is odd in elements
+          const uintptr_t first = reinterpret_cast<uintptr_t>(this->w) + 2 * (uintptr_t)((long long)eids[u] * this->H);
+          wv = to_acc<T>(reinterpret_cast<const T*>(entry + Ring::kRowBytes)[st.sm.head[i] + (int)((first >> 1) & 1)]);
+        } else if (mode() != kWeightsPerLane) {
           wv = to_acc<T>(reinterpret_cast<const T*>(entry + Ring::kRowBytes)[st.sm.head[i]]);
         } else if constexpr (sizeof(T) == 2) {
           const WWord word = reinterpret_cast<const WWord*>(entry + Ring::kRowBytes)[lane + 32 * i];

@@ -74,6 +74,8 @@ SHAPES = [(1, 16), (4, 32), (8, 64), (2, 64), (1, 128), (3, 5), (1, 1), (2, 12),
     (3, 8, th.float32, th.int32), (2, 16, th.float32, th.int64), (3, 16, th.bfloat16, th.int32),
     # 2-byte weights that travel as 4-byte words (an even number of heads: 4, 8 and 12 bytes per edge)
     (2, 16, th.bfloat16, th.int32), (4, 32, th.bfloat16, th.int64), (6, 8, th.bfloat16, th.int32),
+    # ... and as the words that cover an odd number of them (rows start in either half of a word)
+    (1, 32, th.bfloat16, th.int32), (5, 8, th.bfloat16, th.int64), (1, 128, th.bfloat16, th.int32),
 ])
 def test_vector_spmm(name, g, cs, h, d, dtype, idt):
     if g.n_dst > g.n_src:
@@ -91,6 +93,24 @@ def test_vector_spmm(name, g, cs, h, d, dtype, idt):
     assert_close(ded, want_ded, rt, at * scale, "dedata")
     assert_close(dx, want_dx, rt, at * max(1.0, float(want_dx.abs().max())), "dx")
     assert ded.shape == w.shape and dx.shape == x.shape
+
+
+@pytest.mark.parametrize("h", [1, 2, 3, 4])
+@pytest.mark.parametrize("lead,tail", [(1, 0), (1, 1), (2, 1), (0, 1)])
+def test_vector_spmm_bf16_weights_at_any_2_byte_alignment(h, lead, tail):
+    """bfloat16 edge weights in a view that starts `lead` elements into its allocation and stops `tail` elements
+    before its end: rows begin in either half of an aligned 4-byte word, and the words at the tensor's two ends
+    are only half inside it.  The elements around the view hold NaN: a weight read from outside would show."""
+    g = ZOO[0][1]
+    r = chunked(g, 32, dtype=th.int32)
+    w = _row_weights(g, h, th.bfloat16, 1)
+    x = _nodes(g.n_src, h, 32, th.bfloat16, 2)
+    box = th.full((lead + w.numel() + tail,), float("nan"), dtype=th.bfloat16, device=DEV)
+    view = box[lead:lead + w.numel()].view(w.shape)
+    view.copy_(w)
+    assert view.is_contiguous() and view.data_ptr() % 4 == (2 * lead) % 4
+    y = graphop.vector_spmm_forward(*_cuda(r), view, x.to(DEV))
+    assert_close(y, orc.vector_spmm_forward(*r, w, x), TOL[th.bfloat16][0], _atol(g, th.bfloat16), "y")
 
 
 def test_vector_spmm_rectangular_num_dst():
