@@ -68,3 +68,47 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_capi, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         _capi.lib()
+
+
+C_CONSUMER = r"""
+#include <stdio.h>
+#include <string.h>
+#include "graphop_b200.h"
+#include "graphop_dlpack.h"
+
+int main(void) {
+  /* host-only calls: none of them needs a GPU */
+  if (graphop_version() < 100) return 1;
+  if (!graphop_error_string(GRAPHOP_OK) || !graphop_error_string(GRAPHOP_ERR_INVALID_ARGUMENT)) return 2;
+  if (strcmp(graphop_error_string(GRAPHOP_OK), graphop_error_string(GRAPHOP_ERR_WORKSPACE)) == 0) return 3;
+  if (graphop_workspace_bytes(GRAPHOP_OP_SPMM_FWD, 1000, 100, 4, 32, 4, 4) == 0) return 4;
+  if (graphop_plan_bytes(1000, 100, 100, 4) < sizeof(graphop_plan_t)) return 5;
+  /* argument checks come before any CUDA call: a null graph is refused, not dereferenced */
+  if (graphop_vector_spmm_forward_f32_i32(NULL, NULL, NULL, NULL, NULL, NULL, NULL, 4, 10, 5, 5, 1, -3, NULL, 0, NULL)
+      == GRAPHOP_OK) return 6;
+  {
+    graphop_dltensor_t t;
+    memset(&t, 0, sizeof t);
+    if (sizeof t != 48 && sizeof t != 40) return 7;   /* DLTensor's layout: 48 bytes on LP64 */
+  }
+  printf("ok %d\n", graphop_version());
+  return 0;
+}
+"""
+
+
+def test_a_plain_c_program_compiles_links_and_runs_against_the_headers(tmp_path):
+    """The boundary is a C ABI: a C99 translation unit includes both headers (no C++, no torch), links the shared
+    library and calls its host-only entry points."""
+    lib = _capi.LIB_PATH
+    assert os.path.exists(lib)
+    src = tmp_path / "consumer.c"
+    src.write_text(C_CONSUMER)
+    exe = tmp_path / "consumer"
+    inc = os.path.join(ROOT, "include")
+    cmd = ["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I" + inc, str(src), "-o", str(exe),
+           "-L" + os.path.dirname(lib), "-l:" + os.path.basename(lib), "-Wl,-rpath," + os.path.dirname(lib)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.startswith("ok "), (run.returncode, run.stdout, run.stderr)
