@@ -465,7 +465,7 @@ struct AttnBwdDstOp {
 
   __device__ __forceinline__ void setup(State& st, int lane) const { st.sm.init(lane, S, V, D, 0); }
   __device__ __forceinline__ void begin(State& st, int node, int lane) const { begin_ordered<0>(st, node, lane); }
-  // kAscLph > 0: one slot per lane, that many lanes per head, delta summed in the ascending butterfly order
+  // kAscLph > 0: that many lanes per head (a head inside one of the lane's slots), delta summed in the ascending butterfly order
   // (the order in which the staged fast path sums dO . v)
   template <int kAscLph>
   __device__ __forceinline__ void begin_ordered(State& st, int node, int) const {
@@ -487,8 +487,12 @@ struct AttnBwdDstOp {
         st.lse[i] = __ldg(lse + (long long)node * H + st.sm.head[i]);
       }
     }
-    if constexpr (kAscLph > 0) dl[0] = reduce_ascending<kAscLph, A>(dl[0]);
-    else reduce_heads<A, R>(dl, lph);
+    if constexpr (kAscLph > 0) {
+#pragma unroll
+      for (int i = 0; i < R; ++i) dl[i] = reduce_ascending<kAscLph, A>(dl[i]);
+    } else {
+      reduce_heads<A, R>(dl, lph);
+    }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       st.delta[i] = dl[i];

@@ -428,14 +428,15 @@ __device__ __forceinline__ A reduce_transposed(const A (&s)[U], int lane) {
   for (int o = U; o < LPH; o <<= 1) keep += __shfl_xor_sync(kFull, keep, o);
   return keep;
 }
-// Batch size, scratch and lane roles of the ops that reduce with reduce_transposed: rows of one 16-byte slot
-// per lane, 2 to 32 lanes per head.  Lane l of a head's group owns edge l & (U - 1) of the batch; the first U
+// Batch size, scratch and lane roles of the ops that reduce with reduce_transposed: rows of one or two 16-byte
+// slots per lane (a lane's two slots belong to two heads, 32 / LPH apart), 2 to 32 lanes per head.  Lane l of a head's group owns edge l & (U - 1) of the batch; the first U
 // lanes of each group publish their edge's scalar in the warp's scratch, U consecutive values per head.
 constexpr int kFastBatch = GK_FAST_BATCH;
-constexpr int kFastScratch = 128;  // U values of kAccBytes for each of the 32 / LPH heads of a 32-slot row
+constexpr int kFastScratch = 128;  // U values of kAccBytes for each of the 32 R / LPH heads of a row of 32 R slots
 template <int R, int LPH, int kAccBytes = 4> struct FastShape {
-  static constexpr bool value = R == 1 && LPH >= kFastBatch && (LPH == 2 || LPH == 4 || LPH == 8 || LPH == 16 || LPH == 32) &&
-                                (32 / (LPH ? LPH : 1)) * kFastBatch * kAccBytes <= kFastScratch;
+  static constexpr bool value = (R == 1 || R == 2) && LPH >= kFastBatch &&
+                                (LPH == 2 || LPH == 4 || LPH == 8 || LPH == 16 || LPH == 32) &&
+                                (32 * R / (LPH ? LPH : 1)) * kFastBatch * kAccBytes <= kFastScratch;
 };
 template <int U, typename A>
 __device__ __forceinline__ void lds_batch(A (&d)[U], const A* p) {
@@ -764,44 +765,53 @@ struct AttnFwdStaged : AttnFwdOp<T, V, R, kBias> {
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_fast(State& st, const unsigned char* ring, int cnt, int lane) const {
     constexpr int U = kFastBatch;
-    A s[U];
+    A s[R][U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      s[u] = A(0);
-      if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
-        A kv[V];
-        load_key(kv, GK_RING_SLOT(u), lane);
-        s[u] = st.q[0][0] * kv[0];
 #pragma unroll
-        for (int e = 1; e < V; ++e) s[u] += st.q[0][e] * kv[e];
+      for (int i = 0; i < R; ++i) {
+        s[i][u] = A(0);
+        if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
+          A kv[V];
+          load_key(kv, GK_RING_SLOT(u), lane + 32 * i);
+          s[i][u] = st.q[i][0] * kv[0];
+#pragma unroll
+          for (int e = 1; e < V; ++e) s[i][u] += st.q[i][e] * kv[e];
+        }
       }
     }
-    A mine = reduce_transposed<LPH, U, A>(s, lane);
-    if (!kFullBatch && (lane & (U - 1)) >= cnt) mine = neg_inf<A>();  // positions past the batch: probability 0
-    A* sc = reinterpret_cast<A*>(st.scratch) + (lane / LPH) * U;
-    if ((lane & (LPH - 1)) < U) sc[lane & (U - 1)] = mine;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      A mine = reduce_transposed<LPH, U, A>(s[i], lane);
+      if (!kFullBatch && (lane & (U - 1)) >= cnt) mine = neg_inf<A>();  // positions past the batch: probability 0
+      A* sc = reinterpret_cast<A*>(st.scratch) + ((lane + 32 * i) / LPH) * U;
+      if ((lane & (LPH - 1)) < U) sc[lane & (U - 1)] = mine;
+    }
     __syncwarp();
-    A sv[U];
-    lds_batch<U, A>(sv, sc);
-    A mn = st.m[0];
 #pragma unroll
-    for (int u = 0; u < U; ++u) mn = sv[u] > mn ? sv[u] : mn;
-    const A corr = gk_exp2(st.m[0] - mn);  // m = -inf at a node's first batch: 2^-inf = 0
-    A p[U];
-    A psum = A(0);
+    for (int i = 0; i < R; ++i) {
+      A sv[U];
+      lds_batch<U, A>(sv, reinterpret_cast<const A*>(st.scratch) + ((lane + 32 * i) / LPH) * U);
+      A mn = st.m[i];
 #pragma unroll
-    for (int u = 0; u < U; ++u) { p[u] = gk_exp2(sv[u] - mn); psum += p[u]; }
-    st.m[0] = mn;
-    st.l[0] = st.l[0] * corr + psum;
+      for (int u = 0; u < U; ++u) mn = sv[u] > mn ? sv[u] : mn;
+      const A corr = gk_exp2(st.m[i] - mn);  // m = -inf at a node's first batch: 2^-inf = 0
+      A p[U];
+      A psum = A(0);
 #pragma unroll
-    for (int e = 0; e < V; ++e) st.acc[0][e] *= corr;
+      for (int u = 0; u < U; ++u) { p[u] = gk_exp2(sv[u] - mn); psum += p[u]; }
+      st.m[i] = mn;
+      st.l[i] = st.l[i] * corr + psum;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (kFullBatch || u < cnt) {
-        A vv[V];
-        lds_acc<T, V>(vv, GK_RING_SLOT(u) + Ring::kRowBytes + lane * 16);
+      for (int e = 0; e < V; ++e) st.acc[i][e] *= corr;
 #pragma unroll
-        for (int e = 0; e < V; ++e) st.acc[0][e] += p[u] * vv[e];
+      for (int u = 0; u < U; ++u) {
+        if (kFullBatch || u < cnt) {
+          A vv[V];
+          lds_acc<T, V>(vv, GK_RING_SLOT(u) + Ring::kRowBytes + (lane + 32 * i) * 16);
+#pragma unroll
+          for (int e = 0; e < V; ++e) st.acc[i][e] += p[u] * vv[e];
+        }
       }
     }
   }
@@ -950,45 +960,54 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R, kBias> {
   template <bool kFullBatch>
   __device__ __forceinline__ void consume_fast(State& st, const unsigned char* ring, int cnt, int lane) const {
     constexpr int U = kFastBatch;
-    A s[U], dp[U];
+    A s[R][U], dp[R][U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      s[u] = A(0);
-      dp[u] = A(0);
-      if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
-        const unsigned char* entry = GK_RING_SLOT(u);
-        A kv[V], vv[V];
-        load_key(kv, entry, lane);
-        lds_acc<T, V>(vv, entry + Ring::kRowBytes + lane * 16);
-        s[u] = st.q[0][0] * kv[0];
-        dp[u] = st.g[0][0] * vv[0];
 #pragma unroll
-        for (int e = 1; e < V; ++e) { s[u] += st.q[0][e] * kv[e]; dp[u] += st.g[0][e] * vv[e]; }
+      for (int i = 0; i < R; ++i) {
+        s[i][u] = A(0);
+        dp[i][u] = A(0);
+        if (kFullBatch || u < cnt) {  // a partial batch may end at the ring's last entry: nothing is read past it
+          const unsigned char* entry = GK_RING_SLOT(u);
+          A kv[V], vv[V];
+          load_key(kv, entry, lane + 32 * i);
+          lds_acc<T, V>(vv, entry + Ring::kRowBytes + (lane + 32 * i) * 16);
+          s[i][u] = st.q[i][0] * kv[0];
+          dp[i][u] = st.g[i][0] * vv[0];
+#pragma unroll
+          for (int e = 1; e < V; ++e) { s[i][u] += st.q[i][e] * kv[e]; dp[i][u] += st.g[i][e] * vv[e]; }
+        }
       }
     }
-    const A s_mine = reduce_transposed<LPH, U, A>(s, lane);
-    const A dp_mine = reduce_transposed<LPH, U, A>(dp, lane);
-    const A p = gk_exp2(s_mine - st.lse[0]);
-    A ds = p * (dp_mine - st.delta[0]) * this->scale;
     const bool live = kFullBatch || (lane & (U - 1)) < cnt;
-    if (!live) ds = A(0);
-    if (st.pdw[0] && live) {
-      const unsigned pairb = (unsigned)this->Hp * (unsigned)sizeof(EdgePair<A>);
-      *reinterpret_cast<EdgePair<A>*>(st.pdw[0] + (unsigned long long)(unsigned)(st.tile_base + st.batch_pos) * pairb) =
-          EdgePair<A>{p, ds};
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const A s_mine = reduce_transposed<LPH, U, A>(s[i], lane);
+      const A dp_mine = reduce_transposed<LPH, U, A>(dp[i], lane);
+      const A p = gk_exp2(s_mine - st.lse[i]);
+      A ds = p * (dp_mine - st.delta[i]) * this->scale;
+      if (!live) ds = A(0);
+      if (st.pdw[i] && live) {
+        const unsigned pairb = (unsigned)this->Hp * (unsigned)sizeof(EdgePair<A>);
+        *reinterpret_cast<EdgePair<A>*>(st.pdw[i] + (unsigned long long)(unsigned)(st.tile_base + st.batch_pos) * pairb) =
+            EdgePair<A>{p, ds};
+      }
+      A* sc = reinterpret_cast<A*>(st.scratch) + ((lane + 32 * i) / LPH) * U;
+      if ((lane & (LPH - 1)) < U) sc[lane & (U - 1)] = ds;
     }
-    A* sc = reinterpret_cast<A*>(st.scratch) + (lane / LPH) * U;
-    if ((lane & (LPH - 1)) < U) sc[lane & (U - 1)] = ds;
     __syncwarp();
-    A dsv[U];
-    lds_batch<U, A>(dsv, sc);
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (kFullBatch || u < cnt) {
-        A kv[V];
-        load_key(kv, GK_RING_SLOT(u), lane);
+    for (int i = 0; i < R; ++i) {
+      A dsv[U];
+      lds_batch<U, A>(dsv, reinterpret_cast<const A*>(st.scratch) + ((lane + 32 * i) / LPH) * U);
 #pragma unroll
-        for (int e = 0; e < V; ++e) st.acc[0][e] += dsv[u] * kv[e];
+      for (int u = 0; u < U; ++u) {
+        if (kFullBatch || u < cnt) {
+          A kv[V];
+          load_key(kv, GK_RING_SLOT(u), lane + 32 * i);
+#pragma unroll
+          for (int e = 0; e < V; ++e) st.acc[i][e] += dsv[u] * kv[e];
+        }
       }
     }
   }
@@ -1024,8 +1043,12 @@ struct AttnBwdDstStaged : AttnBwdDstOp<T, V, R, kBias> {
       }
       // the fast path sums dO.v in the ascending order: delta the same way, so that a node with a single edge
       // gets dp - delta = 0 exactly
-      if constexpr (kFast) dl[0] = reduce_ascending<LPH, A>(dl[0]);
-      else reduce_heads_ct<LPH, A, R>(dl, this->lph);
+      if constexpr (kFast) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) dl[i] = reduce_ascending<LPH, A>(dl[i]);
+      } else {
+        reduce_heads_ct<LPH, A, R>(dl, this->lph);
+      }
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         st.delta[i] = dl[i];
